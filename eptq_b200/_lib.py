@@ -1,0 +1,70 @@
+"""ctypes binding of ``libeptq_b200.so`` (the C ABI in ``include/eptq_b200.h``).
+
+The library is the only compute path of this package.  If it is missing or a
+call fails, a ``RuntimeError`` is raised; nothing falls back to PyTorch.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+from typing import Optional
+
+LIB_PATH = Path(__file__).resolve().parent / "lib" / "libeptq_b200.so"
+
+EPTQ_E8, EPTQ_E8D4 = 0, 1
+QUANTIZER_ID = {"e8_lattice": EPTQ_E8, "e8_d4": EPTQ_E8D4}
+
+# Every symbol the header declares, with (restype, argtypes).
+_vp, _i, _sz = C.c_void_p, C.c_int, C.c_size_t
+EXPORTS = {
+    "eptq_abi_version": (_i, []),
+    "eptq_strerror": (C.c_char_p, [_i]),
+    "eptq_launch_count": (C.c_uint64, []),
+    "eptq_workspace_bytes": (_sz, [_i, _i, _i]),
+    "eptq_e8_forward": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _sz, _vp]),
+    "eptq_e8d4_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _sz, _vp]),
+    "eptq_linear_forward": (_i, [_vp, _vp, _vp, _i, _vp, _sz, _vp]),
+    "eptq_dequantize": (_i, [_vp, _vp, _vp]),
+}
+
+
+class EptqLayer(C.Structure):
+    """struct EptqLayer of include/eptq_b200.h."""
+    _fields_ = [
+        ("quantizer", C.c_int32), ("M", C.c_int32), ("N", C.c_int32),
+        ("n_masked", C.c_int32), ("qb_size", C.c_int32), ("table_rows", C.c_int32),
+        ("Q", _vp), ("table32", _vp), ("table16", _vp), ("g", _vp), ("h", _vp),
+        ("O_vals", _vp), ("O_col", _vp), ("O_row_ptr", _vp), ("bias", _vp), ("S_group", _vp),
+    ]
+
+
+_lib: Optional[C.CDLL] = None
+
+
+def load() -> C.CDLL:
+    """Load the library (once) and declare its prototypes."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m eptq_b200.build` "
+            "(the eptq_b200 kernels have no fallback path)")
+    lib = C.CDLL(str(LIB_PATH))
+    for name, (res, args) in EXPORTS.items():
+        fn = getattr(lib, name)          # AttributeError if the symbol is not exported
+        fn.restype, fn.argtypes = res, args
+    if lib.eptq_abi_version() != 1:
+        raise RuntimeError("libeptq_b200.so has an unexpected ABI version")
+    _lib = lib
+    return lib
+
+
+def check(status: int, what: str) -> None:
+    if status != 0:
+        msg = load().eptq_strerror(status).decode()
+        raise RuntimeError(f"{what}: {msg} (eptq status {status})")
+
+
+def launch_count() -> int:
+    return int(load().eptq_launch_count())

@@ -1,0 +1,51 @@
+// Shared device/host helpers of the eptq_b200 kernels (sm_100a only).
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <atomic>
+
+#include "../../include/eptq_b200.h"
+
+#if defined(__CUDA_ARCH__) && (__CUDA_ARCH__ < 1000)
+#error "eptq_b200 kernels are written for sm_100a"
+#endif
+
+namespace eptq {
+
+constexpr unsigned kMarkerIndex = 65535u;   // codebook index that marks a critical block
+constexpr int kMaxSplits = 16;              // column splits a GEMV may use (sizes the scratch)
+constexpr int kRowsPerCta = 8;              // Q rows (groups of 8 outputs) per SIMT GEMV block
+
+extern std::atomic<uint64_t> g_launches;    // kernels launched by this library
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Scratch layout shared by every GEMV variant:
+//   [0, counter_bytes)              unsigned arrival counters, zero between calls
+//   [counter_bytes, ...)            float partial sums [split][batch][8*M]
+inline size_t counter_bytes(int M, int B) {
+    size_t n = (static_cast<size_t>(M) / kRowsPerCta + 2) * static_cast<size_t>(B > 0 ? B : 1);
+    return (n * sizeof(unsigned) + 255) & ~static_cast<size_t>(255);
+}
+inline size_t partial_bytes(int M, int B) {
+    return static_cast<size_t>(kMaxSplits) * static_cast<size_t>(B) * 8u * static_cast<size_t>(M) * sizeof(float);
+}
+
+__device__ __forceinline__ uint4 ldg128(const void* p) {
+    return __ldg(reinterpret_cast<const uint4*>(p));
+}
+
+__device__ __forceinline__ void unpack8(const uint4& v, float (&out)[8]) {
+    const __half2* h2 = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float2 f = __half22float2(h2[i]);
+        out[2 * i] = f.x;
+        out[2 * i + 1] = f.y;
+    }
+}
+
+}  // namespace eptq

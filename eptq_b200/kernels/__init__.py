@@ -1,0 +1,188 @@
+"""Op-level API of the quantized-linear path.
+
+``e8_forward`` and ``e8d4_forward`` keep the reference's signatures
+(kernels/__init__.py:50-84, csrc/eptq_kernels.h:15-41) and are registered as
+``torch.library.custom_op`` with fake implementations, so ``torch.compile`` and
+CUDA-graph capture see them as single ops, as in the reference
+(kernels/__init__.py:46-91).  They are registered under the namespace
+``eptq_b200`` so that the reference package can be imported next to this one.
+
+``linear_forward`` takes the whole layer (group scales included) and
+``dequantize_layer`` reconstructs the fp16 weight on the GPU, bit-for-bit the
+reference's ``dequantize_layer`` (algorithms/eptq.py:406-471).
+
+Inputs must be CUDA tensors; a CPU tensor raises -- there is no CPU path.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from .. import _lib
+
+__all__ = ["e8_forward", "e8d4_forward", "linear_forward", "dequantize_layer", "workspace_for"]
+
+_workspaces: Dict[Tuple[int, int], torch.Tensor] = {}
+
+
+def workspace_for(device: torch.device, nbytes: int) -> torch.Tensor:
+    """Zero-initialised scratch for (device, current stream), grown on demand.
+
+    Calls ordered on one stream share it; the kernels leave it zeroed where they
+    need zeros.  Growing allocates, so size it before capturing a CUDA graph."""
+    stream = torch.cuda.current_stream(device)
+    key = (device.index if device.index is not None else torch.cuda.current_device(), stream.cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def _require_cuda(**tensors) -> None:
+    for name, t in tensors.items():
+        if t is not None and not t.is_cuda:
+            raise RuntimeError(f"eptq_b200: `{name}` must be a CUDA tensor (no CPU path exists)")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None or t.numel() == 0 else t.data_ptr()
+
+
+def _stream(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _check_common(Q, g, h, x):
+    if Q.dtype != torch.int16 or not Q.is_contiguous():
+        raise RuntimeError("Q must be a contiguous CUDA int16 tensor")
+    if x.dtype != torch.float16 or not x.is_contiguous():
+        raise RuntimeError("x must be a contiguous CUDA fp16 tensor")
+    if x.dim() != 2 or x.shape[1] != Q.shape[1]:
+        raise RuntimeError(f"x must have shape (B, {Q.shape[1]})")
+    if g.dtype != torch.float16 or h.dtype != torch.float16:
+        raise RuntimeError("g and h must be fp16")
+
+
+def _forward_impl(kind: str, Q, table, g, h, x, O_vals, O_col, O_row_ptr, bias) -> torch.Tensor:
+    _require_cuda(Q=Q, codebook=table, g=g, h=h, x=x, O_vals=O_vals, O_col=O_col, O_row_ptr=O_row_ptr)
+    _check_common(Q, g, h, x)
+    if table.dtype != torch.float16 or not table.is_contiguous():
+        raise RuntimeError("codebook must be a contiguous fp16 tensor")
+    lib = _lib.load()
+    M, N = Q.shape
+    B = x.shape[0]
+    y = torch.empty((B, M * 8), dtype=torch.float16, device=x.device)
+    if B == 0:
+        return y
+    nbytes = lib.eptq_workspace_bytes(M, N, B)
+    ws = workspace_for(x.device, nbytes)
+    with torch.cuda.device(x.device):
+        if kind == "e8_lattice":
+            st = lib.eptq_e8_forward(Q.data_ptr(), table.data_ptr(), table.shape[0], g.data_ptr(), h.data_ptr(),
+                                     x.data_ptr(), _ptr(O_vals), _ptr(O_col), O_row_ptr.data_ptr(), _ptr(bias),
+                                     y.data_ptr(), M, N, B, ws.data_ptr(), ws.numel(), _stream(x.device))
+        else:
+            if table.numel() != 2048:
+                raise RuntimeError("E8-D4 codes must hold 512 x 4 values")
+            st = lib.eptq_e8d4_forward(Q.data_ptr(), table.data_ptr(), g.data_ptr(), h.data_ptr(),
+                                       x.data_ptr(), _ptr(O_vals), _ptr(O_col), O_row_ptr.data_ptr(), _ptr(bias),
+                                       y.data_ptr(), M, N, B, ws.data_ptr(), ws.numel(), _stream(x.device))
+    _lib.check(st, f"eptq {kind} forward")
+    return y
+
+
+@torch.library.custom_op("eptq_b200::e8_forward", mutates_args=())
+def e8_forward(Q: torch.Tensor, codebook: torch.Tensor, g: torch.Tensor, h: torch.Tensor, x: torch.Tensor,
+               O_vals: torch.Tensor, O_col: torch.Tensor, O_row_ptr: torch.Tensor,
+               bias: torch.Tensor) -> torch.Tensor:
+    """E8 fused dequantise + GEMV.  Arguments as the reference's ``e8_forward``
+    (csrc/eptq_kernels.h:4-25); an empty ``bias`` tensor means no bias.  Returns a
+    new (B, 8M) fp16 tensor on x's device."""
+    return _forward_impl("e8_lattice", Q, codebook, g, h, x, O_vals, O_col, O_row_ptr, bias)
+
+
+@e8_forward.register_fake
+def _(Q, codebook, g, h, x, O_vals, O_col, O_row_ptr, bias):
+    return x.new_empty(x.shape[0], Q.shape[0] * 8, dtype=torch.float16)
+
+
+@torch.library.custom_op("eptq_b200::e8d4_forward", mutates_args=())
+def e8d4_forward(Q: torch.Tensor, codes: torch.Tensor, g: torch.Tensor, h: torch.Tensor, x: torch.Tensor,
+                 O_vals: torch.Tensor, O_col: torch.Tensor, O_row_ptr: torch.Tensor,
+                 bias: torch.Tensor) -> torch.Tensor:
+    """E8-D4 fused dequantise + GEMV.  ``codes`` is the fp16 (512, 4) table
+    (csrc/eptq_kernels.h:27-41)."""
+    return _forward_impl("e8_d4", Q, codes, g, h, x, O_vals, O_col, O_row_ptr, bias)
+
+
+@e8d4_forward.register_fake
+def _(Q, codes, g, h, x, O_vals, O_col, O_row_ptr, bias):
+    return x.new_empty(x.shape[0], Q.shape[0] * 8, dtype=torch.float16)
+
+
+def _make_desc(quantizer_type: str, Q, table32, table16, g, h, O_vals, O_col, O_row_ptr, bias, S_group,
+               qb_size: int) -> _lib.EptqLayer:
+    d = _lib.EptqLayer()
+    d.quantizer = _lib.QUANTIZER_ID[quantizer_type]
+    d.M, d.N = Q.shape
+    d.n_masked = int(O_col.shape[0]) if O_col is not None else 0
+    d.qb_size = int(qb_size) if S_group is not None else 0
+    tab = table16 if table16 is not None else table32
+    d.table_rows = 512 if quantizer_type == "e8_d4" else int(tab.shape[0])
+    d.Q = Q.data_ptr()
+    d.table32 = _ptr(table32)
+    d.table16 = _ptr(table16)
+    d.g, d.h = g.data_ptr(), h.data_ptr()
+    d.O_vals, d.O_col, d.O_row_ptr = _ptr(O_vals), _ptr(O_col), O_row_ptr.data_ptr()
+    d.bias, d.S_group = _ptr(bias), _ptr(S_group)
+    return d
+
+
+@torch.library.custom_op("eptq_b200::linear_forward", mutates_args=())
+def linear_forward(x: torch.Tensor, Q: torch.Tensor, table16: torch.Tensor, table32: Optional[torch.Tensor],
+                   g: torch.Tensor, h: torch.Tensor, O_vals: torch.Tensor, O_col: torch.Tensor,
+                   O_row_ptr: torch.Tensor, bias: Optional[torch.Tensor], S_group: Optional[torch.Tensor],
+                   quantizer_type: str, qb_size: int) -> torch.Tensor:
+    """Layer forward from the full layer description: (B, in) fp16 -> (B, out) fp16,
+    group scales applied in the kernel."""
+    _require_cuda(Q=Q, table16=table16, g=g, h=h, x=x, O_row_ptr=O_row_ptr)
+    _check_common(Q, g, h, x)
+    lib = _lib.load()
+    M, N = Q.shape
+    B = x.shape[0]
+    y = torch.empty((B, M * 8), dtype=torch.float16, device=x.device)
+    if B == 0:
+        return y
+    desc = _make_desc(quantizer_type, Q, table32, table16, g, h, O_vals, O_col, O_row_ptr, bias, S_group, qb_size)
+    ws = workspace_for(x.device, lib.eptq_workspace_bytes(M, N, B))
+    with torch.cuda.device(x.device):
+        st = lib.eptq_linear_forward(C.byref(desc), x.data_ptr(), y.data_ptr(), B,
+                                     ws.data_ptr(), ws.numel(), _stream(x.device))
+    _lib.check(st, "eptq linear forward")
+    return y
+
+
+@linear_forward.register_fake
+def _(x, Q, table16, table32, g, h, O_vals, O_col, O_row_ptr, bias, S_group, quantizer_type, qb_size):
+    return x.new_empty(x.shape[0], Q.shape[0] * 8, dtype=torch.float16)
+
+
+def dequantize_layer(Q: torch.Tensor, table32: torch.Tensor, g: torch.Tensor, h: torch.Tensor,
+                     O_vals: torch.Tensor, O_col: torch.Tensor, O_row_ptr: torch.Tensor,
+                     S_group: Optional[torch.Tensor], quantizer_type: str, qb_size: int = 0) -> torch.Tensor:
+    """fp16 (out, in) weight, bit-identical to the reference's ``dequantize_layer``
+    (algorithms/eptq.py:406-471) given the same fp32 table."""
+    _require_cuda(Q=Q, table32=table32, g=g, h=h, O_row_ptr=O_row_ptr)
+    if table32.dtype != torch.float32 or not table32.is_contiguous():
+        raise RuntimeError("table32 must be a contiguous fp32 tensor")
+    lib = _lib.load()
+    M, N = Q.shape
+    W = torch.empty((M * 8, N), dtype=torch.float16, device=Q.device)
+    desc = _make_desc(quantizer_type, Q, table32, None, g, h, O_vals, O_col, O_row_ptr, None, S_group, qb_size)
+    with torch.cuda.device(Q.device):
+        st = lib.eptq_dequantize(C.byref(desc), W.data_ptr(), _stream(Q.device))
+    _lib.check(st, "eptq dequantize")
+    return W

@@ -1,0 +1,170 @@
+"""EPTQLinear: ``nn.Linear`` replacement that keeps the weight quantized.
+
+Same constructor, class method, buffers and ``forward`` contract as the
+reference module (kernels/linear.py:20-219): buffers ``Q, g, h, O_vals, O_col,
+O_row_ptr, bias``; a codebook shared between layers and moved by ``_apply``;
+inputs of any leading shape; non-fp16 activations are cast to fp16 and the
+result cast back.  Differences, all on purpose:
+
+* one compute path (the C-ABI library), chosen by batch size only -- no Triton,
+  no environment switches, no CPU fallback;
+* layers with group scales run in the kernel; the reference reconstructs an
+  fp16 weight at load time and calls ``F.linear`` (kernels/linear.py:97-120);
+* an fp32 copy of the codebook is kept next to the fp16 one, because bit-exact
+  reconstruction (``dequantize()`` and the prefill GEMM) needs the table the
+  reference's ``dequantize_layer`` reads.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.nn as nn
+
+from . import dequantize_layer, linear_forward
+
+MARKER = 32767     # int16 value that marks a critical block (index 65535 - 32768)
+
+_table_cache: dict = {}
+
+
+def _shared_table(codebook: torch.Tensor, dtype: torch.dtype, quantizer_type: str) -> torch.Tensor:
+    """One converted copy per (source tensor, dtype): layers of a model share it."""
+    key = (codebook.data_ptr(), codebook.device, tuple(codebook.shape), codebook.dtype, dtype,
+           codebook._version, quantizer_type)
+    hit = _table_cache.get(key)
+    if hit is not None:
+        return hit
+    tab = codebook.detach().to(dtype=dtype)
+    tab = tab.reshape(512, 4) if quantizer_type == "e8_d4" else tab
+    tab = tab.contiguous()
+    if len(_table_cache) > 64:
+        _table_cache.clear()
+    _table_cache[key] = tab
+    return tab
+
+
+class EPTQLinear(nn.Module):
+    """Quantized linear layer computing ``y = x W^T + bias`` straight from
+    ``Q`` (int16 (out/8, in)), the codebook, ``g``, ``h`` and the critical blocks."""
+
+    def __init__(
+        self,
+        Q: torch.Tensor,
+        codebook: torch.Tensor,
+        g: torch.Tensor,
+        h: torch.Tensor,
+        O_vals: torch.Tensor,
+        O_col: torch.Tensor,
+        O_row_ptr: torch.Tensor,
+        bias: Optional[torch.Tensor],
+        quantizer_type: str,
+        materialized_weight: Optional[torch.Tensor] = None,
+        S_group: Optional[torch.Tensor] = None,
+        codebook32: Optional[torch.Tensor] = None,
+    ):
+        super().__init__()
+        if quantizer_type not in ("e8_lattice", "e8_d4"):
+            raise ValueError(f"unknown quantizer_type {quantizer_type!r}")
+        self.in_features = Q.shape[1]
+        self.out_features = Q.shape[0] * 8
+        self.quantizer_type = quantizer_type
+
+        self.register_buffer("Q", Q.contiguous())
+        self.register_buffer("g", g.contiguous())
+        self.register_buffer("h", h.contiguous())
+        self.register_buffer("O_vals", O_vals.contiguous())
+        self.register_buffer("O_col", O_col.contiguous())
+        self.register_buffer("O_row_ptr", O_row_ptr.contiguous())
+        self.register_buffer("bias", bias.contiguous() if bias is not None else None)
+        self.register_buffer("S_group", S_group.contiguous() if S_group is not None else None)
+        # Accepted for signature compatibility; this implementation never needs it.
+        self.register_buffer("_materialized_weight",
+                             materialized_weight.contiguous() if materialized_weight is not None else None)
+        self.qb_size = self.out_features // S_group.shape[0] if S_group is not None else 0
+
+        # Shared between layers, therefore plain attributes, not buffers.
+        self._codebook = codebook
+        self._codebook32 = codebook32
+
+    def _apply(self, fn, *args, **kwargs):
+        super()._apply(fn, *args, **kwargs)
+        self._codebook = self._move_shared(self._codebook, fn)
+        if self._codebook32 is not None:
+            moved = self._move_shared(self._codebook32, fn)
+            self._codebook32 = moved if moved.dtype == torch.float32 else self._codebook32.to(moved.device)
+        return self
+
+    @staticmethod
+    def _move_shared(t: torch.Tensor, fn) -> torch.Tensor:
+        key = ("moved", t.data_ptr(), t.device, t.dtype, tuple(t.shape), t._version)
+        out = fn(t)
+        if out is t:
+            return t
+        hit = _table_cache.get(key)
+        if hit is not None and hit.device == out.device and hit.dtype == out.dtype:
+            return hit
+        _table_cache[key] = out
+        return out
+
+    @classmethod
+    def from_quantized_data(cls, quant_data, codebook: torch.Tensor, quantizer_type: str) -> "EPTQLinear":
+        """Build the layer from a ``QuantizedLayerData`` and the codebook already
+        divided by its radius: (rows, 8) for E8, (4, 128, 4) or (512, 4) for E8-D4."""
+        Q = quant_data.Q
+        M = Q.shape[0]
+        cb16 = _shared_table(codebook, torch.float16, quantizer_type)
+        cb32 = _shared_table(codebook, torch.float32, quantizer_type) if codebook.dtype == torch.float32 else None
+
+        # Markers in row-major order: this is the order of the rows of O
+        # (algorithms/eptq.py:376-378), so O needs no permutation.
+        rows, cols = (Q == MARKER).nonzero(as_tuple=True)
+        n_masked = rows.shape[0]
+        if quant_data.O.shape[0] != n_masked:
+            raise AssertionError(
+                f"O shape mismatch: got {quant_data.O.shape[0]} values but found {n_masked} masked positions in Q")
+        counts = torch.bincount(rows, minlength=M)
+        row_ptr = torch.zeros(M + 1, dtype=torch.int32, device=Q.device)
+        row_ptr[1:] = counts.cumsum(0).to(torch.int32)
+
+        return cls(
+            Q=Q, codebook=cb16,
+            g=quant_data.g.to(torch.float16), h=quant_data.h.to(torch.float16),
+            O_vals=quant_data.O.to(torch.float16).reshape(-1, 8),
+            O_col=cols.to(torch.int32), O_row_ptr=row_ptr,
+            bias=quant_data.bias.to(torch.float16) if quant_data.bias is not None else None,
+            quantizer_type=quantizer_type,
+            S_group=quant_data.S_group.to(torch.float16) if quant_data.S_group is not None else None,
+            codebook32=cb32,
+        )
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if not x.is_cuda:
+            raise RuntimeError("EPTQLinear runs on CUDA tensors only (there is no CPU path)")
+        lead, out_dtype = x.shape[:-1], x.dtype
+        x2 = x.reshape(-1, self.in_features)
+        if x2.dtype != torch.float16:
+            x2 = x2.half()
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        y = linear_forward(x2, self.Q, self._codebook, self._codebook32, self.g, self.h,
+                           self.O_vals, self.O_col, self.O_row_ptr, self.bias, self.S_group,
+                           self.quantizer_type, self.qb_size)
+        if out_dtype != torch.float16:
+            y = y.to(out_dtype)
+        return y.reshape(*lead, self.out_features)
+
+    def dequantize(self) -> torch.Tensor:
+        """fp16 (out, in) weight reconstructed on the GPU, bit-identical to the
+        reference's ``dequantize_layer`` when the layer was built from an fp32 codebook."""
+        if self._codebook32 is None:
+            raise RuntimeError("this layer was built from an fp16 codebook; exact reconstruction needs the fp32 table")
+        return dequantize_layer(self.Q, self._codebook32, self.g, self.h, self.O_vals, self.O_col,
+                                self.O_row_ptr, self.S_group, self.quantizer_type, self.qb_size)
+
+    def extra_repr(self) -> str:
+        return (f"in={self.in_features}, out={self.out_features}, quantizer={self.quantizer_type}, "
+                f"n_masked={self.O_col.shape[0]}")
+
+
+QuantizedLinear = EPTQLinear

@@ -1,0 +1,151 @@
+/*
+ * eptq_b200 -- C ABI of the B200 (sm_100a) quantized-linear inference path.
+ *
+ * Plain C, no torch types: every pointer is a raw CUDA device pointer owned by
+ * the caller, every size an int, `stream` a cudaStream_t passed as void*.
+ * Calls are asynchronous on `stream`, never synchronise, never allocate or free
+ * device memory and keep no pointer after they return.  Every function returns
+ * an EptqStatus; eptq_strerror() turns it into text.
+ *
+ * The entry points replace the reference's pybind module `_eptq_cuda`
+ * (csrc/binding.cpp:4-16) and the C++ functions behind it
+ * (csrc/eptq_kernels.h:15-41, csrc/eptq_kernels.cu:466-579).
+ */
+#ifndef EPTQ_B200_H
+#define EPTQ_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define EPTQ_ABI_VERSION 1
+
+typedef enum EptqStatus {
+    EPTQ_OK = 0,
+    EPTQ_ERR_NULL = 1,        /* a required pointer is null                         */
+    EPTQ_ERR_SHAPE = 2,       /* M, N, B, qb_size or table size out of range        */
+    EPTQ_ERR_ALIGN = 3,       /* a pointer is not aligned for 128-bit access        */
+    EPTQ_ERR_QUANTIZER = 4,   /* quantizer id is neither EPTQ_E8 nor EPTQ_E8D4      */
+    EPTQ_ERR_WORKSPACE = 5,   /* workspace missing or smaller than required         */
+    EPTQ_ERR_LAUNCH = 6,      /* the CUDA runtime rejected a launch or set-up call  */
+    EPTQ_ERR_UNSUPPORTED = 7, /* valid arguments, but no kernel covers them         */
+    EPTQ_ERR_TIMEOUT = 8      /* a bounded device-side wait ran out                 */
+} EptqStatus;
+
+enum { EPTQ_E8 = 0, EPTQ_E8D4 = 1 };
+
+/*
+ * One quantized linear layer, as the reference stores it in
+ * `QuantizedLayerData` (config.py:98-159) plus the side tables
+ * `EPTQLinear.from_quantized_data` derives at load time
+ * (kernels/linear.py:122-139).
+ *
+ *   Q          int16 (M, N) row-major, M = out_features/8, N = in_features.
+ *              Stored value = codebook index - 32768; 32767 marks a critical
+ *              block whose 8 values live in O_vals.
+ *   table32    fp32 codebook already divided by the radius: E8 (table_rows, 8),
+ *              E8-D4 (512, 4) = (4 classes, 128 codes, 4 dims) flattened.
+ *              Needed for bit-exact reconstruction (eptq_dequantize, eptq_gemm).
+ *   table16    the same table rounded to fp16 (what the reference's kernels
+ *              read, kernels/linear.py:93-95).  Needed by the GEMV.
+ *   g, h       fp16 row scales (8*M) and column scales (N).
+ *   O_vals     fp16 (n_masked, 8), ordered by row-major position of the markers.
+ *   O_col      int32 (n_masked) column of each marker, same order.
+ *   O_row_ptr  int32 (M+1) CSR row pointers into O_vals / O_col.
+ *   bias       fp16 (8*M) or NULL.
+ *   S_group    fp16 (8*M/qb_size, N) group scales or NULL (then qb_size = 0).
+ *              qb_size must be a multiple of 8.
+ */
+typedef struct EptqLayer {
+    int32_t quantizer;        /* EPTQ_E8 or EPTQ_E8D4 */
+    int32_t M;
+    int32_t N;
+    int32_t n_masked;
+    int32_t qb_size;
+    int32_t table_rows;       /* E8: rows of the table (<= 65535); E8-D4: 512 */
+    const int16_t* Q;
+    const float* table32;
+    const uint16_t* table16;
+    const uint16_t* g;
+    const uint16_t* h;
+    const uint16_t* O_vals;
+    const int32_t* O_col;
+    const int32_t* O_row_ptr;
+    const uint16_t* bias;
+    const uint16_t* S_group;
+} EptqLayer;
+
+/* ABI version of the loaded library (EPTQ_ABI_VERSION at build time). */
+int eptq_abi_version(void);
+
+/* Text for a status code; never NULL. */
+const char* eptq_strerror(int status);
+
+/* Number of kernels this library has launched in the calling process since it
+ * was loaded (all entry points, all streams).  For launch accounting only. */
+uint64_t eptq_launch_count(void);
+
+/*
+ * Bytes of device scratch eptq_linear_forward / eptq_e8_forward /
+ * eptq_e8d4_forward may need for a layer of this shape at batch B.  The caller
+ * allocates it once (256-byte aligned), zero-fills it once, and may reuse it
+ * for every call that is ordered on one stream; the kernels return it zeroed
+ * where it must be.  Calls that may overlap on the GPU need separate scratch.
+ */
+size_t eptq_workspace_bytes(int M, int N, int B);
+
+/*
+ * Fused dequantise + matrix-vector product for decode, the replacement of
+ * `e8_forward` (csrc/eptq_kernels.h:15-25, csrc/eptq_kernels.cu:563-570).
+ * Same arguments with raw pointers: Q (M,N) int16; codebook fp16
+ * (table_rows, 8); g (8M); h (N); x (B,N) fp16 contiguous; O_vals (n,8);
+ * O_col (n); O_row_ptr (M+1); bias (8M) or NULL; y (B, 8M) fp16 written by the
+ * call.  Unlike the reference there is no M % 4 restriction.
+ */
+int eptq_e8_forward(const int16_t* Q, const uint16_t* codebook, int table_rows,
+                    const uint16_t* g, const uint16_t* h, const uint16_t* x,
+                    const uint16_t* O_vals, const int32_t* O_col,
+                    const int32_t* O_row_ptr, const uint16_t* bias,
+                    uint16_t* y, int M, int N, int B,
+                    void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Same for the E8-D4 codebook, the replacement of `e8d4_forward`
+ * (csrc/eptq_kernels.h:31-41, csrc/eptq_kernels.cu:572-579).  `codes` is the
+ * fp16 (512, 4) table; an index unpacks as type = (idx>>14)&3, i = (idx>>7)&127,
+ * j = idx&127 and decodes to [codes[type*128+i], codes[type*128+j]].
+ */
+int eptq_e8d4_forward(const int16_t* Q, const uint16_t* codes,
+                      const uint16_t* g, const uint16_t* h, const uint16_t* x,
+                      const uint16_t* O_vals, const int32_t* O_col,
+                      const int32_t* O_row_ptr, const uint16_t* bias,
+                      uint16_t* y, int M, int N, int B,
+                      void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Layer forward from the full descriptor: y (B, 8M) fp16 = x (B, N) fp16
+ * through the quantized layer, including group scales (the reference has no
+ * kernel for those and multiplies by a pre-reconstructed weight instead,
+ * kernels/linear.py:97-120,159-164).  Chooses the decode GEMV or the
+ * tensor-core GEMM from B alone.
+ */
+int eptq_linear_forward(const EptqLayer* layer, const uint16_t* x, uint16_t* y,
+                        int B, void* workspace, size_t workspace_bytes,
+                        void* stream);
+
+/*
+ * Reconstruct the fp16 weight (8M, N) row-major, bit-for-bit what the
+ * reference's `dequantize_layer` returns (algorithms/eptq.py:406-471):
+ * table32 value (or the critical block from O_vals, which skips the group
+ * scale), times S_group, times g, times h, each an fp32 multiply in that
+ * order, one round-to-nearest-even to fp16.
+ */
+int eptq_dequantize(const EptqLayer* layer, uint16_t* W, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* EPTQ_B200_H */

@@ -1,0 +1,86 @@
+"""Host-side logic that needs no GPU: format round trip, codebooks, CSR build, error behaviour."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from eptq_b200 import QuantizedLayerData
+from eptq_b200.kernels.linear import EPTQLinear
+from eptq_b200.quantizers import E8D4Quantizer, E8LatticeQuantizer
+from eptq_b200.synthetic import make_layer
+from tests import util
+
+
+def test_layer_data_round_trip(tmp_path):
+    qd = make_layer(64, 48, seed=3, bias=True, qb_size=32)
+    qd.chosen_r = 1.7
+    qd.save(tmp_path / "l.pt")
+    back = QuantizedLayerData.load(tmp_path / "l.pt")
+    for k in ("Q", "g", "h", "O", "bias", "S_group"):
+        assert torch.equal(getattr(qd, k), getattr(back, k))
+    assert back.chosen_r == 1.7 and back.Q.device.type == "cpu"
+    assert set(qd.to_dict()) == {"Q", "g", "h", "O", "bias", "chosen_r", "S_group"}
+    assert set(make_layer(16, 8).to_dict()) == {"Q", "g", "h", "O"}
+
+
+def test_product_tables_equal_oracle_tables():
+    e8 = E8LatticeQuantizer(radius=1.6)
+    e8.remove_last()
+    assert np.array_equal(e8.points.numpy(), oracle.e8_table(1.6))
+    d4 = E8D4Quantizer(radius=1.75)
+    assert np.array_equal(d4.codes.numpy(), oracle.d4_table(1.75))
+    d4.set_radius(1.9)
+    assert np.array_equal(d4.codes.numpy(), oracle.d4_table(1.9))
+
+
+@pytest.mark.parametrize("kind", ["e8_lattice", "e8_d4"])
+def test_quantizer_dequant_matches_oracle_lookup(kind):
+    qd = make_layer(32, 24, seed=5, outlier_frac=0.0)
+    idx = qd.Q.int() + 32768
+    if kind == "e8_lattice":
+        q = E8LatticeQuantizer(radius=1.6)
+        q.remove_last()
+        tab = oracle.e8_table(1.6)
+    else:
+        q = E8D4Quantizer(radius=1.75)
+        tab = oracle.d4_table(1.75)
+    W = q.dequant(idx, 1.0).numpy()
+    one = np.ones(32, np.float16)
+    Wo = oracle.dequantize_layer(
+        oracle.LayerArrays(Q=qd.Q.numpy(), g=one, h=np.ones(24, np.float16), O=qd.O.numpy()), tab)
+    assert np.array_equal(W.astype(np.float16), Wo)
+
+
+def test_linear_builds_csr_like_oracle():
+    d = util.load_case("d4_marker_rows")
+    lin = EPTQLinear.from_quantized_data(util.case_qld(d), torch.from_numpy(oracle.d4_table(1.75)), "e8_d4")
+    col, ptr = oracle.csr_from_q(d["Q"])
+    assert np.array_equal(lin.O_col.numpy(), col) and np.array_equal(lin.O_row_ptr.numpy(), ptr)
+    assert lin.O_col.dtype == torch.int32 and lin.O_row_ptr.dtype == torch.int32
+    assert lin.in_features == 19 and lin.out_features == 24
+    assert lin._codebook.shape == (512, 4) and lin._codebook.dtype == torch.float16
+    assert "n_masked=21" in lin.extra_repr()
+
+
+def test_linear_rejects_inconsistent_O():
+    qd = make_layer(32, 16, seed=1, outlier_frac=0.1)
+    qd.O = qd.O[:-1]
+    with pytest.raises(AssertionError):
+        EPTQLinear.from_quantized_data(qd, torch.from_numpy(oracle.d4_table(1.75)), "e8_d4")
+
+
+def test_codebook_is_shared_between_layers():
+    tab = torch.from_numpy(oracle.d4_table(1.75))
+    a = EPTQLinear.from_quantized_data(make_layer(16, 8, seed=1), tab, "e8_d4")
+    b = EPTQLinear.from_quantized_data(make_layer(24, 8, seed=2), tab, "e8_d4")
+    assert a._codebook is b._codebook and a._codebook32 is b._codebook32
+
+
+def test_cpu_tensor_raises_instead_of_falling_back(built_library):
+    lin = EPTQLinear.from_quantized_data(make_layer(16, 8, seed=1), torch.from_numpy(oracle.d4_table(1.75)), "e8_d4")
+    with pytest.raises(RuntimeError, match="CUDA"):
+        lin(torch.zeros(1, 8, dtype=torch.float16))
+    from eptq_b200.kernels import e8d4_forward
+    with pytest.raises(RuntimeError, match="CUDA"):
+        e8d4_forward(lin.Q, lin._codebook, lin.g, lin.h, torch.zeros(1, 8, dtype=torch.float16),
+                     lin.O_vals, lin.O_col, lin.O_row_ptr, torch.empty(0, dtype=torch.float16))
