@@ -1,0 +1,354 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-linear decode path on B200.
+
+Workload (N = 1): the Llama-2-7B decode layer set of the baseline's second
+configuration -- q/k/v/o 4096x4096, gate/up 11008x4096, down 4096x11008, E8-D4
+codebook at radius 1.75, 0.2 % critical blocks -- for 32 decoder layers with
+distinct synthetic weights (1.66 GB of indices, far larger than the 126 MB L2,
+so every step streams from HBM).  One step = one pass over all 224 linears at
+batch B (default 1), i.e. the quantized-linear work of one decode token.
+
+  value     algorithmic GB/s with everything resident in HBM (step replayed
+            from a CUDA graph of C-ABI calls, CUDA-event timed)
+  e2e       the same GB/s through EPTQLinear.forward with the activations in
+            pinned HOST memory: H2D copy of x, 224 module calls, D2H copy of the
+            last output inside the timed region of every step
+  roofline  achieved GB/s of the GEMV launches against the measured HBM peak
+  cpu_baseline  the reconstruct-then-matmul CPU path (numpy port of the
+            reference's dequantize_layer, torch CPU matmul) on a bounded sample
+
+With --gpus N > 1 (torchrun) the linears are sharded tensor-parallel
+(q/k/v/gate/up by output rows, o/down by input columns with an NCCL
+all-reduce) and the whole-model bytes are divided by the slowest rank's time.
+
+`--impl reference` times the CPU path alone, on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "dequant_gemv_hbm_gbps"
+UNIT = "GB/s"
+KIND, RADIUS = "e8_d4", 1.75
+N_LAYERS = 32
+
+
+def algorithmic_bytes(out_f: int, in_f: int, n_masked: int, batch: int, bias: bool = False) -> int:
+    """Bytes one GEMV call must move: Q, critical blocks, g, h, x, y (+bias)."""
+    M = out_f // 8
+    return (2 * M * in_f + 16 * n_masked + 2 * out_f + 2 * in_f
+            + 2 * batch * in_f + 2 * batch * out_f + (2 * out_f if bias else 0))
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1])); mx.append(float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------- CPU path
+
+def cpu_reference_path(batch: int, reps: int, threads: int | None = None):
+    """Reference's CPU path on one decoder layer's seven linears: reconstruct once
+    (numpy port of dequantize_layer), then steady-state fp32 matmul on the host cores."""
+    import numpy as np
+    import torch
+    import oracle
+    from eptq_b200.synthetic import LLAMA2_7B_LINEARS, make_activations, make_layer
+
+    if threads:
+        torch.set_num_threads(threads)
+    table = oracle.d4_table(RADIUS)
+    weights, xs, total_bytes = [], [], 0
+    t0 = time.perf_counter()
+    for i, (name, (out_f, in_f)) in enumerate(LLAMA2_7B_LINEARS.items()):
+        qd = make_layer(out_f, in_f, seed=1000 + i)
+        arr = oracle.LayerArrays(Q=qd.Q.numpy(), g=qd.g.numpy(), h=qd.h.numpy(), O=qd.O.numpy())
+        weights.append(torch.from_numpy(oracle.dequantize_layer(arr, table)).float())
+        xs.append(make_activations(batch, in_f, seed=i).float())
+        total_bytes += algorithmic_bytes(out_f, in_f, qd.O.shape[0], batch)
+    reconstruct_s = time.perf_counter() - t0
+    times = []
+    for r in range(reps + 2):
+        t = time.perf_counter()
+        for W, x in zip(weights, xs):
+            _ = x @ W.T
+        times.append(time.perf_counter() - t)
+    med = statistics.median(times[2:])
+    return {"value": total_bytes / med / 1e9, "unit": UNIT, "cores": torch.get_num_threads(),
+            "host_cpus": os.cpu_count(), "kind": "port",
+            "sample": f"1 of {N_LAYERS} decoder layers (7 linears, batch {batch}), median of {reps} fp32 matmul passes; "
+                      f"one-time reconstruct {reconstruct_s:.2f} s excluded",
+            "ms_per_layer_set": med * 1e3, "reconstruct_s": reconstruct_s}
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    t0 = time.perf_counter()
+    reps = max(args.steps, 3)
+    res = cpu_reference_path(args.batch, reps)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": res["value"], "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": res["ms_per_layer_set"] * N_LAYERS,
+        "higher_is_better": True, "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "llama2-7b decode layer set, E8-D4 r=1.75, 0.2% critical blocks",
+                   "batch": args.batch, "layers": N_LAYERS, "cpu_sample_layers": 1},
+        "cpu_baseline": {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": res["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "wall_s": time.perf_counter() - t0,
+    }
+    print(json.dumps(line))
+
+
+# --------------------------------------------------------------------------- GPU path
+
+def run_gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+
+    from eptq_b200 import _lib
+    from eptq_b200.build import build_library
+    from eptq_b200.kernels import _make_desc
+    from eptq_b200.kernels.linear import EPTQLinear
+    from eptq_b200.parallel import shard_layer, ROW_PARALLEL
+    from eptq_b200.quantizers import E8D4Quantizer
+    from eptq_b200.synthetic import LLAMA2_7B_LINEARS, make_layer
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    if rank == 0:
+        build_library()
+    if world > 1:
+        dist.barrier()
+    lib = _lib.load()
+    B = args.batch
+    n_layers = args.layers
+
+    table = E8D4Quantizer(radius=RADIUS).codes.to(dev)
+    layers, total_bytes = [], 0
+    for li in range(n_layers):
+        for i, (name, (out_f, in_f)) in enumerate(LLAMA2_7B_LINEARS.items()):
+            qd = make_layer(out_f, in_f, seed=li * 16 + i, device=str(dev))
+            total_bytes += algorithmic_bytes(out_f, in_f, qd.O.shape[0], B)
+            if world > 1:
+                qd = shard_layer(qd, name, rank, world)
+            lin = EPTQLinear.from_quantized_data(qd, table, KIND)
+            lin.tp_row_parallel = world > 1 and name.split(".")[-1] in ROW_PARALLEL
+            layers.append((name, lin))
+    torch.cuda.synchronize()
+
+    # Device-resident arm: C-ABI calls captured once, replayed per step.
+    xs = {n: torch.randn(B, n, device=dev).half() for n in {l.in_features for _, l in layers}}
+    ys = {m: torch.empty(B, m, device=dev, dtype=torch.float16) for m in {l.out_features for _, l in layers}}
+    ws_bytes = max(lib.eptq_workspace_bytes(l.Q.shape[0], l.Q.shape[1], B) for _, l in layers)
+    ws = torch.zeros(ws_bytes, dtype=torch.uint8, device=dev)
+    descs = [_make_desc(l.quantizer_type, l.Q, l._codebook32, l._codebook, l.g, l.h, l.O_vals, l.O_col,
+                        l.O_row_ptr, l.bias, l.S_group, l.qb_size) for _, l in layers]
+
+    def step_abi():
+        stream = torch.cuda.current_stream().cuda_stream
+        for (name, l), d in zip(layers, descs):
+            y = ys[l.out_features]
+            st = lib.eptq_linear_forward(C.byref(d), xs[l.in_features].data_ptr(), y.data_ptr(), B,
+                                         ws.data_ptr(), ws.numel(), stream)
+            if st != 0:
+                raise RuntimeError(lib.eptq_strerror(st).decode())
+            if l.tp_row_parallel:
+                dist.all_reduce(y)
+
+    side = torch.cuda.Stream(device=dev)
+    with torch.cuda.stream(side):
+        step_abi()
+        torch.cuda.synchronize()
+        before = _lib.launch_count()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            step_abi()
+        launches_per_step = _lib.launch_count() - before
+    torch.cuda.synchronize()
+
+    def timed(run, steps, warmup):
+        for _ in range(warmup):
+            run()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(local) as cs:
+            e0.record()
+            for _ in range(steps):
+                run()
+            e1.record()
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+                torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, cs.summary()
+
+    ms_dev, clocks = timed(graph.replay, args.steps, args.warmup)
+
+    # End-to-end arm: public module API, activations start and results end in pinned host memory.
+    x_host = {n: torch.randn(B, n).half().pin_memory() for n in xs}
+    y_host = torch.empty(B, layers[-1][1].out_features, dtype=torch.float16).pin_memory()
+    x_dev = {n: torch.empty_like(v, device=dev) for n, v in x_host.items()}
+
+    def step_module():
+        for n in x_dev:
+            x_dev[n].copy_(x_host[n], non_blocking=True)
+        y = None
+        for name, l in layers:
+            y = l(x_dev[l.in_features])
+            if l.tp_row_parallel:
+                dist.all_reduce(y)
+        y_host.copy_(y, non_blocking=True)
+
+    with torch.cuda.stream(side):
+        step_module()
+        torch.cuda.synchronize()
+        graph2 = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph2, stream=side):
+            step_module()
+    torch.cuda.synchronize()
+
+    def e2e_step():
+        graph2.replay()
+        torch.cuda.current_stream().synchronize()     # the host reads the result of every step
+
+    ms_e2e, _ = timed(e2e_step, args.steps, args.warmup)
+    h2d = sum(v.numel() * 2 for v in x_host.values())
+    d2h = y_host.numel() * 2
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    step_ms = ms_dev / args.steps
+    value = total_bytes / (step_ms * 1e-3) / 1e9
+    e2e_value = total_bytes / (ms_e2e / args.steps * 1e-3) / 1e9
+    peak, peak_kind = measured_peaks()
+    n_calls = len(layers)
+    per_launch_bytes = total_bytes / world / n_calls
+    per_launch_us = step_ms * 1e3 / n_calls
+    achieved = per_launch_bytes / (per_launch_us * 1e-6) / 1e9
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": step_ms, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "llama2-7b decode layer set, E8-D4 r=1.75, 0.2% critical blocks",
+                   "batch": B, "layers": n_layers, "linears_per_step": n_calls,
+                   "l2_policy": "inputs larger than L2 (1.66 GB of indices per step)" if n_layers >= 8 else "reduced layer count: may be L2-resident",
+                   "parallelism": f"tp{world}" if world > 1 else "single"},
+        "decode_tokens_per_s_linears_only": 1e3 / step_ms * B,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_kind": f"{peak_kind} copy bandwidth",
+                     "per_launch_bytes": per_launch_bytes, "per_launch_us": per_launch_us},
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": ms_e2e / args.steps},
+        "gpu_launches": int(launches_per_step * args.steps),
+        "clocks": clocks,
+    }
+    if not args.no_cpu_baseline and world == 1:
+        res = cpu_reference_path(B, 10)
+        line["cpu_baseline"] = {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--layers", type=int, default=N_LAYERS)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -77,7 +77,7 @@ size_t eptq_workspace_bytes(int M, int N, int B) {
     if (M <= 0 || N <= 0 || B <= 0) return 0;
     int cols = 0;
     const int splits = simt_plan_splits(M, N, B, &cols);
-    size_t bytes = counter_bytes(M, B);
+    size_t bytes = kCounterBytes;
     bytes += static_cast<size_t>(splits > 1 ? splits : 1) * B * 8u * M * sizeof(float);
     return (bytes + 255) & ~static_cast<size_t>(255);
 }

@@ -23,16 +23,13 @@ extern std::atomic<uint64_t> g_launches;    // kernels launched by this library
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-// Scratch layout shared by every GEMV variant:
-//   [0, counter_bytes)              unsigned arrival counters, zero between calls
-//   [counter_bytes, ...)            float partial sums [split][batch][8*M]
-inline size_t counter_bytes(int M, int B) {
-    size_t n = (static_cast<size_t>(M) / kRowsPerCta + 2) * static_cast<size_t>(B > 0 ? B : 1);
-    return (n * sizeof(unsigned) + 255) & ~static_cast<size_t>(255);
-}
-inline size_t partial_bytes(int M, int B) {
-    return static_cast<size_t>(kMaxSplits) * static_cast<size_t>(B) * 8u * static_cast<size_t>(M) * sizeof(float);
-}
+// Scratch layout shared by every GEMV variant.  The counter region has a fixed
+// size so that its position does not depend on the layer: the same scratch is
+// reused by layers of different shapes, and only this region must stay zero.
+//   [0, kCounterBytes)              unsigned arrival counters, zero between calls
+//   [kCounterBytes, ...)            float partial sums [split][batch][8*M]
+constexpr size_t kCounterBytes = 4096;
+constexpr int kMaxCounters = static_cast<int>(kCounterBytes / sizeof(unsigned));
 
 __device__ __forceinline__ uint4 ldg128(const void* p) {
     return __ldg(reinterpret_cast<const uint4*>(p));

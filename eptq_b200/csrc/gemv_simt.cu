@@ -255,7 +255,7 @@ int simt_plan_splits(int M, int N, int B, int* cols_per_split) {
     const int max_by_cols = (N + 511) / 512;
     if (splits > max_by_cols) splits = max_by_cols;
     if (splits > kMaxSplits) splits = kMaxSplits;
-    if (splits < 1) splits = 1;
+    if (splits < 1 || denom > kMaxCounters) splits = 1;
     int cols = (N + splits - 1) / splits;
     cols = (cols + 7) & ~7;
     splits = (N + cols - 1) / cols;
@@ -291,10 +291,10 @@ int launch_gemv_simt(const EptqLayer& L, const uint16_t* x, uint16_t* y, int B,
     a.partial = nullptr;
     a.counters = nullptr;
     if (splits > 1) {
-        const size_t need = counter_bytes(L.M, B) + static_cast<size_t>(splits) * B * 8u * L.M * sizeof(float);
+        const size_t need = kCounterBytes + static_cast<size_t>(splits) * B * 8u * L.M * sizeof(float);
         if (workspace == nullptr || workspace_bytes < need) return EPTQ_ERR_WORKSPACE;
         a.counters = reinterpret_cast<unsigned*>(workspace);
-        a.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + counter_bytes(L.M, B));
+        a.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + kCounterBytes);
     }
     dim3 grid(row_blocks, splits, batch_blocks);
     if (L.quantizer == EPTQ_E8) return launch_simt_kind<EPTQ_E8>(a, bt, grid, stream);

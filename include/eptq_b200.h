@@ -92,8 +92,10 @@ uint64_t eptq_launch_count(void);
  * Bytes of device scratch eptq_linear_forward / eptq_e8_forward /
  * eptq_e8d4_forward may need for a layer of this shape at batch B.  The caller
  * allocates it once (256-byte aligned), zero-fills it once, and may reuse it
- * for every call that is ordered on one stream; the kernels return it zeroed
- * where it must be.  Calls that may overlap on the GPU need separate scratch.
+ * for every call that is ordered on one stream, for layers of any shape (take
+ * the maximum of the sizes): the first 4096 bytes hold counters that every
+ * kernel returns to zero, the rest is overwritten before it is read.  Calls
+ * that may overlap on the GPU need separate scratch.
  */
 size_t eptq_workspace_bytes(int M, int N, int B);
 
