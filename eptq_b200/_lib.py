@@ -21,6 +21,7 @@ EXPORTS = {
     "eptq_strerror": (C.c_char_p, [_i]),
     "eptq_launch_count": (C.c_uint64, []),
     "eptq_workspace_bytes": (_sz, [_i, _i, _i]),
+    "eptq_prepare_d4_table8": (_i, [_vp, _vp, _vp]),
     "eptq_e8_forward": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _sz, _vp]),
     "eptq_e8d4_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _sz, _vp]),
     "eptq_linear_forward": (_i, [_vp, _vp, _vp, _i, _vp, _sz, _vp]),
@@ -35,6 +36,7 @@ class EptqLayer(C.Structure):
         ("n_masked", C.c_int32), ("qb_size", C.c_int32), ("table_rows", C.c_int32),
         ("Q", _vp), ("table32", _vp), ("table16", _vp), ("g", _vp), ("h", _vp),
         ("O_vals", _vp), ("O_col", _vp), ("O_row_ptr", _vp), ("bias", _vp), ("S_group", _vp),
+        ("table8", _vp), ("table8_scale", C.c_float),
     ]
 
 

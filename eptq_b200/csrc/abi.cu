@@ -2,6 +2,8 @@
 // codes.  The functions here stand where the reference has `_run_forward`
 // (csrc/eptq_kernels.cu:466-558) and the pybind module (csrc/binding.cpp:4-16).
 
+#include <cmath>
+
 #include "common.cuh"
 
 namespace eptq {
@@ -12,6 +14,10 @@ int launch_dequant(const EptqLayer& L, uint16_t* W, cudaStream_t stream);
 int launch_gemv_simt(const EptqLayer& L, const uint16_t* x, uint16_t* y, int B,
                      void* workspace, size_t workspace_bytes, cudaStream_t stream);
 int simt_plan_splits(int M, int N, int B, int* cols_per_split);
+bool mma_gemv_supported(const EptqLayer& L, int B);
+size_t mma_workspace_bytes(int M, int N);
+int launch_gemv_mma(const EptqLayer& L, const uint16_t* x, uint16_t* y,
+                    void* workspace, size_t workspace_bytes, cudaStream_t stream);
 
 namespace {
 
@@ -44,7 +50,30 @@ int forward_checked(const EptqLayer& L, const uint16_t* x, uint16_t* y, int B,
     if (!aligned16(L.table16)) return EPTQ_ERR_ALIGN;
     if ((L.N % 8) == 0 && !aligned16(x)) return EPTQ_ERR_ALIGN;
     if (workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return EPTQ_ERR_ALIGN;
+    if (mma_gemv_supported(L, B) && aligned16(L.g) && (L.bias == nullptr || aligned16(L.bias)) && aligned16(y))
+        return launch_gemv_mma(L, x, y, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
     return launch_gemv_simt(L, x, y, B, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+// Round-to-nearest-even float -> FP8 E4M3 (1-4-3, bias 7, max 448), host side.
+uint8_t host_e4m3(float v) {
+    const uint8_t sign = v < 0.f ? 0x80 : 0x00;
+    float a = v < 0.f ? -v : v;
+    if (!(a == a)) return 0x7f;
+    if (a > 448.f) a = 448.f;
+    if (a < 0.0009765625f) return sign;                       // below half the smallest subnormal
+    int e = 0;
+    float m = std::frexp(a, &e);                              // a = m * 2^e, m in [0.5, 1)
+    int exp = e - 1;                                          // a = (2m) * 2^exp, 2m in [1, 2)
+    if (exp < -6) {                                           // subnormal: multiples of 2^-9
+        const int q = static_cast<int>(std::nearbyint(a * 512.f));
+        return sign | static_cast<uint8_t>(q);                // q == 8 is the smallest normal
+    }
+    int mant = static_cast<int>(std::nearbyint((2.f * m - 1.f) * 8.f));
+    if (mant == 8) { mant = 0; ++exp; }
+    if (exp > 8) { exp = 8; mant = 6; }
+    if (exp == 8 && mant > 6) mant = 6;
+    return sign | static_cast<uint8_t>(((exp + 7) << 3) | mant);
 }
 
 }  // namespace
@@ -79,7 +108,39 @@ size_t eptq_workspace_bytes(int M, int N, int B) {
     const int splits = simt_plan_splits(M, N, B, &cols);
     size_t bytes = kCounterBytes;
     bytes += static_cast<size_t>(splits > 1 ? splits : 1) * B * 8u * M * sizeof(float);
+    if (B == 1) {
+        const size_t mma = mma_workspace_bytes(M, N);
+        if (mma > bytes) bytes = mma;
+    }
     return (bytes + 255) & ~static_cast<size_t>(255);
+}
+
+int eptq_prepare_d4_table8(const float* table, uint8_t* out, float* scale) {
+    if (table == nullptr || out == nullptr || scale == nullptr) return EPTQ_ERR_NULL;
+    // Smallest non-zero magnitude is a coordinate 0.5 of the lattice.
+    double amin = 0.0;
+    for (int i = 0; i < 2048; ++i) {
+        const double a = std::fabs(static_cast<double>(table[i]));
+        if (a > 0.0 && (amin == 0.0 || a < amin)) amin = a;
+    }
+    if (amin == 0.0) return EPTQ_ERR_UNSUPPORTED;
+    // Least-squares scale against the rounded half-integers.
+    double num = 0.0, den = 0.0;
+    for (int i = 0; i < 2048; ++i) {
+        const double r = std::nearbyint(table[i] / amin) * 0.5;     // amin is the coordinate 0.5
+        num += r * table[i];
+        den += r * r;
+    }
+    if (den == 0.0) return EPTQ_ERR_UNSUPPORTED;
+    const double sc = num / den;
+    for (int i = 0; i < 2048; ++i) {
+        const double r2 = table[i] / sc * 2.0;
+        const double r = std::nearbyint(r2);
+        if (std::fabs(r2 - r) > 2e-3 || std::fabs(r) > 15.0) return EPTQ_ERR_UNSUPPORTED;
+        out[i] = host_e4m3(static_cast<float>(r * 0.5));
+    }
+    *scale = static_cast<float>(sc);
+    return EPTQ_OK;
 }
 
 int eptq_e8_forward(const int16_t* Q, const uint16_t* codebook, int table_rows,

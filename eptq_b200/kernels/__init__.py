@@ -87,9 +87,10 @@ def _forward_impl(kind: str, Q, table, g, h, x, O_vals, O_col, O_row_ptr, bias) 
         else:
             if table.numel() != 2048:
                 raise RuntimeError("E8-D4 codes must hold 512 x 4 values")
-            st = lib.eptq_e8d4_forward(Q.data_ptr(), table.data_ptr(), g.data_ptr(), h.data_ptr(),
-                                       x.data_ptr(), _ptr(O_vals), _ptr(O_col), O_row_ptr.data_ptr(), _ptr(bias),
-                                       y.data_ptr(), M, N, B, ws.data_ptr(), ws.numel(), _stream(x.device))
+            desc = _make_desc("e8_d4", Q, None, table, g, h, O_vals, O_col, O_row_ptr,
+                              None if bias is None or bias.numel() == 0 else bias, None, 0)
+            st = lib.eptq_linear_forward(C.byref(desc), x.data_ptr(), y.data_ptr(), B,
+                                         ws.data_ptr(), ws.numel(), _stream(x.device))
     _lib.check(st, f"eptq {kind} forward")
     return y
 
@@ -123,6 +124,31 @@ def _(Q, codes, g, h, x, O_vals, O_col, O_row_ptr, bias):
     return x.new_empty(x.shape[0], Q.shape[0] * 8, dtype=torch.float16)
 
 
+_table8_cache: Dict[tuple, Optional[Tuple[torch.Tensor, float]]] = {}
+
+
+def d4_table8(table: torch.Tensor) -> Optional[Tuple[torch.Tensor, float]]:
+    """(device uint8 (2048,) tensor, scale) with the E8-D4 table expressed as
+    scale * half-integer lattice coordinates in FP8 E4M3, or None if the table is
+    not such a multiple.  Prepared on the host once per table tensor."""
+    key = (table.data_ptr(), table.device, table.dtype, table._version)
+    if key in _table8_cache:
+        return _table8_cache[key]
+    import numpy as np
+    host = np.ascontiguousarray(table.detach().float().cpu().numpy().reshape(-1))
+    res = None
+    if host.size == 2048:
+        out = np.zeros(2048, dtype=np.uint8)
+        scale = C.c_float(0.0)
+        st = _lib.load().eptq_prepare_d4_table8(host.ctypes.data, out.ctypes.data, C.addressof(scale))
+        if st == 0:
+            res = (torch.from_numpy(out).to(table.device), float(scale.value))
+    if len(_table8_cache) > 64:
+        _table8_cache.clear()
+    _table8_cache[key] = res
+    return res
+
+
 def _make_desc(quantizer_type: str, Q, table32, table16, g, h, O_vals, O_col, O_row_ptr, bias, S_group,
                qb_size: int) -> _lib.EptqLayer:
     d = _lib.EptqLayer()
@@ -138,6 +164,12 @@ def _make_desc(quantizer_type: str, Q, table32, table16, g, h, O_vals, O_col, O_
     d.g, d.h = g.data_ptr(), h.data_ptr()
     d.O_vals, d.O_col, d.O_row_ptr = _ptr(O_vals), _ptr(O_col), O_row_ptr.data_ptr()
     d.bias, d.S_group = _ptr(bias), _ptr(S_group)
+    d.table8, d.table8_scale = None, 0.0
+    if quantizer_type == "e8_d4" and Q.is_cuda:
+        t8 = d4_table8(table32 if table32 is not None else table16)
+        if t8 is not None:
+            d._keep = t8[0]                      # keep the device table alive as long as the descriptor
+            d.table8, d.table8_scale = t8[0].data_ptr(), t8[1]
     return d
 
 

@@ -51,6 +51,10 @@ enum { EPTQ_E8 = 0, EPTQ_E8D4 = 1 };
  *              Needed for bit-exact reconstruction (eptq_dequantize, eptq_gemm).
  *   table16    the same table rounded to fp16 (what the reference's kernels
  *              read, kernels/linear.py:93-95).  Needed by the GEMV.
+ *   table8     E8-D4 only, optional: the raw lattice coordinates of the 512 codes
+ *              (table = raw * table8_scale) as FP8 E4M3 bytes, 4 per code, made
+ *              by eptq_prepare_d4_table8.  Enables the tensor-core GEMV; NULL
+ *              selects the general kernel.
  *   g, h       fp16 row scales (8*M) and column scales (N).
  *   O_vals     fp16 (n_masked, 8), ordered by row-major position of the markers.
  *   O_col      int32 (n_masked) column of each marker, same order.
@@ -76,6 +80,8 @@ typedef struct EptqLayer {
     const int32_t* O_row_ptr;
     const uint16_t* bias;
     const uint16_t* S_group;
+    const uint8_t* table8;
+    float table8_scale;
 } EptqLayer;
 
 /* ABI version of the loaded library (EPTQ_ABI_VERSION at build time). */
@@ -87,6 +93,16 @@ const char* eptq_strerror(int status);
 /* Number of kernels this library has launched in the calling process since it
  * was loaded (all entry points, all streams).  For launch accounting only. */
 uint64_t eptq_launch_count(void);
+
+/*
+ * Host-side, no GPU involved: express an E8-D4 table (512 x 4 fp32, already
+ * divided by the radius, as the reference builds it in quantizers/e8_d4.py:83-86)
+ * as scale * (half-integer lattice coordinates) and write the coordinates as
+ * 2048 FP8 E4M3 bytes to `out`, the scale to `*scale`.  Returns
+ * EPTQ_ERR_UNSUPPORTED when the table is not such a multiple (for example a
+ * radially warped codebook); such layers run on the general kernel.
+ */
+int eptq_prepare_d4_table8(const float* table, uint8_t* out, float* scale);
 
 /*
  * Bytes of device scratch eptq_linear_forward / eptq_e8_forward /

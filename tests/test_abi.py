@@ -46,3 +46,26 @@ def test_argument_checks_need_no_gpu(built_library):
     assert lib.eptq_dequantize(ctypes.byref(d), None, None) == 4                 # EPTQ_ERR_QUANTIZER
     d.quantizer = 0
     assert lib.eptq_dequantize(ctypes.byref(d), None, None) == 2                 # EPTQ_ERR_SHAPE
+
+
+def test_prepare_d4_table8_on_host(built_library):
+    """Host-only entry point: lattice tables convert exactly, a warped table is refused."""
+    import numpy as np
+    import oracle
+    from eptq_b200 import _lib
+    lib = _lib.load()
+    tab = np.ascontiguousarray(oracle.d4_table(1.75).reshape(-1))
+    out = np.zeros(2048, np.uint8)
+    scale = ctypes.c_float(0)
+    assert lib.eptq_prepare_d4_table8(tab.ctypes.data, out.ctypes.data, ctypes.addressof(scale)) == 0
+    assert abs(scale.value - 1 / 1.75) < 1e-6
+    # decode E4M3 on the host and compare with the raw lattice coordinates
+    def e4m3(b):
+        s = -1.0 if b & 0x80 else 1.0
+        e, m = (b >> 3) & 0xF, b & 7
+        return s * (m / 8 * 2.0 ** -6 if e == 0 else (1 + m / 8) * 2.0 ** (e - 7))
+    dec = np.array([e4m3(int(b)) for b in out], dtype=np.float32)
+    assert np.array_equal(dec, oracle.d4_raw_codes().reshape(-1))
+    warped = tab * (1 + 0.05 * np.abs(tab))
+    assert lib.eptq_prepare_d4_table8(np.ascontiguousarray(warped).ctypes.data, out.ctypes.data,
+                                      ctypes.addressof(scale)) == 7

@@ -1,0 +1,97 @@
+"""The tensor-core E8-D4 GEMV (batch 1) against the oracle and against the general kernel."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from eptq_b200.kernels.linear import EPTQLinear
+from eptq_b200.synthetic import make_activations, make_layer
+from tests import util
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def build(qd):
+    return EPTQLinear.from_quantized_data(qd, torch.from_numpy(oracle.d4_table(1.75)), "e8_d4").to(DEV)
+
+
+def reference(qd, x):
+    W16 = oracle.dequantize_layer(util.qld_arrays(qd), oracle.d4_table(1.75))
+    return oracle.linear_reference(x.cpu().numpy(), W16, None if qd.bias is None else qd.bias.numpy())
+
+
+@pytest.mark.parametrize("out_f,in_f", [
+    (8, 32), (16, 32), (40, 96), (128, 128), (136, 160), (264, 2752), (2048, 1024), (1024, 8192),
+    (11008, 4096), (4096, 11008), (4096, 4096), (14336, 4096), (1024, 4096), (768, 3072), (50 * 8, 64),
+])
+@pytest.mark.parametrize("bias", [False, True])
+def test_shapes(out_f, in_f, bias):
+    qd = make_layer(out_f, in_f, seed=out_f * 7 + in_f, outlier_frac=0.004, bias=bias)
+    x = make_activations(1, in_f, seed=11)
+    y = build(qd)(x.to(DEV)).float().cpu().numpy()
+    assert util.max_rel_err(y, reference(qd, x)) <= util.REL_TOL
+
+
+@pytest.mark.parametrize("scale", [1e-4, 1e-2, 30.0, 2000.0])
+def test_activation_magnitudes(scale):
+    """The per-block power-of-two scaling keeps precision whatever the magnitude of x."""
+    qd = make_layer(1024, 2048, seed=3)
+    x = (make_activations(1, 2048, seed=12).float() * scale).half()
+    y = build(qd)(x.to(DEV)).float().cpu().numpy()
+    assert util.max_rel_err(y, reference(qd, x)) <= util.REL_TOL
+
+
+def test_sparse_and_spiky_activations():
+    qd = make_layer(512, 4096, seed=4)
+    x = make_activations(1, 4096, seed=13)
+    x[0, ::3] = 0
+    x[0, 100] = 300.0            # one dominant channel inside a block of ordinary values
+    x[0, 3000:3200] = 0          # a column block that is entirely zero
+    y = build(qd)(x.to(DEV)).float().cpu().numpy()
+    assert util.max_rel_err(y, reference(qd, x)) <= util.REL_TOL
+    z = build(qd)(torch.zeros(1, 4096, dtype=torch.float16, device=DEV))
+    assert float(z.abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("frac", [0.0, 0.1, 1.0])
+def test_marker_density(frac):
+    qd = make_layer(256, 512, seed=5, outlier_frac=frac, bias=True)
+    x = make_activations(1, 512, seed=14)
+    y = build(qd)(x.to(DEV)).float().cpu().numpy()
+    assert util.max_rel_err(y, reference(qd, x)) <= util.REL_TOL
+
+
+def test_agrees_with_general_kernel_and_is_repeatable():
+    """Batch 2 with two identical rows runs on the general kernel; batch 1 on the tensor-core one."""
+    qd = make_layer(4096, 4096, seed=6)
+    lin = build(qd)
+    x = make_activations(1, 4096, seed=15).to(DEV)
+    y1 = lin(x)
+    y2 = lin(torch.cat([x, x]))
+    ref = y2[0].float()
+    assert float((y1[0].float() - ref).abs().max() / ref.abs().max()) <= util.REL_TOL
+    for _ in range(3):
+        assert torch.equal(lin(x), y1)
+
+
+def test_interleaved_shapes_share_scratch():
+    """Layers of different shapes called back to back on one stream reuse one scratch buffer."""
+    shapes = [(4096, 4096), (11008, 4096), (4096, 11008), (264, 2752)]
+    lins = [build(make_layer(o, i, seed=o + i)) for o, i in shapes]
+    xs = [make_activations(1, i, seed=i).to(DEV) for _, i in shapes]
+    first = [lin(x) for lin, x in zip(lins, xs)]
+    for _ in range(3):
+        for lin, x, y0 in zip(lins, xs, first):
+            assert torch.equal(lin(x), y0)
+    g = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        outs = [lin(x) for lin, x in zip(lins, xs)]
+        torch.cuda.synchronize()
+        with torch.cuda.graph(g, stream=side):
+            outs = [lin(x) for lin, x in zip(lins, xs)]
+    g.replay()
+    torch.cuda.synchronize()
+    for y, y0 in zip(outs, first):
+        assert torch.equal(y, y0)
