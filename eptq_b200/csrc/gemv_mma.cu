@@ -74,10 +74,10 @@ constexpr int kSmemBytes = kTableBytes + kPiecesBytes + kRedBytes + 64;
 __device__ __forceinline__ unsigned smem_u32(const void* p) {
     return static_cast<unsigned>(__cvta_generic_to_shared(p));
 }
-__device__ __forceinline__ unsigned lds32(unsigned addr) {
-    unsigned v;
-    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
-    return v;
+// Table read at byte offset `off` (already includes 4*lane).  Plain shared-memory
+// indexing: the compiler folds the table's base address into the load.
+__device__ __forceinline__ unsigned table_read(const unsigned char* tab, unsigned off) {
+    return *reinterpret_cast<const unsigned*>(tab + off);
 }
 __device__ __forceinline__ unsigned prmt(unsigned a, unsigned b, unsigned sel) {
     unsigned d;
@@ -119,43 +119,53 @@ __device__ __forceinline__ unsigned split_pieces(float v) {
     return out;
 }
 
-// Shared-memory addresses of the two half-codewords of the index in the low 16
-// bits of `q` (raw stored bits; the table is laid out for them, so the +32768 of
-// the format costs nothing).  `lane_base` = table base + 4*lane.
-__device__ __forceinline__ void code_addresses(unsigned q, unsigned lane_base, unsigned& ai, unsigned& aj) {
-    ai = (q & 0xFF80u) | lane_base;                                   // (class, i) * 128 B
-    aj = ((q << 7) & 0x3F80u) | ((q & 0xC000u) | lane_base);          // (class, j) * 128 B
+// Byte offsets into the table of the two half-codewords of the index in the low
+// 16 bits of `q` (raw stored bits; the table is laid out for them, so the +32768
+// of the format costs nothing).  `lane4` = 4*lane occupies bits 2..6.
+__device__ __forceinline__ void code_offsets(unsigned q, unsigned lane4, unsigned& oi, unsigned& oj) {
+    oi = (q & 0xFF80u) | lane4;                                   // (class, i) * 128 B
+    oj = ((q << 7) & 0x3F80u) | ((q & 0xC000u) | lane4);          // (class, j) * 128 B
 }
 
-// Accumulate the critical-block correction of one row tile (lanes: 2 per row).
-__device__ __forceinline__ void correction_tile(const MmaGemvArgs& p, int rt, int lane, float (&acc)[8]) {
-    const int row = rt * 16 + (lane >> 1);
-    const int sub = lane & 1;
+// Critical-block correction of 4 consecutive Q rows by one warp (8 lanes per row,
+// up to 4 entries per lane per pass).  Everything that is part of the weights
+// (row pointers, columns, O, h) is loaded before `wait_dep` is called, only x after.
+template <typename WaitFn>
+__device__ __forceinline__ void correction_rows(const MmaGemvArgs& p, int row0, int lane, float (&acc)[8],
+                                                WaitFn wait_dep) {
+    const int row = row0 + (lane >> 3);
+    const int sub = lane & 7;
 #pragma unroll
     for (int k = 0; k < 8; ++k) acc[k] = 0.f;
-    if (row >= p.M) return;
-    // Value the main loop added for a marker: table entry (3,127) in both halves.
-    const unsigned cbytes = __ldg(p.table8 + 511);
+    const unsigned cbytes = __ldg(p.table8 + 511);      // what the main loop added for a marker: entry (3,127), both halves
     float cstar[4];
 #pragma unroll
     for (int d = 0; d < 4; ++d) cstar[d] = e4m3_to_f32((cbytes >> (8 * d)) & 0xffu) * p.table_scale;
-    const int lo = __ldg(p.O_row_ptr + row), hi = __ldg(p.O_row_ptr + row + 1);
-    for (int i = lo + sub; i < hi; i += 8) {
+    int lo = 0, hi = 0;
+    if (row < p.M) {
+        lo = __ldg(p.O_row_ptr + row);
+        hi = __ldg(p.O_row_ptr + row + 1);
+    }
+    bool waited = false;
+    for (int i = lo + sub; __any_sync(0xffffffffu, i < hi) || !waited; i += 32) {
         int col[4];
-        float xv[4];
+        float hv[4], xv[4];
         uint4 ov[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) col[j] = (i + 2 * j < hi) ? __ldg(p.O_col + i + 2 * j) : -1;
+        for (int j = 0; j < 4; ++j) col[j] = (i + 8 * j < hi) ? __ldg(p.O_col + i + 8 * j) : -1;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             if (col[j] >= 0) {
-                xv[j] = __half2float(__ldg(p.x + col[j])) * __half2float(__ldg(p.h + col[j]));
-                ov[j] = ldg128(p.O_vals + static_cast<size_t>(i + 2 * j) * 8);
+                hv[j] = __half2float(__ldg(p.h + col[j]));
+                ov[j] = ldg128(p.O_vals + static_cast<size_t>(i + 8 * j) * 8);
             } else {
-                xv[j] = 0.f;
+                hv[j] = 0.f;
                 ov[j] = make_uint4(0, 0, 0, 0);
             }
         }
+        if (!waited) { wait_dep(); waited = true; }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) xv[j] = (col[j] >= 0) ? hv[j] * __half2float(__ldg(p.x + col[j])) : 0.f;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             float o8[8];
@@ -163,6 +173,12 @@ __device__ __forceinline__ void correction_tile(const MmaGemvArgs& p, int rt, in
 #pragma unroll
             for (int k = 0; k < 8; ++k) acc[k] = fmaf(o8[k] - cstar[k & 3], xv[j], acc[k]);
         }
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        acc[k] += __shfl_xor_sync(0xffffffffu, acc[k], 1);
+        acc[k] += __shfl_xor_sync(0xffffffffu, acc[k], 2);
+        acc[k] += __shfl_xor_sync(0xffffffffu, acc[k], 4);
     }
 }
 
@@ -175,7 +191,7 @@ __device__ __forceinline__ void arrive_and_finalize(const MmaGemvArgs& p, int rt
     unsigned ticket = 0;
     if (lane == 0) ticket = atomicAdd(p.counters + rt, 1u);
     ticket = __shfl_sync(0xffffffffu, ticket, 0);
-    if (ticket != static_cast<unsigned>(slots) - 1u) return;
+    if (ticket != static_cast<unsigned>(p.col_blocks) + 3u) return;     // col_blocks GEMV + 4 correction arrivals
     __threadfence();
     if (lane == 0) p.counters[rt] = 0u;
     float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -220,18 +236,20 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_d4_kernel(const MmaGemvArgs p
     const int slots = p.col_blocks + 1;
 
     if (static_cast<int>(blockIdx.y) >= p.main_groups) {
-        // ---- correction blocks: one row tile per warp, striding over all row tiles
+        // ---- correction blocks: 4 Q rows per warp, striding over all quarter tiles
         asm volatile("griddepcontrol.launch_dependents;");
-        asm volatile("griddepcontrol.wait;" ::: "memory");
         const int nwarps = (gridDim.y - p.main_groups) * gridDim.x * 8;
         const int w0 = ((blockIdx.y - p.main_groups) * gridDim.x + blockIdx.x) * 8 + warp;
-        for (int rt = w0; rt < p.row_tiles; rt += nwarps) {
+        bool waited = false;
+        for (int qt = w0; qt < p.row_tiles * 4; qt += nwarps) {
             float acc[8];
-            correction_tile(p, rt, lane, acc);
-#pragma unroll
-            for (int k = 0; k < 8; ++k) acc[k] += __shfl_xor_sync(0xffffffffu, acc[k], 1);
-            if ((lane & 1) == 0) {
-                float* dst = p.partial + (static_cast<size_t>(rt) * slots + p.col_blocks) * 128 + (lane >> 1) * 8;
+            correction_rows(p, qt * 4, lane, acc, [&]() {
+                if (!waited) { asm volatile("griddepcontrol.wait;" ::: "memory"); waited = true; }
+            });
+            const int rt = qt >> 2;
+            if ((lane & 7) == 0) {
+                float* dst = p.partial + (static_cast<size_t>(rt) * slots + p.col_blocks) * 128
+                           + ((qt & 3) * 4 + (lane >> 3)) * 8;
                 __stcg(reinterpret_cast<float4*>(dst), make_float4(acc[0], acc[1], acc[2], acc[3]));
                 __stcg(reinterpret_cast<float4*>(dst + 4), make_float4(acc[4], acc[5], acc[6], acc[7]));
             }
@@ -317,7 +335,8 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_d4_kernel(const MmaGemvArgs p
     __syncthreads();
 
     // 4. main loop
-    const unsigned lane_base = smem_u32(tab) + 4u * lane;
+    const unsigned lane4 = 4u * lane;
+    const unsigned char* tab_bytes = smem_raw;
     unsigned sel[2];
 #pragma unroll
     for (int s = 0; s < 2; ++s) {
@@ -358,14 +377,14 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_d4_kernel(const MmaGemvArgs p
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
                     unsigned ai[4], aj[4], ad0, ad1;
-                    code_addresses(qav[u], lane_base, ad0, ad1);
-                    ai[0] = lds32(ad0); aj[0] = lds32(ad1);
-                    code_addresses(qbv[u], lane_base, ad0, ad1);
-                    ai[1] = lds32(ad0); aj[1] = lds32(ad1);
-                    code_addresses(qav[u] >> 16, lane_base, ad0, ad1);
-                    ai[2] = lds32(ad0); aj[2] = lds32(ad1);
-                    code_addresses(qbv[u] >> 16, lane_base, ad0, ad1);
-                    ai[3] = lds32(ad0); aj[3] = lds32(ad1);
+                    code_offsets(qav[u], lane4, ad0, ad1);
+                    ai[0] = table_read(tab_bytes, ad0); aj[0] = table_read(tab_bytes, ad1);
+                    code_offsets(qbv[u], lane4, ad0, ad1);
+                    ai[1] = table_read(tab_bytes, ad0); aj[1] = table_read(tab_bytes, ad1);
+                    code_offsets(qav[u] >> 16, lane4, ad0, ad1);
+                    ai[2] = table_read(tab_bytes, ad0); aj[2] = table_read(tab_bytes, ad1);
+                    code_offsets(qbv[u] >> 16, lane4, ad0, ad1);
+                    ai[3] = table_read(tab_bytes, ad0); aj[3] = table_read(tab_bytes, ad1);
                     const unsigned b00 = prmt(wv[2 * u], 0u, sel[0]), b01 = prmt(wv[2 * u + 1], 0u, sel[0]);
                     const unsigned b10 = prmt(wv[2 * u], 0u, sel[1]), b11 = prmt(wv[2 * u + 1], 0u, sel[1]);
                     mma_e4m3(acc[0][0], ai, b00, b01);
@@ -461,7 +480,7 @@ int mma_plan(int M, int N, int* wc_out, int* col_blocks, int* groups, int* corr_
     int gy = 148 / cb;
     if (gy < 1) gy = 1;
     if (gy > row_blocks) gy = row_blocks;
-    int cg = (row_tiles + cb * 8 - 1) / (cb * 8);
+    int cg = (row_tiles * 4 + cb * 8 - 1) / (cb * 8);
     if (cg < 1) cg = 1;
     *wc_out = wc; *col_blocks = cb; *groups = gy; *corr_groups = cg;
     return row_tiles;
