@@ -1,26 +1,25 @@
 // E8-D4 decode GEMV on the tensor cores (batch 1), for sm_100a.
 //
 // Why tensor cores for a matrix-vector product: at HBM speed an SM has to
-// consume about 11 indices per clock.  Eight fp32 FMAs per index do not fit in
-// that budget, and neither does reading 16 B of fp16 codeword per index from
-// shared memory (128 B/clk).  So the codebook is held in shared memory as FP8
-// (E4M3) -- the D4 lattice points are half-integers of magnitude <= 2.5 and are
-// exact in E4M3; the radius is folded into one output scale -- and each 4-byte
-// half-codeword read from shared memory is used, unmodified, as one A-fragment
-// register of mma.sync.m16n8k32 (e4m3 x e4m3 -> f32):
+// consume about 11 indices per clock, and eight fp32 FMAs per index do not fit
+// in that instruction budget.  Here each 8-byte half-codeword (4 fp16) read
+// from shared memory is used, unmodified, as two A-fragment registers of
+// mma.sync.m16n8k16 (f16 x f16 -> f32):
 //
-//   A[row = Q row, K = (column slot n_l, dim d)] = code[Q[row, n_l]][d]      (16 x 32)
-//   B[K = (n_l, d), col = (piece p, dim d')]     = piece_p(h*x)[n_l] * [d == d']   (32 x 8)
+//   A[row = Q row, K = (column slot n_l, dim d)] = code[Q[row, n_l]][d]            (16 x 16)
+//   B[K = (n_l, d), col = (piece p, dim d')]     = piece_p(h*x)[n_l] * [d == d']   (16 x 8)
 //   D[row, (p, d')] += sum_{n_l} code[..][d'] * piece_p(h*x)[n_l]
 //
-// The activations keep more than fp16 precision by splitting s*h*x into four
-// E4M3 pieces (p0 + p1/16 + p2/256 + p3/4096, s a power of two per column
-// block); the pieces are separate output columns and are recombined in fp32.
-// Three quarters of each MMA multiply by the zeros of [d == d'], which is free:
-// FP8 mma.sync sustains ~0.9 instructions/clk/SM and this kernel needs ~0.36.
+// The activations keep fp32-like precision: s*h*x (s a power of two per column
+// block) is split into an fp16 high part and an fp16 remainder, which are the
+// two "pieces" p and are added again in fp32.  Three quarters of each MMA
+// multiply the zeros of [d == d']; the tensor pipe has that much to spare.
+// (FP8 mma.sync would halve the shared-memory bytes per index, but on sm_100a
+// it is expanded into conversions plus two fp16 MMAs and runs slower.)
 //
-// Shared-memory reads are bank-conflict free because the 2 KB table is stored
-// 32 times, once per lane (word address = entry*32 + lane): 64 KB per block.
+// Shared-memory reads are bank-conflict free because the 4 KB fp16 table is
+// stored 16 times, once per lane of a half-warp (byte address = entry*128 +
+// (lane%16)*8): 64 KB per block.
 //
 // Critical blocks: the marker index 65535 decodes to the ordinary table entry
 // (3,127,127), so the main loop needs no test; dedicated warps add
@@ -34,8 +33,9 @@
 // them in slot order, applies g and bias and writes fp16.
 //
 // Programmatic dependent launch: everything that does not depend on x (table
-// build, first Q loads) runs before griddepcontrol.wait, so it overlaps the
-// tail of the previous kernel in the stream when the launch allows it.
+// build, first Q loads, the static part of the corrections) runs before
+// griddepcontrol.wait, so it overlaps the tail of the previous kernel in the
+// stream when the launch allows it.
 //
 // Reference counterpart: e8d4_fused_kernel_t (csrc/eptq_kernels.cu:161-292).
 
@@ -45,8 +45,7 @@ namespace eptq {
 
 struct MmaGemvArgs {
     const int16_t* Q;
-    const uint32_t* table8;     // 512 entries, 4 E4M3 bytes each (raw lattice coordinates)
-    float table_scale;          // true codeword = raw * table_scale
+    const uint2* table16;       // 512 entries, 4 fp16 each
     const __half* g;
     const __half* h;
     const __half* x;
@@ -66,39 +65,22 @@ struct MmaGemvArgs {
 
 namespace {
 
-constexpr int kTableBytes = 512 * 32 * 4;         // lane-replicated table
+constexpr int kTableBytes = 512 * 16 * 8;         // table replicated for the 16 lanes of a half-warp
 constexpr int kPiecesBytes = 1024 * 4;            // up to 8 slices x 128 columns
 constexpr int kRedBytes = 2 * 8 * 128 * 4;        // double-buffered cross-warp reduction
 constexpr int kSmemBytes = kTableBytes + kPiecesBytes + kRedBytes + 64;
 
-__device__ __forceinline__ unsigned smem_u32(const void* p) {
-    return static_cast<unsigned>(__cvta_generic_to_shared(p));
-}
-// Table read at byte offset `off` (already includes 4*lane).  Plain shared-memory
-// indexing: the compiler folds the table's base address into the load.
-__device__ __forceinline__ unsigned table_read(const unsigned char* tab, unsigned off) {
-    return *reinterpret_cast<const unsigned*>(tab + off);
-}
 __device__ __forceinline__ unsigned prmt(unsigned a, unsigned b, unsigned sel) {
     unsigned d;
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
     return d;
 }
-__device__ __forceinline__ void mma_e4m3(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+__device__ __forceinline__ void mma_f16(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                        unsigned b0, unsigned b1) {
     asm volatile(
-        "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ unsigned f32_to_e4m3(float v) {
-    unsigned short r;
-    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(0.f), "f"(v));   // low byte = v
-    return r & 0xffu;
-}
-__device__ __forceinline__ float e4m3_to_f32(unsigned byte) {
-    unsigned h2;
-    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(static_cast<unsigned short>(byte)));
-    return __half2float(__ushort_as_half(static_cast<unsigned short>(h2 & 0xffffu)));
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 __device__ __forceinline__ uint4 ldg_stream(const void* p) {
     uint4 v;
@@ -107,24 +89,22 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
     return v;
 }
 
-// Four E4M3 pieces of v: v ~= p0 + p1/16 + p2/256 + p3/4096 (byte p of the result).
+// v as fp16 high part (low 16 bits) and fp16 remainder (high 16 bits).
 __device__ __forceinline__ unsigned split_pieces(float v) {
-    unsigned out = 0;
-#pragma unroll
-    for (int p = 0; p < 4; ++p) {
-        const unsigned e = f32_to_e4m3(v);
-        out |= e << (8 * p);
-        v = (v - e4m3_to_f32(e)) * 16.f;
-    }
-    return out;
+    const __half hi = __float2half_rn(v);
+    const __half lo = __float2half_rn(v - __half2float(hi));
+    return static_cast<unsigned>(__half_as_ushort(hi)) | (static_cast<unsigned>(__half_as_ushort(lo)) << 16);
 }
 
 // Byte offsets into the table of the two half-codewords of the index in the low
 // 16 bits of `q` (raw stored bits; the table is laid out for them, so the +32768
-// of the format costs nothing).  `lane4` = 4*lane occupies bits 2..6.
-__device__ __forceinline__ void code_offsets(unsigned q, unsigned lane4, unsigned& oi, unsigned& oj) {
-    oi = (q & 0xFF80u) | lane4;                                   // (class, i) * 128 B
-    oj = ((q << 7) & 0x3F80u) | ((q & 0xC000u) | lane4);          // (class, j) * 128 B
+// of the format costs nothing).  `lane8` = 8*(lane%16) occupies bits 3..6.
+__device__ __forceinline__ void code_offsets(unsigned q, unsigned lane8, unsigned& oi, unsigned& oj) {
+    oi = (q & 0xFF80u) | lane8;                                   // (class, i) * 128 B
+    oj = ((q << 7) & 0x3F80u) | ((q & 0xC000u) | lane8);          // (class, j) * 128 B
+}
+__device__ __forceinline__ uint2 table_read(const unsigned char* tab, unsigned off) {
+    return *reinterpret_cast<const uint2*>(tab + off);
 }
 
 // Critical-block correction of 4 consecutive Q rows by one warp (8 lanes per row,
@@ -137,10 +117,10 @@ __device__ __forceinline__ void correction_rows(const MmaGemvArgs& p, int row0, 
     const int sub = lane & 7;
 #pragma unroll
     for (int k = 0; k < 8; ++k) acc[k] = 0.f;
-    const unsigned cbytes = __ldg(p.table8 + 511);      // what the main loop added for a marker: entry (3,127), both halves
-    float cstar[4];
-#pragma unroll
-    for (int d = 0; d < 4; ++d) cstar[d] = e4m3_to_f32((cbytes >> (8 * d)) & 0xffu) * p.table_scale;
+    const uint2 craw = __ldg(p.table16 + 511);          // what the main loop added for a marker: entry (3,127), both halves
+    const float2 c01 = __half22float2(*reinterpret_cast<const __half2*>(&craw.x));
+    const float2 c23 = __half22float2(*reinterpret_cast<const __half2*>(&craw.y));
+    const float cstar[4] = {c01.x, c01.y, c23.x, c23.y};
     int lo = 0, hi = 0;
     if (row < p.M) {
         lo = __ldg(p.O_row_ptr + row);
@@ -294,8 +274,8 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_d4_kernel(const MmaGemvArgs p
 
     // 2. lane-replicated table; entry order follows the raw stored bits (true index ^ 0x100 on 9 bits)
     for (int e = threadIdx.x; e < 512; e += 256) {
-        const unsigned v = __ldg(p.table8 + (e ^ 0x100));
-        const uint4 vv = make_uint4(v, v, v, v);
+        const uint2 v = __ldg(p.table16 + (e ^ 0x100));
+        const uint4 vv = make_uint4(v.x, v.y, v.x, v.y);
         uint4* dst = reinterpret_cast<uint4*>(tab + e * 32);
 #pragma unroll
         for (int i = 0; i < 8; ++i) dst[i] = vv;
@@ -321,12 +301,12 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_d4_kernel(const MmaGemvArgs p
     __syncthreads();
 #pragma unroll
     for (int w = 0; w < 8; ++w) mx = fmaxf(mx, warpmax[w]);
-    // scale = 2^(7 - exponent(mx)): mx * scale in [128, 256), below the E4M3 maximum of 448
+    // scale = 2^(13 - exponent(mx)): mx * scale in [2^13, 2^14), well inside the fp16 range
     int ex = static_cast<int>((__float_as_uint(mx) >> 23) & 0xffu) - 127;
-    if (mx == 0.f || ex > 100) ex = 7;
+    if (mx == 0.f || ex > 100) ex = 13;
     if (ex < -100) ex = -100;
-    const float scale = __uint_as_float(static_cast<unsigned>(127 + 7 - ex) << 23);
-    const float inv_scale = __uint_as_float(static_cast<unsigned>(127 - 7 + ex) << 23);
+    const float scale = __uint_as_float(static_cast<unsigned>(127 + 13 - ex) << 23);
+    const float inv_scale = __uint_as_float(static_cast<unsigned>(127 - 13 + ex) << 23);
 #pragma unroll
     for (int i = 0; i < CPT; ++i) {
         const int c = threadIdx.x + 256 * i;
@@ -335,15 +315,21 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_d4_kernel(const MmaGemvArgs p
     __syncthreads();
 
     // 4. main loop
-    const unsigned lane4 = 4u * lane;
+    const unsigned lane8 = 8u * (lane & 15);
     const unsigned char* tab_bytes = smem_raw;
-    unsigned sel[2];
-#pragma unroll
-    for (int s = 0; s < 2; ++s) {
-        const unsigned pidx = 2u * s + (g >> 2), pos = g & 3;
-        sel[s] = 0x4444u ^ ((4u ^ pidx) << (4u * pos));      // byte `pidx` of the word -> byte `pos`, zeros elsewhere
+    // Column g of B is (piece g>>2, dim g&3).  K index of (n_l, d) is (d>>1)*8 + 2*n_l + (d&1), so this
+    // thread's b0 holds dims 0,1 and b1 dims 2,3 of column slot n_l = t: exactly one half of one of
+    // them is the piece, the rest is zero.
+    unsigned sel0, sel1;
+    {
+        const unsigned pb = 2u * (g >> 2);                      // first byte of the piece inside the word
+        const unsigned lo_half = 0x4400u | ((pb + 1) << 4) | pb;              // piece in bits 0..15
+        const unsigned hi_half = (((pb + 1) << 12) | (pb << 8)) | 0x0044u;     // piece in bits 16..31
+        const unsigned place = (g & 1) ? hi_half : lo_half;
+        sel0 = (g & 2) ? 0x4444u : place;
+        sel1 = (g & 2) ? place : 0x4444u;
     }
-    const float own_scale = ((t >> 1) == 0 ? 1.f : 0.0625f) * inv_scale * p.table_scale;
+    const float own_scale = inv_scale;
     int buf = 0;
 
     for (; rb < p.row_blocks; rb += p.main_groups) {
@@ -353,13 +339,11 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_d4_kernel(const MmaGemvArgs p
         const int16_t *na = nullptr, *nb = nullptr;
         if (has_next) row_ptrs(rb_next, na, nb);
 
-        float acc[2][2][4];
+        float acc[2][4];
 #pragma unroll
         for (int a = 0; a < 2; ++a)
 #pragma unroll
-            for (int b = 0; b < 2; ++b)
-#pragma unroll
-                for (int c = 0; c < 4; ++c) acc[a][b][c] = 0.f;
+            for (int c = 0; c < 4; ++c) acc[a][c] = 0.f;
 
 #pragma unroll
         for (int s = 0; s < 4; ++s) {
@@ -375,33 +359,28 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_d4_kernel(const MmaGemvArgs p
                 const unsigned qav[4] = {ca.x, ca.y, ca.z, ca.w};
                 const unsigned qbv[4] = {cb.x, cb.y, cb.z, cb.w};
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    unsigned ai[4], aj[4], ad0, ad1;
-                    code_offsets(qav[u], lane4, ad0, ad1);
-                    ai[0] = table_read(tab_bytes, ad0); aj[0] = table_read(tab_bytes, ad1);
-                    code_offsets(qbv[u], lane4, ad0, ad1);
-                    ai[1] = table_read(tab_bytes, ad0); aj[1] = table_read(tab_bytes, ad1);
-                    code_offsets(qav[u] >> 16, lane4, ad0, ad1);
-                    ai[2] = table_read(tab_bytes, ad0); aj[2] = table_read(tab_bytes, ad1);
-                    code_offsets(qbv[u] >> 16, lane4, ad0, ad1);
-                    ai[3] = table_read(tab_bytes, ad0); aj[3] = table_read(tab_bytes, ad1);
-                    const unsigned b00 = prmt(wv[2 * u], 0u, sel[0]), b01 = prmt(wv[2 * u + 1], 0u, sel[0]);
-                    const unsigned b10 = prmt(wv[2 * u], 0u, sel[1]), b11 = prmt(wv[2 * u + 1], 0u, sel[1]);
-                    mma_e4m3(acc[0][0], ai, b00, b01);
-                    mma_e4m3(acc[0][1], ai, b10, b11);
-                    mma_e4m3(acc[1][0], aj, b00, b01);
-                    mma_e4m3(acc[1][1], aj, b10, b11);
+                for (int e = 0; e < 8; ++e) {
+                    const unsigned qa16 = (e & 1) ? (qav[e >> 1] >> 16) : qav[e >> 1];
+                    const unsigned qb16 = (e & 1) ? (qbv[e >> 1] >> 16) : qbv[e >> 1];
+                    unsigned oi, oj;
+                    code_offsets(qa16, lane8, oi, oj);
+                    const uint2 ia = table_read(tab_bytes, oi), ja = table_read(tab_bytes, oj);
+                    code_offsets(qb16, lane8, oi, oj);
+                    const uint2 ib = table_read(tab_bytes, oi), jb = table_read(tab_bytes, oj);
+                    const unsigned b0 = prmt(wv[e], 0u, sel0), b1 = prmt(wv[e], 0u, sel1);
+                    mma_f16(acc[0], ia.x, ib.x, ia.y, ib.y, b0, b1);
+                    mma_f16(acc[1], ja.x, jb.x, ja.y, jb.y, b0, b1);
                 }
             }
         }
 
-        // 5. recombine the four pieces: this thread holds pieces (t>>1) and 2+(t>>1); partner t^2 the others
+        // 5. add the two pieces: this thread holds piece (t>>1), partner t^2 the other
         float tot[2][4];
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf)
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                const float own = fmaf(acc[hf][1][c], 1.f / 256.f, acc[hf][0][c]) * own_scale;
+                const float own = acc[hf][c] * own_scale;
                 tot[hf][c] = own + __shfl_xor_sync(0xffffffffu, own, 2);
             }
         // thread (g, t<2): rows g and g+8, dims hf*4 + 2*(t&1) + {0,1}
@@ -494,9 +473,8 @@ size_t mma_workspace_bytes(int M, int N) {
 }
 
 bool mma_gemv_supported(const EptqLayer& L, int B) {
-    return L.quantizer == EPTQ_E8D4 && L.table8 != nullptr && L.S_group == nullptr && B == 1 &&
-           (L.N % 32) == 0 && (L.M + 15) / 16 <= kMaxCounters && aligned16(L.Q) &&
-           (reinterpret_cast<uintptr_t>(L.table8) & 3u) == 0;
+    return L.quantizer == EPTQ_E8D4 && L.table16 != nullptr && L.S_group == nullptr && B == 1 &&
+           (L.N % 32) == 0 && (L.M + 15) / 16 <= kMaxCounters && aligned16(L.Q) && aligned16(L.table16);
 }
 
 int launch_gemv_mma(const EptqLayer& L, const uint16_t* x, uint16_t* y,
@@ -507,8 +485,7 @@ int launch_gemv_mma(const EptqLayer& L, const uint16_t* x, uint16_t* y,
     if (workspace == nullptr || workspace_bytes < need) return EPTQ_ERR_WORKSPACE;
     MmaGemvArgs a;
     a.Q = L.Q;
-    a.table8 = reinterpret_cast<const uint32_t*>(L.table8);
-    a.table_scale = L.table8_scale;
+    a.table16 = reinterpret_cast<const uint2*>(L.table16);
     a.g = reinterpret_cast<const __half*>(L.g);
     a.h = reinterpret_cast<const __half*>(L.h);
     a.x = reinterpret_cast<const __half*>(x);
