@@ -15,8 +15,8 @@ int launch_gemv_simt(const EptqLayer& L, const uint16_t* x, uint16_t* y, int B,
                      void* workspace, size_t workspace_bytes, cudaStream_t stream);
 int simt_plan_splits(int M, int N, int B, int* cols_per_split);
 bool mma_gemv_supported(const EptqLayer& L, int B);
-size_t mma_workspace_bytes(int M, int N);
-int launch_gemv_mma(const EptqLayer& L, const uint16_t* x, uint16_t* y,
+size_t mma_workspace_bytes(int M, int N, int B);
+int launch_gemv_mma(const EptqLayer& L, const uint16_t* x, uint16_t* y, int B,
                     void* workspace, size_t workspace_bytes, cudaStream_t stream);
 
 namespace {
@@ -51,7 +51,7 @@ int forward_checked(const EptqLayer& L, const uint16_t* x, uint16_t* y, int B,
     if ((L.N % 8) == 0 && !aligned16(x)) return EPTQ_ERR_ALIGN;
     if (workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return EPTQ_ERR_ALIGN;
     if (mma_gemv_supported(L, B) && aligned16(L.g) && (L.bias == nullptr || aligned16(L.bias)) && aligned16(y))
-        return launch_gemv_mma(L, x, y, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+        return launch_gemv_mma(L, x, y, B, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
     return launch_gemv_simt(L, x, y, B, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
@@ -108,8 +108,8 @@ size_t eptq_workspace_bytes(int M, int N, int B) {
     const int splits = simt_plan_splits(M, N, B, &cols);
     size_t bytes = kCounterBytes;
     bytes += static_cast<size_t>(splits > 1 ? splits : 1) * B * 8u * M * sizeof(float);
-    if (B == 1) {
-        const size_t mma = mma_workspace_bytes(M, N);
+    if (B <= 4 && (N % 32) == 0) {
+        const size_t mma = mma_workspace_bytes(M, N, B);
         if (mma > bytes) bytes = mma;
     }
     return (bytes + 255) & ~static_cast<size_t>(255);

@@ -1,21 +1,27 @@
-// E8-D4 decode GEMV on the tensor cores (batch 1), for sm_100a.
+// E8-D4 decode GEMV on the tensor cores (batch 1..4), for sm_100a.
 //
 // Why tensor cores for a matrix-vector product: at HBM speed an SM has to
 // consume about 11 indices per clock, and eight fp32 FMAs per index do not fit
 // in that instruction budget.  Here each 8-byte half-codeword (4 fp16) read
-// from shared memory is used, unmodified, as two A-fragment registers of
-// mma.sync.m16n8k16 (f16 x f16 -> f32):
+// from shared memory is used, unmodified, as an A-fragment register pair of
+// mma.sync.m16n8k16 (f16 x f16 -> f32).  With g = lane/4, t = lane%4:
 //
-//   A[row = Q row, K = (column slot n_l, dim d)] = code[Q[row, n_l]][d]            (16 x 16)
-//   B[K = (n_l, d), col = (piece p, dim d')]     = piece_p(h*x)[n_l] * [d == d']   (16 x 8)
-//   D[row, (p, d')] += sum_{n_l} code[..][d'] * piece_p(h*x)[n_l]
+//   MMA row   (g, s)      Q row g of the tile, dims 2s,2s+1 of the half-codeword (s = 0,1 <-> rows g, g+8)
+//   MMA K     (n_l, dd)   column slot n_l = 0..7 of the strip, dim 2s+dd;  K = 2*(n_l%4) + dd + 8*(n_l/4)
+//   MMA col   (b, p, dd') batch row b = 0,1, activation piece p = 0,1, dim 2s+dd'
+//
+//   A[(g,s), (n_l,dd)] = code[Q[g, n_l]][2s+dd]          registers a0,a1 = one 8-byte table read (n_l = t),
+//                                                         a2,a3 = another (n_l = t+4)
+//   B[(n_l,dd), (b,p,dd')] = piece_p(h*x_b)[n_l] * [dd == dd']
+//   D[(g,s), (b,p,dd')] += sum_{n_l} code[..][2s+dd'] * piece_p(h*x_b)[n_l]
 //
 // The activations keep fp32-like precision: s*h*x (s a power of two per column
-// block) is split into an fp16 high part and an fp16 remainder, which are the
-// two "pieces" p and are added again in fp32.  Three quarters of each MMA
-// multiply the zeros of [d == d']; the tensor pipe has that much to spare.
-// (FP8 mma.sync would halve the shared-memory bytes per index, but on sm_100a
-// it is expanded into conversions plus two fp16 MMAs and runs slower.)
+// block and batch row) is split into an fp16 high part and an fp16 remainder,
+// the two pieces, which are added again in fp32.  Half of each MMA multiplies
+// the zeros of [dd == dd']; the tensor pipe has that much to spare, and a second
+// batch row rides along for free.  (FP8 mma.sync would halve the shared-memory
+// bytes per index, but on sm_100a it is expanded into conversions plus two fp16
+// MMAs and runs slower.)
 //
 // Shared-memory reads are bank-conflict free because the 4 KB fp16 table is
 // stored 16 times, once per lane of a half-warp (byte address = entry*128 +
@@ -54,9 +60,9 @@ struct MmaGemvArgs {
     const int* O_row_ptr;
     const __half* bias;
     __half* y;
-    float* partial;             // [row tile][col_blocks + 1][128]
+    float* partial;             // [row tile][col_blocks + 1][batch][128]
     unsigned* counters;         // [row tile]
-    int M, N;
+    int M, N, B;
     int row_tiles;              // ceil(M / 16)
     int row_blocks;             // ceil(row_tiles / WR)
     int col_blocks;             // grid.x
@@ -66,21 +72,20 @@ struct MmaGemvArgs {
 namespace {
 
 constexpr int kTableBytes = 512 * 16 * 8;         // table replicated for the 16 lanes of a half-warp
-constexpr int kPiecesBytes = 1024 * 4;            // up to 8 slices x 128 columns
-constexpr int kRedBytes = 2 * 8 * 128 * 4;        // double-buffered cross-warp reduction
-constexpr int kSmemBytes = kTableBytes + kPiecesBytes + kRedBytes + 64;
+constexpr int kMaxBatch = 4;
+constexpr int kPiecesBytes = kMaxBatch * 1024 * 4;   // [batch][up to 8 slices x 128 columns]
+constexpr int kRedBytes = 2 * 8 * 2 * 128 * 4;    // double-buffered cross-warp reduction, 2 batch rows per pass
+constexpr int kSmemBytes = kTableBytes + kPiecesBytes + kRedBytes + 256;
 
 __device__ __forceinline__ unsigned prmt(unsigned a, unsigned b, unsigned sel) {
     unsigned d;
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
     return d;
 }
-__device__ __forceinline__ void mma_f16(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
-                                        unsigned b0, unsigned b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+__device__ __forceinline__ void mma_f16(float (&c)[4], const uint2& a01, const uint2& a23, unsigned b0, unsigned b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+        : "r"(a01.x), "r"(a01.y), "r"(a23.x), "r"(a23.y), "r"(b0), "r"(b1));
 }
 __device__ __forceinline__ uint4 ldg_stream(const void* p) {
     uint4 v;
@@ -108,15 +113,18 @@ __device__ __forceinline__ uint2 table_read(const unsigned char* tab, unsigned o
 }
 
 // Critical-block correction of 4 consecutive Q rows by one warp (8 lanes per row,
-// up to 4 entries per lane per pass).  Everything that is part of the weights
-// (row pointers, columns, O, h) is loaded before `wait_dep` is called, only x after.
+// up to 4 entries per lane per pass) for batch rows [0, B).  Everything that is
+// part of the weights (row pointers, columns, O, h) is loaded before `wait_dep`
+// is called, only x after.  acc[b][k]: row (lane>>3), output dim k, valid in lanes with lane%8 == 0.
 template <typename WaitFn>
-__device__ __forceinline__ void correction_rows(const MmaGemvArgs& p, int row0, int lane, float (&acc)[8],
-                                                WaitFn wait_dep) {
+__device__ __forceinline__ void correction_rows(const MmaGemvArgs& p, int row0, int lane,
+                                                float (&acc)[kMaxBatch][8], WaitFn wait_dep) {
     const int row = row0 + (lane >> 3);
     const int sub = lane & 7;
 #pragma unroll
-    for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+    for (int b = 0; b < kMaxBatch; ++b)
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[b][k] = 0.f;
     const uint2 craw = __ldg(p.table16 + 511);          // what the main loop added for a marker: entry (3,127), both halves
     const float2 c01 = __half22float2(*reinterpret_cast<const __half2*>(&craw.x));
     const float2 c23 = __half22float2(*reinterpret_cast<const __half2*>(&craw.y));
@@ -129,7 +137,7 @@ __device__ __forceinline__ void correction_rows(const MmaGemvArgs& p, int row0, 
     bool waited = false;
     for (int i = lo + sub; __any_sync(0xffffffffu, i < hi) || !waited; i += 32) {
         int col[4];
-        float hv[4], xv[4];
+        float hv[4];
         uint4 ov[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) col[j] = (i + 8 * j < hi) ? __ldg(p.O_col + i + 8 * j) : -1;
@@ -145,25 +153,37 @@ __device__ __forceinline__ void correction_rows(const MmaGemvArgs& p, int row0, 
         }
         if (!waited) { wait_dep(); waited = true; }
 #pragma unroll
-        for (int j = 0; j < 4; ++j) xv[j] = (col[j] >= 0) ? hv[j] * __half2float(__ldg(p.x + col[j])) : 0.f;
-#pragma unroll
         for (int j = 0; j < 4; ++j) {
             float o8[8];
             unpack8(ov[j], o8);
 #pragma unroll
-            for (int k = 0; k < 8; ++k) acc[k] = fmaf(o8[k] - cstar[k & 3], xv[j], acc[k]);
+            for (int k = 0; k < 8; ++k) o8[k] -= cstar[k & 3];
+#pragma unroll
+            for (int b = 0; b < kMaxBatch; ++b) {
+                if (b < p.B) {
+                    const float xv = (col[j] >= 0) ? hv[j] * __half2float(__ldg(p.x + static_cast<size_t>(b) * p.N + col[j])) : 0.f;
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) acc[b][k] = fmaf(o8[k], xv, acc[b][k]);
+                }
+            }
         }
     }
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-        acc[k] += __shfl_xor_sync(0xffffffffu, acc[k], 1);
-        acc[k] += __shfl_xor_sync(0xffffffffu, acc[k], 2);
-        acc[k] += __shfl_xor_sync(0xffffffffu, acc[k], 4);
+    for (int b = 0; b < kMaxBatch; ++b) {
+        if (b < p.B) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                acc[b][k] += __shfl_xor_sync(0xffffffffu, acc[b][k], 1);
+                acc[b][k] += __shfl_xor_sync(0xffffffffu, acc[b][k], 2);
+                acc[b][k] += __shfl_xor_sync(0xffffffffu, acc[b][k], 4);
+            }
+        }
     }
 }
 
 // Publish one row tile's partial (already in global memory) and, if this warp is
-// the last of `expected` arrivals, reduce all slots and write y.
+// the last arrival (col_blocks GEMV partials + 4 correction quarters), reduce all
+// slots in slot order and write y.
 __device__ __forceinline__ void arrive_and_finalize(const MmaGemvArgs& p, int rt, int lane) {
     const int slots = p.col_blocks + 1;
     __threadfence();
@@ -171,45 +191,47 @@ __device__ __forceinline__ void arrive_and_finalize(const MmaGemvArgs& p, int rt
     unsigned ticket = 0;
     if (lane == 0) ticket = atomicAdd(p.counters + rt, 1u);
     ticket = __shfl_sync(0xffffffffu, ticket, 0);
-    if (ticket != static_cast<unsigned>(p.col_blocks) + 3u) return;     // col_blocks GEMV + 4 correction arrivals
+    if (ticket != static_cast<unsigned>(p.col_blocks) + 3u) return;
     __threadfence();
     if (lane == 0) p.counters[rt] = 0u;
-    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-    const float* base = p.partial + static_cast<size_t>(rt) * slots * 128 + lane * 4;
-    for (int k = 0; k < slots; ++k) {
-        const float4 v = __ldcg(reinterpret_cast<const float4*>(base + static_cast<size_t>(k) * 128));
-        s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
-    }
     const int row = rt * 16 + (lane >> 1);
-    if (row < p.M) {
-        const int o = row * 8 + (lane & 1) * 4;
-        const uint2 graw = __ldg(reinterpret_cast<const uint2*>(p.g + o));
-        const __half2* g2 = reinterpret_cast<const __half2*>(&graw);
-        float2 g01 = __half22float2(g2[0]), g23 = __half22float2(g2[1]);
-        float b0 = 0.f, b1 = 0.f, b2 = 0.f, b3 = 0.f;
-        if (p.bias != nullptr) {
-            const uint2 braw = __ldg(reinterpret_cast<const uint2*>(p.bias + o));
-            const __half2* bb = reinterpret_cast<const __half2*>(&braw);
-            float2 b01 = __half22float2(bb[0]), b23 = __half22float2(bb[1]);
-            b0 = b01.x; b1 = b01.y; b2 = b23.x; b3 = b23.y;
+    if (row >= p.M) return;
+    const int o = row * 8 + (lane & 1) * 4;
+    const uint2 graw = __ldg(reinterpret_cast<const uint2*>(p.g + o));
+    const float2 g01 = __half22float2(*reinterpret_cast<const __half2*>(&graw.x));
+    const float2 g23 = __half22float2(*reinterpret_cast<const __half2*>(&graw.y));
+    float b0 = 0.f, b1 = 0.f, b2 = 0.f, b3 = 0.f;
+    if (p.bias != nullptr) {
+        const uint2 braw = __ldg(reinterpret_cast<const uint2*>(p.bias + o));
+        const float2 b01 = __half22float2(*reinterpret_cast<const __half2*>(&braw.x));
+        const float2 b23 = __half22float2(*reinterpret_cast<const __half2*>(&braw.y));
+        b0 = b01.x; b1 = b01.y; b2 = b23.x; b3 = b23.y;
+    }
+    for (int b = 0; b < p.B; ++b) {
+        float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+        const float* base = p.partial + (static_cast<size_t>(rt) * slots * p.B + b) * 128 + lane * 4;
+        for (int k = 0; k < slots; ++k) {
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(base + static_cast<size_t>(k) * p.B * 128));
+            s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
         }
-        __half2 o01 = __floats2half2_rn(fmaf(s.x, g01.x, b0), fmaf(s.y, g01.y, b1));
-        __half2 o23 = __floats2half2_rn(fmaf(s.z, g23.x, b2), fmaf(s.w, g23.y, b3));
+        const __half2 o01 = __floats2half2_rn(fmaf(s.x, g01.x, b0), fmaf(s.y, g01.y, b1));
+        const __half2 o23 = __floats2half2_rn(fmaf(s.z, g23.x, b2), fmaf(s.w, g23.y, b3));
         uint2 outv;
-        outv.x = *reinterpret_cast<unsigned*>(&o01);
-        outv.y = *reinterpret_cast<unsigned*>(&o23);
-        *reinterpret_cast<uint2*>(p.y + o) = outv;
+        outv.x = *reinterpret_cast<const unsigned*>(&o01);
+        outv.y = *reinterpret_cast<const unsigned*>(&o23);
+        *reinterpret_cast<uint2*>(p.y + static_cast<size_t>(b) * 8 * p.M + o) = outv;
     }
 }
 
-template <int WC>
+// WC: column slices per block (WR = 8/WC row tiles).  NBP: batch-row pairs (batch <= 2*NBP).
+template <int WC, int NBP>
 __global__ void __launch_bounds__(256, 2) gemv_mma_d4_kernel(const MmaGemvArgs p) {
     constexpr int WR = 8 / WC;
+    constexpr int COLS = WC * 128;
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    unsigned* tab = reinterpret_cast<unsigned*>(smem_raw);
-    unsigned* pieces = reinterpret_cast<unsigned*>(smem_raw + kTableBytes);
-    float* red = reinterpret_cast<float*>(smem_raw + kTableBytes + kPiecesBytes);
-    float* warpmax = reinterpret_cast<float*>(smem_raw + kTableBytes + kPiecesBytes + kRedBytes);
+    unsigned* pieces = reinterpret_cast<unsigned*>(smem_raw + kTableBytes);                 // [batch][1024]
+    float* red = reinterpret_cast<float*>(smem_raw + kTableBytes + kPiecesBytes);           // [2][8 warps][2][128]
+    float* warpmax = reinterpret_cast<float*>(smem_raw + kTableBytes + kPiecesBytes + kRedBytes);   // [batch][8]
 
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
@@ -222,16 +244,21 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_d4_kernel(const MmaGemvArgs p
         const int w0 = ((blockIdx.y - p.main_groups) * gridDim.x + blockIdx.x) * 8 + warp;
         bool waited = false;
         for (int qt = w0; qt < p.row_tiles * 4; qt += nwarps) {
-            float acc[8];
+            float acc[kMaxBatch][8];
             correction_rows(p, qt * 4, lane, acc, [&]() {
                 if (!waited) { asm volatile("griddepcontrol.wait;" ::: "memory"); waited = true; }
             });
             const int rt = qt >> 2;
             if ((lane & 7) == 0) {
-                float* dst = p.partial + (static_cast<size_t>(rt) * slots + p.col_blocks) * 128
-                           + ((qt & 3) * 4 + (lane >> 3)) * 8;
-                __stcg(reinterpret_cast<float4*>(dst), make_float4(acc[0], acc[1], acc[2], acc[3]));
-                __stcg(reinterpret_cast<float4*>(dst + 4), make_float4(acc[4], acc[5], acc[6], acc[7]));
+#pragma unroll
+                for (int b = 0; b < kMaxBatch; ++b) {
+                    if (b < p.B) {
+                        float* dst = p.partial + ((static_cast<size_t>(rt) * slots + p.col_blocks) * p.B + b) * 128
+                                   + ((qt & 3) * 4 + (lane >> 3)) * 8;
+                        __stcg(reinterpret_cast<float4*>(dst), make_float4(acc[b][0], acc[b][1], acc[b][2], acc[b][3]));
+                        __stcg(reinterpret_cast<float4*>(dst + 4), make_float4(acc[b][4], acc[b][5], acc[b][6], acc[b][7]));
+                    }
+                }
             }
             arrive_and_finalize(p, rt, lane);
         }
@@ -242,12 +269,11 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_d4_kernel(const MmaGemvArgs p
     const int g = lane >> 2, t = lane & 3;
     const int wr = warp / WC, wc = warp % WC;
     const int N = p.N;
-    const int cta_col = blockIdx.x * (WC * 128);
+    const int cta_col = blockIdx.x * COLS;
     const int warp_col = cta_col + wc * 128;
     const int thread_col = warp_col + 8 * t;
 
-    // Row block list of this block: by, by + groups, ...
-    int rb = blockIdx.y;
+    int rb = blockIdx.y;                       // row blocks of this block: by, by + groups, ...
     auto row_ptrs = [&](int rblock, const int16_t*& pa, const int16_t*& pb) {
         const int rtile = rblock * WR + wr;
         const int ra = min(rtile * 16 + g, p.M - 1), rbw = min(rtile * 16 + g + 8, p.M - 1);
@@ -272,64 +298,78 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_d4_kernel(const MmaGemvArgs p
         }
     }
 
-    // 2. lane-replicated table; entry order follows the raw stored bits (true index ^ 0x100 on 9 bits)
-    for (int e = threadIdx.x; e < 512; e += 256) {
-        const uint2 v = __ldg(p.table16 + (e ^ 0x100));
-        const uint4 vv = make_uint4(v.x, v.y, v.x, v.y);
-        uint4* dst = reinterpret_cast<uint4*>(tab + e * 32);
+    // 2. replicated table; entry order follows the raw stored bits (true index ^ 0x100 on 9 bits).
+    //    Eight consecutive threads write the eight 16-byte chunks of one entry.
+    {
+        const int chunk = threadIdx.x & 7;
+        for (int e = threadIdx.x >> 3; e < 512; e += 32) {
+            const uint2 v = __ldg(p.table16 + (e ^ 0x100));
+            *reinterpret_cast<uint4*>(smem_raw + e * 128 + chunk * 16) = make_uint4(v.x, v.y, v.x, v.y);
+        }
+    }
+    // h of this column block is part of the weights as well
+    constexpr int CPT = (COLS + 255) / 256;
+    float hcol[CPT];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) dst[i] = vv;
+    for (int i = 0; i < CPT; ++i) {
+        const int c = threadIdx.x + 256 * i;
+        hcol[i] = (c < COLS && cta_col + c < N) ? __half2float(__ldg(p.h + cta_col + c)) : 0.f;
     }
 
     asm volatile("griddepcontrol.launch_dependents;");
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
-    // 3. activations of this column block: h*x, block maximum, power-of-two scale, four E4M3 pieces
-    constexpr int CPT = (WC * 128 + 255) / 256;
-    float xh[CPT];
-    float mx = 0.f;
+    // 3. activations of this column block: h*x, block maximum, power-of-two scale, fp16 hi/lo pieces
+    float inv_scale[2 * NBP];
+    {
+        float xh[2 * NBP][CPT];
+        float mx[2 * NBP];
 #pragma unroll
-    for (int i = 0; i < CPT; ++i) {
-        const int c = threadIdx.x + 256 * i;
-        const int col = cta_col + c;
-        xh[i] = (c < WC * 128 && col < N) ? __half2float(__ldg(p.x + col)) * __half2float(__ldg(p.h + col)) : 0.f;
-        mx = fmaxf(mx, fabsf(xh[i]));
+        for (int b = 0; b < 2 * NBP; ++b) {
+            mx[b] = 0.f;
+#pragma unroll
+            for (int i = 0; i < CPT; ++i) {
+                const int c = threadIdx.x + 256 * i;
+                const int col = cta_col + c;
+                xh[b][i] = (b < p.B && c < COLS && col < N)
+                               ? __half2float(__ldg(p.x + static_cast<size_t>(b) * N + col)) * hcol[i] : 0.f;
+                mx[b] = fmaxf(mx[b], fabsf(xh[b][i]));
+            }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) mx[b] = fmaxf(mx[b], __shfl_xor_sync(0xffffffffu, mx[b], off));
+            if (lane == 0) warpmax[b * 8 + warp] = mx[b];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int b = 0; b < 2 * NBP; ++b) {
+#pragma unroll
+            for (int w = 0; w < 8; ++w) mx[b] = fmaxf(mx[b], warpmax[b * 8 + w]);
+            // scale = 2^(13 - exponent(mx)): mx * scale in [2^13, 2^14), well inside the fp16 range
+            int ex = static_cast<int>((__float_as_uint(mx[b]) >> 23) & 0xffu) - 127;
+            if (mx[b] == 0.f || ex > 100) ex = 13;
+            if (ex < -100) ex = -100;
+            const float scale = __uint_as_float(static_cast<unsigned>(127 + 13 - ex) << 23);
+            inv_scale[b] = __uint_as_float(static_cast<unsigned>(127 - 13 + ex) << 23);
+#pragma unroll
+            for (int i = 0; i < CPT; ++i) {
+                const int c = threadIdx.x + 256 * i;
+                if (c < COLS) pieces[b * 1024 + c] = split_pieces(xh[b][i] * scale);
+            }
+        }
+        __syncthreads();
     }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
-    if (lane == 0) warpmax[warp] = mx;
-    __syncthreads();
-#pragma unroll
-    for (int w = 0; w < 8; ++w) mx = fmaxf(mx, warpmax[w]);
-    // scale = 2^(13 - exponent(mx)): mx * scale in [2^13, 2^14), well inside the fp16 range
-    int ex = static_cast<int>((__float_as_uint(mx) >> 23) & 0xffu) - 127;
-    if (mx == 0.f || ex > 100) ex = 13;
-    if (ex < -100) ex = -100;
-    const float scale = __uint_as_float(static_cast<unsigned>(127 + 13 - ex) << 23);
-    const float inv_scale = __uint_as_float(static_cast<unsigned>(127 - 13 + ex) << 23);
-#pragma unroll
-    for (int i = 0; i < CPT; ++i) {
-        const int c = threadIdx.x + 256 * i;
-        if (c < WC * 128) pieces[c] = split_pieces(xh[i] * scale);
-    }
-    __syncthreads();
 
     // 4. main loop
     const unsigned lane8 = 8u * (lane & 15);
     const unsigned char* tab_bytes = smem_raw;
-    // Column g of B is (piece g>>2, dim g&3).  K index of (n_l, d) is (d>>1)*8 + 2*n_l + (d&1), so this
-    // thread's b0 holds dims 0,1 and b1 dims 2,3 of column slot n_l = t: exactly one half of one of
-    // them is the piece, the rest is zero.
-    unsigned sel0, sel1;
-    {
-        const unsigned pb = 2u * (g >> 2);                      // first byte of the piece inside the word
-        const unsigned lo_half = 0x4400u | ((pb + 1) << 4) | pb;              // piece in bits 0..15
-        const unsigned hi_half = (((pb + 1) << 12) | (pb << 8)) | 0x0044u;     // piece in bits 16..31
-        const unsigned place = (g & 1) ? hi_half : lo_half;
-        sel0 = (g & 2) ? 0x4444u : place;
-        sel1 = (g & 2) ? place : 0x4444u;
-    }
-    const float own_scale = inv_scale;
+    // B column g = (batch g>>2, piece (g>>1)&1, dd' = g&1): the piece goes to the low or high half
+    // of the B register, the other half stays zero.
+    const unsigned pb = 2u * ((g >> 1) & 1);
+    const unsigned sel = (g & 1) ? ((((pb + 1) << 12) | (pb << 8)) | 0x0044u) : (0x4400u | ((pb + 1) << 4) | pb);
+    const unsigned* my_pieces = pieces + (g >> 2) * 1024 + wc * 128 + 8 * t;     // + bp*2048 for the next batch pair
+    float own_scale[NBP];
+#pragma unroll
+    for (int bp = 0; bp < NBP; ++bp) own_scale[bp] = (t >> 1) ? inv_scale[2 * bp + 1] : inv_scale[2 * bp];
     int buf = 0;
 
     for (; rb < p.row_blocks; rb += p.main_groups) {
@@ -339,11 +379,15 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_d4_kernel(const MmaGemvArgs p
         const int16_t *na = nullptr, *nb = nullptr;
         if (has_next) row_ptrs(rb_next, na, nb);
 
-        float acc[2][4];
+        float acc[NBP][2][2][4];              // [batch pair][row group g / g+8][half i / j][dims]
 #pragma unroll
-        for (int a = 0; a < 2; ++a)
+        for (int a = 0; a < NBP; ++a)
 #pragma unroll
-            for (int c = 0; c < 4; ++c) acc[a][c] = 0.f;
+            for (int b = 0; b < 2; ++b)
+#pragma unroll
+                for (int c = 0; c < 2; ++c)
+#pragma unroll
+                    for (int d = 0; d < 4; ++d) acc[a][b][c][d] = 0.f;
 
 #pragma unroll
         for (int s = 0; s < 4; ++s) {
@@ -353,80 +397,108 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_d4_kernel(const MmaGemvArgs p
                     qa[s] = ldg_stream(na + 32 * s);
                     qb[s] = ldg_stream(nb + 32 * s);
                 }
-                const uint4 w0 = *reinterpret_cast<const uint4*>(pieces + wc * 128 + 32 * s + 8 * t);
-                const uint4 w1 = *reinterpret_cast<const uint4*>(pieces + wc * 128 + 32 * s + 8 * t + 4);
-                const unsigned wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+                unsigned wv[NBP][8];
+#pragma unroll
+                for (int bp = 0; bp < NBP; ++bp) {
+                    const uint4 w0 = *reinterpret_cast<const uint4*>(my_pieces + bp * 2048 + 32 * s);
+                    const uint4 w1 = *reinterpret_cast<const uint4*>(my_pieces + bp * 2048 + 32 * s + 4);
+                    wv[bp][0] = w0.x; wv[bp][1] = w0.y; wv[bp][2] = w0.z; wv[bp][3] = w0.w;
+                    wv[bp][4] = w1.x; wv[bp][5] = w1.y; wv[bp][6] = w1.z; wv[bp][7] = w1.w;
+                }
                 const unsigned qav[4] = {ca.x, ca.y, ca.z, ca.w};
                 const unsigned qbv[4] = {cb.x, cb.y, cb.z, cb.w};
 #pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    const unsigned qa16 = (e & 1) ? (qav[e >> 1] >> 16) : qav[e >> 1];
-                    const unsigned qb16 = (e & 1) ? (qbv[e >> 1] >> 16) : qbv[e >> 1];
-                    unsigned oi, oj;
-                    code_offsets(qa16, lane8, oi, oj);
-                    const uint2 ia = table_read(tab_bytes, oi), ja = table_read(tab_bytes, oj);
-                    code_offsets(qb16, lane8, oi, oj);
-                    const uint2 ib = table_read(tab_bytes, oi), jb = table_read(tab_bytes, oj);
-                    const unsigned b0 = prmt(wv[e], 0u, sel0), b1 = prmt(wv[e], 0u, sel1);
-                    mma_f16(acc[0], ia.x, ib.x, ia.y, ib.y, b0, b1);
-                    mma_f16(acc[1], ja.x, jb.x, ja.y, jb.y, b0, b1);
+                for (int m = 0; m < 4; ++m) {
+                    // this thread's columns 8t+2m (slot n_l = t) and 8t+2m+1 (slot n_l = t+4)
+                    unsigned oi0, oj0, oi1, oj1;
+                    code_offsets(qav[m], lane8, oi0, oj0);
+                    code_offsets(qav[m] >> 16, lane8, oi1, oj1);
+                    const uint2 ai0 = table_read(tab_bytes, oi0), aj0 = table_read(tab_bytes, oj0);
+                    const uint2 ai1 = table_read(tab_bytes, oi1), aj1 = table_read(tab_bytes, oj1);
+                    code_offsets(qbv[m], lane8, oi0, oj0);
+                    code_offsets(qbv[m] >> 16, lane8, oi1, oj1);
+                    const uint2 bi0 = table_read(tab_bytes, oi0), bj0 = table_read(tab_bytes, oj0);
+                    const uint2 bi1 = table_read(tab_bytes, oi1), bj1 = table_read(tab_bytes, oj1);
+#pragma unroll
+                    for (int bp = 0; bp < NBP; ++bp) {
+                        const unsigned b0 = prmt(wv[bp][2 * m], 0u, sel), b1 = prmt(wv[bp][2 * m + 1], 0u, sel);
+                        mma_f16(acc[bp][0][0], ai0, ai1, b0, b1);
+                        mma_f16(acc[bp][0][1], aj0, aj1, b0, b1);
+                        mma_f16(acc[bp][1][0], bi0, bi1, b0, b1);
+                        mma_f16(acc[bp][1][1], bj0, bj1, b0, b1);
+                    }
                 }
             }
         }
 
-        // 5. add the two pieces: this thread holds piece (t>>1), partner t^2 the other
-        float tot[2][4];
+        // 5. add the two pieces (partner lane t^1) and hand the row tile's sums over.
+        //    After the shuffle lanes with even t hold, for batch row (t>>1) of each pair and rows g, g+8,
+        //    the 8 output dims: acc[..][rg][0][0..3] = dims 0..3, acc[..][rg][1][0..3] = dims 4..7.
 #pragma unroll
-        for (int hf = 0; hf < 2; ++hf)
+        for (int bp = 0; bp < NBP; ++bp) {
+            float tot[2][2][4];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const float own = acc[hf][c] * own_scale;
-                tot[hf][c] = own + __shfl_xor_sync(0xffffffffu, own, 2);
-            }
-        // thread (g, t<2): rows g and g+8, dims hf*4 + 2*(t&1) + {0,1}
-        if (WC == 1) {
-            if (t < 2 && rt < p.row_tiles) {
-                float* dst = p.partial + (static_cast<size_t>(rt) * slots + blockIdx.x) * 128;
+            for (int rg = 0; rg < 2; ++rg)
 #pragma unroll
-                for (int hf = 0; hf < 2; ++hf) {
-                    __stcg(reinterpret_cast<float2*>(dst + g * 8 + hf * 4 + 2 * t), make_float2(tot[hf][0], tot[hf][1]));
-                    __stcg(reinterpret_cast<float2*>(dst + (g + 8) * 8 + hf * 4 + 2 * t), make_float2(tot[hf][2], tot[hf][3]));
+                for (int hf = 0; hf < 2; ++hf)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const float own = acc[bp][rg][hf][c] * own_scale[bp];
+                        tot[rg][hf][c] = own + __shfl_xor_sync(0xffffffffu, own, 1);
+                    }
+            const int b = 2 * bp + (t >> 1);
+            if (WC == 1) {
+                if ((t & 1) == 0 && rt < p.row_tiles && b < p.B) {
+                    float* dst = p.partial + ((static_cast<size_t>(rt) * slots + blockIdx.x) * p.B + b) * 128;
+#pragma unroll
+                    for (int rg = 0; rg < 2; ++rg)
+#pragma unroll
+                        for (int hf = 0; hf < 2; ++hf)
+                            __stcg(reinterpret_cast<float4*>(dst + (g + 8 * rg) * 8 + hf * 4),
+                                   make_float4(tot[rg][hf][0], tot[rg][hf][1], tot[rg][hf][2], tot[rg][hf][3]));
                 }
-            }
-            if (rt < p.row_tiles) arrive_and_finalize(p, rt, lane);
-        } else {
-            float* rbuf = red + buf * (8 * 128) + warp * 128;
-            if (t < 2) {
+            } else {
+                float* rbuf = red + ((buf * 8 + warp) * 2 + (t >> 1)) * 128;
+                if ((t & 1) == 0) {
 #pragma unroll
-                for (int hf = 0; hf < 2; ++hf) {
-                    *reinterpret_cast<float2*>(rbuf + g * 8 + hf * 4 + 2 * t) = make_float2(tot[hf][0], tot[hf][1]);
-                    *reinterpret_cast<float2*>(rbuf + (g + 8) * 8 + hf * 4 + 2 * t) = make_float2(tot[hf][2], tot[hf][3]);
-                }
-            }
-            __syncthreads();
-            if (wc == 0 && rt < p.row_tiles) {
-                float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int rg = 0; rg < 2; ++rg)
 #pragma unroll
-                for (int k = 0; k < WC; ++k) {
-                    const float4 v = *reinterpret_cast<const float4*>(red + buf * (8 * 128) + (wr * WC + k) * 128 + lane * 4);
-                    s4.x += v.x; s4.y += v.y; s4.z += v.z; s4.w += v.w;
+                        for (int hf = 0; hf < 2; ++hf)
+                            *reinterpret_cast<float4*>(rbuf + (g + 8 * rg) * 8 + hf * 4) =
+                                make_float4(tot[rg][hf][0], tot[rg][hf][1], tot[rg][hf][2], tot[rg][hf][3]);
                 }
-                float* dst = p.partial + (static_cast<size_t>(rt) * slots + blockIdx.x) * 128 + lane * 4;
-                __stcg(reinterpret_cast<float4*>(dst), s4);
-                arrive_and_finalize(p, rt, lane);
+                __syncthreads();
+                if (wc == 0 && rt < p.row_tiles) {
+#pragma unroll
+                    for (int bb = 0; bb < 2; ++bb) {
+                        if (2 * bp + bb < p.B) {
+                            float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                            for (int k = 0; k < WC; ++k) {
+                                const float4 v = *reinterpret_cast<const float4*>(
+                                    red + ((buf * 8 + wr * WC + k) * 2 + bb) * 128 + lane * 4);
+                                s4.x += v.x; s4.y += v.y; s4.z += v.z; s4.w += v.w;
+                            }
+                            float* dst = p.partial + ((static_cast<size_t>(rt) * slots + blockIdx.x) * p.B + 2 * bp + bb) * 128 + lane * 4;
+                            __stcg(reinterpret_cast<float4*>(dst), s4);
+                        }
+                    }
+                }
+                buf ^= 1;
             }
-            buf ^= 1;
         }
+        if ((WC == 1 || wc == 0) && rt < p.row_tiles) arrive_and_finalize(p, rt, lane);
     }
 }
 
-template <int WC>
-int launch_wc(const MmaGemvArgs& a, dim3 grid, cudaStream_t stream) {
+template <int WC, int NBP>
+int launch_variant(const MmaGemvArgs& a, dim3 grid, cudaStream_t stream) {
     static bool attr_done[16] = {};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return EPTQ_ERR_LAUNCH;
-    if (dev < 16 && !attr_done[dev]) {
-        if (cudaFuncSetAttribute(gemv_mma_d4_kernel<WC>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+    if (dev < 0 || dev >= 16) return EPTQ_ERR_UNSUPPORTED;
+    if (!attr_done[dev]) {
+        if (cudaFuncSetAttribute(gemv_mma_d4_kernel<WC, NBP>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
             return EPTQ_ERR_LAUNCH;
         attr_done[dev] = true;
     }
@@ -440,15 +512,25 @@ int launch_wc(const MmaGemvArgs& a, dim3 grid, cudaStream_t stream) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    const cudaError_t err = cudaLaunchKernelEx(&cfg, gemv_mma_d4_kernel<WC>, a);
+    const cudaError_t err = cudaLaunchKernelEx(&cfg, gemv_mma_d4_kernel<WC, NBP>, a);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return err == cudaSuccess ? EPTQ_OK : EPTQ_ERR_LAUNCH;
+}
+
+template <int NBP>
+int launch_wc(int wc, const MmaGemvArgs& a, dim3 grid, cudaStream_t stream) {
+    switch (wc) {
+        case 1: return launch_variant<1, NBP>(a, grid, stream);
+        case 2: return launch_variant<2, NBP>(a, grid, stream);
+        case 4: return launch_variant<4, NBP>(a, grid, stream);
+        default: return launch_variant<8, NBP>(a, grid, stream);
+    }
 }
 
 }  // namespace
 
 // Column slices per block: aim at no more than ~16 column blocks (partials to add
-// at the end) while keeping at least one block per SM.
+// at the end) while keeping about one block per SM.
 int mma_plan(int M, int N, int* wc_out, int* col_blocks, int* groups, int* corr_groups) {
     const int row_tiles = (M + 15) / 16;
     int wc = 1;
@@ -465,23 +547,23 @@ int mma_plan(int M, int N, int* wc_out, int* col_blocks, int* groups, int* corr_
     return row_tiles;
 }
 
-size_t mma_workspace_bytes(int M, int N) {
+size_t mma_workspace_bytes(int M, int N, int B) {
     int wc, cb, gy, cg;
     const int row_tiles = mma_plan(M, N, &wc, &cb, &gy, &cg);
     if (row_tiles > kMaxCounters) return 0;
-    return kCounterBytes + static_cast<size_t>(row_tiles) * (cb + 1) * 128 * sizeof(float);
+    return kCounterBytes + static_cast<size_t>(row_tiles) * (cb + 1) * B * 128 * sizeof(float);
 }
 
 bool mma_gemv_supported(const EptqLayer& L, int B) {
-    return L.quantizer == EPTQ_E8D4 && L.table16 != nullptr && L.S_group == nullptr && B == 1 &&
+    return L.quantizer == EPTQ_E8D4 && L.table16 != nullptr && L.S_group == nullptr && B >= 1 && B <= kMaxBatch &&
            (L.N % 32) == 0 && (L.M + 15) / 16 <= kMaxCounters && aligned16(L.Q) && aligned16(L.table16);
 }
 
-int launch_gemv_mma(const EptqLayer& L, const uint16_t* x, uint16_t* y,
+int launch_gemv_mma(const EptqLayer& L, const uint16_t* x, uint16_t* y, int B,
                     void* workspace, size_t workspace_bytes, cudaStream_t stream) {
     int wc, cb, gy, cg;
     const int row_tiles = mma_plan(L.M, L.N, &wc, &cb, &gy, &cg);
-    const size_t need = mma_workspace_bytes(L.M, L.N);
+    const size_t need = mma_workspace_bytes(L.M, L.N, B);
     if (workspace == nullptr || workspace_bytes < need) return EPTQ_ERR_WORKSPACE;
     MmaGemvArgs a;
     a.Q = L.Q;
@@ -496,18 +578,13 @@ int launch_gemv_mma(const EptqLayer& L, const uint16_t* x, uint16_t* y,
     a.y = reinterpret_cast<__half*>(y);
     a.counters = reinterpret_cast<unsigned*>(workspace);
     a.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + kCounterBytes);
-    a.M = L.M; a.N = L.N;
+    a.M = L.M; a.N = L.N; a.B = B;
     a.row_tiles = row_tiles;
     a.row_blocks = (row_tiles + (8 / wc) - 1) / (8 / wc);
     a.col_blocks = cb;
     a.main_groups = gy;
     const dim3 grid(cb, gy + cg);
-    switch (wc) {
-        case 1: return launch_wc<1>(a, grid, stream);
-        case 2: return launch_wc<2>(a, grid, stream);
-        case 4: return launch_wc<4>(a, grid, stream);
-        default: return launch_wc<8>(a, grid, stream);
-    }
+    return (B <= 2) ? launch_wc<1>(wc, a, grid, stream) : launch_wc<2>(wc, a, grid, stream);
 }
 
 }  // namespace eptq

@@ -62,13 +62,26 @@ def test_marker_density(frac):
     assert util.max_rel_err(y, reference(qd, x)) <= util.REL_TOL
 
 
+@pytest.mark.parametrize("batch", [2, 3, 4])
+@pytest.mark.parametrize("out_f,in_f", [(4096, 4096), (264, 2752), (11008, 4096), (4096, 11008), (40, 96)])
+def test_small_batches(batch, out_f, in_f):
+    """Batches up to 4 ride on the same tensor-core kernel (two batch rows per MMA column set)."""
+    qd = make_layer(out_f, in_f, seed=out_f + in_f + batch, outlier_frac=0.004, bias=True)
+    x = make_activations(batch, in_f, seed=21)
+    x[batch - 1] *= 37.0                      # rows with very different magnitudes get their own scale
+    y = build(qd)(x.to(DEV)).float().cpu().numpy()
+    ref = reference(qd, x)
+    for b in range(batch):
+        assert util.max_rel_err(y[b], ref[b]) <= util.REL_TOL
+
+
 def test_agrees_with_general_kernel_and_is_repeatable():
-    """Batch 2 with two identical rows runs on the general kernel; batch 1 on the tensor-core one."""
+    """Batch 5 (five identical rows) runs on the general kernel; batch 1 on the tensor-core one."""
     qd = make_layer(4096, 4096, seed=6)
     lin = build(qd)
     x = make_activations(1, 4096, seed=15).to(DEV)
     y1 = lin(x)
-    y2 = lin(torch.cat([x, x]))
+    y2 = lin(torch.cat([x, x, x, x, x]))
     ref = y2[0].float()
     assert float((y1[0].float() - ref).abs().max() / ref.abs().max()) <= util.REL_TOL
     for _ in range(3):
