@@ -32,9 +32,11 @@
 // sum (O[i] - code[65535]) * h*x over the CSR of each row as one more partial.
 //
 // Work split: grid = (column blocks, row groups [+ correction blocks]).  A block
-// of 8 warps = WR row tiles (16 Q rows each) x WC column slices (128 columns
+// of 16 warps = WR row tiles (16 Q rows each) x WC column slices (64 columns
 // each); it builds table and activation pieces once and walks down its row
-// blocks with a rolling 4-strip register prefetch of Q.  Partial sums of the
+// blocks with a rolling 2-strip register prefetch of Q.  The kernel is bound by
+// instruction latency, not by any pipe, so it is built for occupancy: 64
+// registers per thread, two blocks (32 warps) per SM.  Partial sums of the
 // column blocks meet in the caller's scratch; the last arrival per row tile adds
 // them in slot order, applies g and bias and writes fp16.
 //
@@ -73,9 +75,12 @@ namespace {
 
 constexpr int kTableBytes = 512 * 16 * 8;         // table replicated for the 16 lanes of a half-warp
 constexpr int kMaxBatch = 4;
-constexpr int kPiecesBytes = kMaxBatch * 1024 * 4;   // [batch][up to 8 slices x 128 columns]
-constexpr int kRedBytes = 2 * 8 * 2 * 128 * 4;    // double-buffered cross-warp reduction, 2 batch rows per pass
-constexpr int kSmemBytes = kTableBytes + kPiecesBytes + kRedBytes + 256;
+constexpr int kWarps = 16;                        // warps per block
+constexpr int kThreads = kWarps * 32;
+constexpr int kSliceCols = 64;                    // columns per warp slice (2 strips of 32)
+constexpr int kRedBytes = 2 * kWarps * 2 * 128 * 4;   // double-buffered cross-warp reduction, 2 batch rows per pass
+__host__ __device__ constexpr int pieces_bytes(int nbp) { return 2 * nbp * 1024 * 4; }       // [batch][up to 16 slices x 64 columns]
+__host__ __device__ constexpr int smem_bytes(int nbp) { return kTableBytes + pieces_bytes(nbp) + kRedBytes + 256; }
 
 __device__ __forceinline__ unsigned prmt(unsigned a, unsigned b, unsigned sel) {
     unsigned d;
@@ -223,15 +228,16 @@ __device__ __forceinline__ void arrive_and_finalize(const MmaGemvArgs& p, int rt
     }
 }
 
-// WC: column slices per block (WR = 8/WC row tiles).  NBP: batch-row pairs (batch <= 2*NBP).
+// WC: column slices per block (WR = 16/WC row tiles).  NBP: batch-row pairs (batch <= 2*NBP).
 template <int WC, int NBP>
-__global__ void __launch_bounds__(256, 2) gemv_mma_d4_kernel(const MmaGemvArgs p) {
-    constexpr int WR = 8 / WC;
-    constexpr int COLS = WC * 128;
+__global__ void __launch_bounds__(kThreads, NBP == 1 ? 2 : 1) gemv_mma_d4_kernel(const MmaGemvArgs p) {
+    constexpr int WR = kWarps / WC;
+    constexpr int COLS = WC * kSliceCols;
+    constexpr int kPiecesBytes = pieces_bytes(NBP);
     extern __shared__ __align__(128) unsigned char smem_raw[];
     unsigned* pieces = reinterpret_cast<unsigned*>(smem_raw + kTableBytes);                 // [batch][1024]
-    float* red = reinterpret_cast<float*>(smem_raw + kTableBytes + kPiecesBytes);           // [2][8 warps][2][128]
-    float* warpmax = reinterpret_cast<float*>(smem_raw + kTableBytes + kPiecesBytes + kRedBytes);   // [batch][8]
+    float* red = reinterpret_cast<float*>(smem_raw + kTableBytes + kPiecesBytes);           // [2][warps][2][128]
+    float* warpmax = reinterpret_cast<float*>(smem_raw + kTableBytes + kPiecesBytes + kRedBytes);   // [batch][warps]
 
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
@@ -240,8 +246,8 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_d4_kernel(const MmaGemvArgs p
     if (static_cast<int>(blockIdx.y) >= p.main_groups) {
         // ---- correction blocks: 4 Q rows per warp, striding over all quarter tiles
         asm volatile("griddepcontrol.launch_dependents;");
-        const int nwarps = (gridDim.y - p.main_groups) * gridDim.x * 8;
-        const int w0 = ((blockIdx.y - p.main_groups) * gridDim.x + blockIdx.x) * 8 + warp;
+        const int nwarps = (gridDim.y - p.main_groups) * gridDim.x * kWarps;
+        const int w0 = ((blockIdx.y - p.main_groups) * gridDim.x + blockIdx.x) * kWarps + warp;
         bool waited = false;
         for (int qt = w0; qt < p.row_tiles * 4; qt += nwarps) {
             float acc[kMaxBatch][8];
@@ -270,7 +276,7 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_d4_kernel(const MmaGemvArgs p
     const int wr = warp / WC, wc = warp % WC;
     const int N = p.N;
     const int cta_col = blockIdx.x * COLS;
-    const int warp_col = cta_col + wc * 128;
+    const int warp_col = cta_col + wc * kSliceCols;
     const int thread_col = warp_col + 8 * t;
 
     int rb = blockIdx.y;                       // row blocks of this block: by, by + groups, ...
@@ -282,12 +288,12 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_d4_kernel(const MmaGemvArgs p
     };
 
     // 1. first Q strips (do not depend on the previous kernel)
-    uint4 qa[4], qb[4];
+    uint4 qa[2], qb[2];
     {
         const int16_t *pa, *pb;
         row_ptrs(rb, pa, pb);
 #pragma unroll
-        for (int s = 0; s < 4; ++s) {
+        for (int s = 0; s < 2; ++s) {
             if (warp_col + 32 * s < N) {
                 qa[s] = ldg_stream(pa + 32 * s);
                 qb[s] = ldg_stream(pb + 32 * s);
@@ -302,17 +308,17 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_d4_kernel(const MmaGemvArgs p
     //    Eight consecutive threads write the eight 16-byte chunks of one entry.
     {
         const int chunk = threadIdx.x & 7;
-        for (int e = threadIdx.x >> 3; e < 512; e += 32) {
+        for (int e = threadIdx.x >> 3; e < 512; e += kThreads / 8) {
             const uint2 v = __ldg(p.table16 + (e ^ 0x100));
             *reinterpret_cast<uint4*>(smem_raw + e * 128 + chunk * 16) = make_uint4(v.x, v.y, v.x, v.y);
         }
     }
     // h of this column block is part of the weights as well
-    constexpr int CPT = (COLS + 255) / 256;
+    constexpr int CPT = (COLS + kThreads - 1) / kThreads;
     float hcol[CPT];
 #pragma unroll
     for (int i = 0; i < CPT; ++i) {
-        const int c = threadIdx.x + 256 * i;
+        const int c = threadIdx.x + kThreads * i;
         hcol[i] = (c < COLS && cta_col + c < N) ? __half2float(__ldg(p.h + cta_col + c)) : 0.f;
     }
 
@@ -329,7 +335,7 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_d4_kernel(const MmaGemvArgs p
             mx[b] = 0.f;
 #pragma unroll
             for (int i = 0; i < CPT; ++i) {
-                const int c = threadIdx.x + 256 * i;
+                const int c = threadIdx.x + kThreads * i;
                 const int col = cta_col + c;
                 xh[b][i] = (b < p.B && c < COLS && col < N)
                                ? __half2float(__ldg(p.x + static_cast<size_t>(b) * N + col)) * hcol[i] : 0.f;
@@ -337,13 +343,13 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_d4_kernel(const MmaGemvArgs p
             }
 #pragma unroll
             for (int off = 16; off > 0; off >>= 1) mx[b] = fmaxf(mx[b], __shfl_xor_sync(0xffffffffu, mx[b], off));
-            if (lane == 0) warpmax[b * 8 + warp] = mx[b];
+            if (lane == 0) warpmax[b * kWarps + warp] = mx[b];
         }
         __syncthreads();
 #pragma unroll
         for (int b = 0; b < 2 * NBP; ++b) {
 #pragma unroll
-            for (int w = 0; w < 8; ++w) mx[b] = fmaxf(mx[b], warpmax[b * 8 + w]);
+            for (int w = 0; w < kWarps; ++w) mx[b] = fmaxf(mx[b], warpmax[b * kWarps + w]);
             // scale = 2^(13 - exponent(mx)): mx * scale in [2^13, 2^14), well inside the fp16 range
             int ex = static_cast<int>((__float_as_uint(mx[b]) >> 23) & 0xffu) - 127;
             if (mx[b] == 0.f || ex > 100) ex = 13;
@@ -352,7 +358,7 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_d4_kernel(const MmaGemvArgs p
             inv_scale[b] = __uint_as_float(static_cast<unsigned>(127 - 13 + ex) << 23);
 #pragma unroll
             for (int i = 0; i < CPT; ++i) {
-                const int c = threadIdx.x + 256 * i;
+                const int c = threadIdx.x + kThreads * i;
                 if (c < COLS) pieces[b * 1024 + c] = split_pieces(xh[b][i] * scale);
             }
         }
@@ -366,7 +372,7 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_d4_kernel(const MmaGemvArgs p
     // of the B register, the other half stays zero.
     const unsigned pb = 2u * ((g >> 1) & 1);
     const unsigned sel = (g & 1) ? ((((pb + 1) << 12) | (pb << 8)) | 0x0044u) : (0x4400u | ((pb + 1) << 4) | pb);
-    const unsigned* my_pieces = pieces + (g >> 2) * 1024 + wc * 128 + 8 * t;     // + bp*2048 for the next batch pair
+    const unsigned* my_pieces = pieces + (g >> 2) * 1024 + wc * kSliceCols + 8 * t;     // + bp*2048 for the next batch pair
     float own_scale[NBP];
 #pragma unroll
     for (int bp = 0; bp < NBP; ++bp) own_scale[bp] = (t >> 1) ? inv_scale[2 * bp + 1] : inv_scale[2 * bp];
@@ -390,7 +396,7 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_d4_kernel(const MmaGemvArgs p
                     for (int d = 0; d < 4; ++d) acc[a][b][c][d] = 0.f;
 
 #pragma unroll
-        for (int s = 0; s < 4; ++s) {
+        for (int s = 0; s < 2; ++s) {
             if (warp_col + 32 * s < N) {                      // warp-uniform
                 const uint4 ca = qa[s], cb = qb[s];
                 if (has_next) {                               // rolling prefetch: refill the slot just consumed
@@ -458,7 +464,7 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_d4_kernel(const MmaGemvArgs p
                                    make_float4(tot[rg][hf][0], tot[rg][hf][1], tot[rg][hf][2], tot[rg][hf][3]));
                 }
             } else {
-                float* rbuf = red + ((buf * 8 + warp) * 2 + (t >> 1)) * 128;
+                float* rbuf = red + ((buf * kWarps + warp) * 2 + (t >> 1)) * 128;
                 if ((t & 1) == 0) {
 #pragma unroll
                     for (int rg = 0; rg < 2; ++rg)
@@ -476,7 +482,7 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_d4_kernel(const MmaGemvArgs p
 #pragma unroll
                             for (int k = 0; k < WC; ++k) {
                                 const float4 v = *reinterpret_cast<const float4*>(
-                                    red + ((buf * 8 + wr * WC + k) * 2 + bb) * 128 + lane * 4);
+                                    red + ((buf * kWarps + wr * WC + k) * 2 + bb) * 128 + lane * 4);
                                 s4.x += v.x; s4.y += v.y; s4.z += v.z; s4.w += v.w;
                             }
                             float* dst = p.partial + ((static_cast<size_t>(rt) * slots + blockIdx.x) * p.B + 2 * bp + bb) * 128 + lane * 4;
@@ -498,14 +504,15 @@ int launch_variant(const MmaGemvArgs& a, dim3 grid, cudaStream_t stream) {
     if (cudaGetDevice(&dev) != cudaSuccess) return EPTQ_ERR_LAUNCH;
     if (dev < 0 || dev >= 16) return EPTQ_ERR_UNSUPPORTED;
     if (!attr_done[dev]) {
-        if (cudaFuncSetAttribute(gemv_mma_d4_kernel<WC, NBP>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+        if (cudaFuncSetAttribute(gemv_mma_d4_kernel<WC, NBP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 smem_bytes(NBP)) != cudaSuccess)
             return EPTQ_ERR_LAUNCH;
         attr_done[dev] = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
-    cfg.blockDim = dim3(256);
-    cfg.dynamicSmemBytes = kSmemBytes;
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem_bytes(NBP);
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -523,25 +530,26 @@ int launch_wc(int wc, const MmaGemvArgs& a, dim3 grid, cudaStream_t stream) {
         case 1: return launch_variant<1, NBP>(a, grid, stream);
         case 2: return launch_variant<2, NBP>(a, grid, stream);
         case 4: return launch_variant<4, NBP>(a, grid, stream);
-        default: return launch_variant<8, NBP>(a, grid, stream);
+        case 8: return launch_variant<8, NBP>(a, grid, stream);
+        default: return launch_variant<16, NBP>(a, grid, stream);
     }
 }
 
 }  // namespace
 
 // Column slices per block: aim at no more than ~16 column blocks (partials to add
-// at the end) while keeping about one block per SM.
+// at the end) and about two blocks per SM.
 int mma_plan(int M, int N, int* wc_out, int* col_blocks, int* groups, int* corr_groups) {
     const int row_tiles = (M + 15) / 16;
     int wc = 1;
-    while (wc < 8 && (N + wc * 128 - 1) / (wc * 128) > 16) wc *= 2;
-    const int cb = (N + wc * 128 - 1) / (wc * 128);
-    const int wr = 8 / wc;
+    while (wc < kWarps && (N + wc * kSliceCols - 1) / (wc * kSliceCols) > 16) wc *= 2;
+    const int cb = (N + wc * kSliceCols - 1) / (wc * kSliceCols);
+    const int wr = kWarps / wc;
     const int row_blocks = (row_tiles + wr - 1) / wr;
-    int gy = 148 / cb;
+    int gy = (2 * 148) / cb;
     if (gy < 1) gy = 1;
     if (gy > row_blocks) gy = row_blocks;
-    int cg = (row_tiles * 4 + cb * 8 - 1) / (cb * 8);
+    int cg = (row_tiles * 4 + cb * kWarps - 1) / (cb * kWarps);
     if (cg < 1) cg = 1;
     *wc_out = wc; *col_blocks = cb; *groups = gy; *corr_groups = cg;
     return row_tiles;
@@ -580,7 +588,7 @@ int launch_gemv_mma(const EptqLayer& L, const uint16_t* x, uint16_t* y, int B,
     a.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + kCounterBytes);
     a.M = L.M; a.N = L.N; a.B = B;
     a.row_tiles = row_tiles;
-    a.row_blocks = (row_tiles + (8 / wc) - 1) / (8 / wc);
+    a.row_blocks = (row_tiles + (kWarps / wc) - 1) / (kWarps / wc);
     a.col_blocks = cb;
     a.main_groups = gy;
     const dim3 grid(cb, gy + cg);
