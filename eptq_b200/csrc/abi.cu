@@ -24,9 +24,9 @@ namespace {
 int check_layer_common(const EptqLayer* L) {
     if (L == nullptr) return EPTQ_ERR_NULL;
     if (L->quantizer != EPTQ_E8 && L->quantizer != EPTQ_E8D4) return EPTQ_ERR_QUANTIZER;
-    if (L->M <= 0 || L->N <= 0 || L->n_masked < 0) return EPTQ_ERR_SHAPE;
+    if (L->M <= 0 || L->N <= 0 || L->n_masked < -1) return EPTQ_ERR_SHAPE;
     if (L->Q == nullptr || L->g == nullptr || L->h == nullptr || L->O_row_ptr == nullptr) return EPTQ_ERR_NULL;
-    if (L->n_masked > 0 && (L->O_vals == nullptr || L->O_col == nullptr)) return EPTQ_ERR_NULL;
+    if (L->n_masked != 0 && (L->O_vals == nullptr || L->O_col == nullptr)) return EPTQ_ERR_NULL;
     if (L->quantizer == EPTQ_E8D4 && L->table_rows != 512) return EPTQ_ERR_SHAPE;
     if (L->quantizer == EPTQ_E8 && (L->table_rows <= 0 || L->table_rows > 65535)) return EPTQ_ERR_SHAPE;
     if (L->S_group != nullptr) {
@@ -37,7 +37,7 @@ int check_layer_common(const EptqLayer* L) {
         if (!aligned16(L->Q) || !aligned16(L->h)) return EPTQ_ERR_ALIGN;
         if (L->S_group != nullptr && !aligned16(L->S_group)) return EPTQ_ERR_ALIGN;
     }
-    if (L->n_masked > 0 && !aligned16(L->O_vals)) return EPTQ_ERR_ALIGN;
+    if (L->n_masked != 0 && !aligned16(L->O_vals)) return EPTQ_ERR_ALIGN;
     return EPTQ_OK;
 }
 
@@ -151,7 +151,7 @@ int eptq_e8_forward(const int16_t* Q, const uint16_t* codebook, int table_rows,
                     void* workspace, size_t workspace_bytes, void* stream) {
     EptqLayer L = {};
     L.quantizer = EPTQ_E8; L.M = M; L.N = N; L.table_rows = table_rows;
-    L.n_masked = (O_vals != nullptr && O_col != nullptr) ? 1 : 0;   // only "present or not" matters here
+    L.n_masked = (O_vals != nullptr && O_col != nullptr) ? -1 : 0;   // count unknown: the CSR row pointers carry it
     L.Q = Q; L.table16 = codebook; L.g = g; L.h = h;
     L.O_vals = O_vals; L.O_col = O_col; L.O_row_ptr = O_row_ptr; L.bias = bias;
     return forward_checked(L, x, y, B, workspace, workspace_bytes, stream);
@@ -165,7 +165,7 @@ int eptq_e8d4_forward(const int16_t* Q, const uint16_t* codes,
                       void* workspace, size_t workspace_bytes, void* stream) {
     EptqLayer L = {};
     L.quantizer = EPTQ_E8D4; L.M = M; L.N = N; L.table_rows = 512;
-    L.n_masked = (O_vals != nullptr && O_col != nullptr) ? 1 : 0;
+    L.n_masked = (O_vals != nullptr && O_col != nullptr) ? -1 : 0;
     L.Q = Q; L.table16 = codes; L.g = g; L.h = h;
     L.O_vals = O_vals; L.O_col = O_col; L.O_row_ptr = O_row_ptr; L.bias = bias;
     return forward_checked(L, x, y, B, workspace, workspace_bytes, stream);

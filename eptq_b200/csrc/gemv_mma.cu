@@ -69,6 +69,7 @@ struct MmaGemvArgs {
     int row_blocks;             // ceil(row_tiles / WR)
     int col_blocks;             // grid.x
     int main_groups;            // blockIdx.y < main_groups: GEMV blocks, else correction blocks
+    int n_marked;               // number of critical blocks, -1 if the caller did not say
 };
 
 namespace {
@@ -186,32 +187,50 @@ __device__ __forceinline__ void correction_rows(const MmaGemvArgs& p, int row0, 
     }
 }
 
-// Publish one row tile's partial (already in global memory) and, if this warp is
-// the last arrival (col_blocks GEMV partials + 4 correction quarters), reduce all
-// slots in slot order and write y.
-__device__ __forceinline__ void arrive_and_finalize(const MmaGemvArgs& p, int rt, int lane) {
+// Scale and bias of the 4 outputs this lane writes if its warp turns out to be the
+// finaliser of row tile `rt` (row rt*16 + lane/2, dims 4*(lane&1)..+3).  Loaded
+// early so that the final step does not wait on DRAM.
+struct OutputAffine {
+    float g[4];
+    float b[4];
+};
+__device__ __forceinline__ OutputAffine load_affine(const MmaGemvArgs& p, int rt, int lane) {
+    OutputAffine a;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { a.g[i] = 0.f; a.b[i] = 0.f; }
+    const int row = rt * 16 + (lane >> 1);
+    if (row < p.M) {
+        const int o = row * 8 + (lane & 1) * 4;
+        const uint2 graw = __ldg(reinterpret_cast<const uint2*>(p.g + o));
+        const float2 g01 = __half22float2(*reinterpret_cast<const __half2*>(&graw.x));
+        const float2 g23 = __half22float2(*reinterpret_cast<const __half2*>(&graw.y));
+        a.g[0] = g01.x; a.g[1] = g01.y; a.g[2] = g23.x; a.g[3] = g23.y;
+        if (p.bias != nullptr) {
+            const uint2 braw = __ldg(reinterpret_cast<const uint2*>(p.bias + o));
+            const float2 b01 = __half22float2(*reinterpret_cast<const __half2*>(&braw.x));
+            const float2 b23 = __half22float2(*reinterpret_cast<const __half2*>(&braw.y));
+            a.b[0] = b01.x; a.b[1] = b01.y; a.b[2] = b23.x; a.b[3] = b23.y;
+        }
+    }
+    return a;
+}
+
+// Publish one row tile's partial (already written to global memory by this warp)
+// and, if this warp is the last arrival (col_blocks GEMV partials + 4 correction
+// quarters), add all slots in slot order and write y.  One acquire-release
+// atomic at GPU scope orders the partial stores before it and the reads after it.
+__device__ __forceinline__ void arrive_and_finalize(const MmaGemvArgs& p, int rt, int lane, const OutputAffine& aff) {
     const int slots = p.col_blocks + 1;
-    __threadfence();
     __syncwarp();
     unsigned ticket = 0;
-    if (lane == 0) ticket = atomicAdd(p.counters + rt, 1u);
+    if (lane == 0)
+        asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(ticket) : "l"(p.counters + rt) : "memory");
     ticket = __shfl_sync(0xffffffffu, ticket, 0);
     if (ticket != static_cast<unsigned>(p.col_blocks) + 3u) return;
-    __threadfence();
     if (lane == 0) p.counters[rt] = 0u;
     const int row = rt * 16 + (lane >> 1);
     if (row >= p.M) return;
     const int o = row * 8 + (lane & 1) * 4;
-    const uint2 graw = __ldg(reinterpret_cast<const uint2*>(p.g + o));
-    const float2 g01 = __half22float2(*reinterpret_cast<const __half2*>(&graw.x));
-    const float2 g23 = __half22float2(*reinterpret_cast<const __half2*>(&graw.y));
-    float b0 = 0.f, b1 = 0.f, b2 = 0.f, b3 = 0.f;
-    if (p.bias != nullptr) {
-        const uint2 braw = __ldg(reinterpret_cast<const uint2*>(p.bias + o));
-        const float2 b01 = __half22float2(*reinterpret_cast<const __half2*>(&braw.x));
-        const float2 b23 = __half22float2(*reinterpret_cast<const __half2*>(&braw.y));
-        b0 = b01.x; b1 = b01.y; b2 = b23.x; b3 = b23.y;
-    }
     for (int b = 0; b < p.B; ++b) {
         float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
         const float* base = p.partial + (static_cast<size_t>(rt) * slots * p.B + b) * 128 + lane * 4;
@@ -219,13 +238,26 @@ __device__ __forceinline__ void arrive_and_finalize(const MmaGemvArgs& p, int rt
             const float4 v = __ldcg(reinterpret_cast<const float4*>(base + static_cast<size_t>(k) * p.B * 128));
             s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
         }
-        const __half2 o01 = __floats2half2_rn(fmaf(s.x, g01.x, b0), fmaf(s.y, g01.y, b1));
-        const __half2 o23 = __floats2half2_rn(fmaf(s.z, g23.x, b2), fmaf(s.w, g23.y, b3));
+        const __half2 o01 = __floats2half2_rn(fmaf(s.x, aff.g[0], aff.b[0]), fmaf(s.y, aff.g[1], aff.b[1]));
+        const __half2 o23 = __floats2half2_rn(fmaf(s.z, aff.g[2], aff.b[2]), fmaf(s.w, aff.g[3], aff.b[3]));
         uint2 outv;
         outv.x = *reinterpret_cast<const unsigned*>(&o01);
         outv.y = *reinterpret_cast<const unsigned*>(&o23);
         *reinterpret_cast<uint2*>(p.y + static_cast<size_t>(b) * 8 * p.M + o) = outv;
     }
+}
+
+// Ask the L2 to fetch this block's share of a small array that later loads depend on.
+__device__ __forceinline__ void prefetch_share(const void* base, size_t bytes, int part, int parts) {
+    if (base == nullptr || bytes == 0) return;
+    size_t chunk = ((bytes + parts - 1) / parts + 15) & ~static_cast<size_t>(15);
+    const size_t off = chunk * part;
+    if (off >= bytes) return;
+    if (off + chunk > bytes) chunk = (bytes - off) & ~static_cast<size_t>(15);
+    if (chunk == 0) return;
+    const char* addr = reinterpret_cast<const char*>(base) + off;
+    if ((reinterpret_cast<uintptr_t>(addr) & 15u) != 0) return;
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" :: "l"(addr), "r"(static_cast<unsigned>(chunk)) : "memory");
 }
 
 // WC: column slices per block (WR = 16/WC row tiles).  NBP: batch-row pairs (batch <= 2*NBP).
@@ -243,6 +275,15 @@ __global__ void __launch_bounds__(kThreads, NBP == 1 ? 2 : 1) gemv_mma_d4_kernel
     const int warp = threadIdx.x >> 5;
     const int slots = p.col_blocks + 1;
 
+    // Small arrays that dependent loads will walk (CSR of the critical blocks): pull them into L2 now.
+    if (threadIdx.x < 3) {
+        const int part = blockIdx.y * gridDim.x + blockIdx.x, parts = gridDim.x * gridDim.y;
+        const int n_marked = p.n_marked > 0 ? p.n_marked : 0;
+        if (threadIdx.x == 0) prefetch_share(p.O_row_ptr, static_cast<size_t>(p.M + 1) * 4, part, parts);
+        if (threadIdx.x == 1) prefetch_share(p.O_col, static_cast<size_t>(n_marked) * 4, part, parts);
+        if (threadIdx.x == 2) prefetch_share(p.O_vals, static_cast<size_t>(n_marked) * 16, part, parts);
+    }
+
     if (static_cast<int>(blockIdx.y) >= p.main_groups) {
         // ---- correction blocks: 4 Q rows per warp, striding over all quarter tiles
         asm volatile("griddepcontrol.launch_dependents;");
@@ -250,6 +291,7 @@ __global__ void __launch_bounds__(kThreads, NBP == 1 ? 2 : 1) gemv_mma_d4_kernel
         const int w0 = ((blockIdx.y - p.main_groups) * gridDim.x + blockIdx.x) * kWarps + warp;
         bool waited = false;
         for (int qt = w0; qt < p.row_tiles * 4; qt += nwarps) {
+            const OutputAffine aff = load_affine(p, qt >> 2, lane);
             float acc[kMaxBatch][8];
             correction_rows(p, qt * 4, lane, acc, [&]() {
                 if (!waited) { asm volatile("griddepcontrol.wait;" ::: "memory"); waited = true; }
@@ -266,7 +308,7 @@ __global__ void __launch_bounds__(kThreads, NBP == 1 ? 2 : 1) gemv_mma_d4_kernel
                     }
                 }
             }
-            arrive_and_finalize(p, rt, lane);
+            arrive_and_finalize(p, rt, lane, aff);
         }
         return;
     }
@@ -380,6 +422,7 @@ __global__ void __launch_bounds__(kThreads, NBP == 1 ? 2 : 1) gemv_mma_d4_kernel
 
     for (; rb < p.row_blocks; rb += p.main_groups) {
         const int rt = rb * WR + wr;
+        const OutputAffine aff = load_affine(p, rt, lane);
         const int rb_next = rb + p.main_groups;
         const bool has_next = rb_next < p.row_blocks;
         const int16_t *na = nullptr, *nb = nullptr;
@@ -493,7 +536,7 @@ __global__ void __launch_bounds__(kThreads, NBP == 1 ? 2 : 1) gemv_mma_d4_kernel
                 buf ^= 1;
             }
         }
-        if ((WC == 1 || wc == 0) && rt < p.row_tiles) arrive_and_finalize(p, rt, lane);
+        if ((WC == 1 || wc == 0) && rt < p.row_tiles) arrive_and_finalize(p, rt, lane, aff);
     }
 }
 
@@ -591,6 +634,7 @@ int launch_gemv_mma(const EptqLayer& L, const uint16_t* x, uint16_t* y, int B,
     a.row_blocks = (row_tiles + (kWarps / wc) - 1) / (kWarps / wc);
     a.col_blocks = cb;
     a.main_groups = gy;
+    a.n_marked = L.n_masked;
     const dim3 grid(cb, gy + cg);
     return (B <= 2) ? launch_wc<1>(wc, a, grid, stream) : launch_wc<2>(wc, a, grid, stream);
 }

@@ -67,7 +67,7 @@ typedef struct EptqLayer {
     int32_t quantizer;        /* EPTQ_E8 or EPTQ_E8D4 */
     int32_t M;
     int32_t N;
-    int32_t n_masked;
+    int32_t n_masked;         /* rows of O_vals; -1 = not stated (read from O_row_ptr[M]) */
     int32_t qb_size;
     int32_t table_rows;       /* E8: rows of the table (<= 65535); E8-D4: 512 */
     const int16_t* Q;
