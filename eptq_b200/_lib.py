@@ -26,6 +26,8 @@ EXPORTS = {
     "eptq_e8d4_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _sz, _vp]),
     "eptq_linear_forward": (_i, [_vp, _vp, _vp, _i, _vp, _sz, _vp]),
     "eptq_dequantize": (_i, [_vp, _vp, _vp]),
+    "eptq_static_scratch_bytes": (_sz, []),
+    "eptq_linear_forward_static_scratch": (_i, [_vp, _vp, _vp, _i, _vp]),
 }
 
 

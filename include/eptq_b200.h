@@ -163,6 +163,28 @@ int eptq_linear_forward(const EptqLayer* layer, const uint16_t* x, uint16_t* y,
  */
 int eptq_dequantize(const EptqLayer* layer, uint16_t* W, void* stream);
 
+/*
+ * (No counterpart in the reference.)  Decode GEMV for callers that cannot
+ * allocate device memory and therefore cannot provide the scratch buffer of
+ * eptq_linear_forward -- a server whose memory is fully pre-reserved, a plug-in
+ * that must stay out of its host's allocator, a loop that may not call an
+ * allocator at all.  Same result as eptq_linear_forward; the scratch is a fixed
+ * array of eptq_static_scratch_bytes() (4 MiB) inside the library's device
+ * image, held by every GPU that loads the library until the process exits.
+ *
+ * Limits: E8-D4 layers without group scales, in_features a multiple of 32,
+ * batch 1..4, and a scratch need of at most eptq_static_scratch_bytes()
+ * (eptq_workspace_bytes tells the need); anything else returns
+ * EPTQ_ERR_UNSUPPORTED or, for the size, EPTQ_ERR_WORKSPACE.  The call itself
+ * never allocates or frees.  All calls on a device share the one array, which
+ * keeps the previous call's contents: calls that may overlap on the GPU race,
+ * so keep them ordered on one stream.  The first call on each device looks up
+ * the array's address; make that first call before any stream capture.
+ */
+size_t eptq_static_scratch_bytes(void);
+int eptq_linear_forward_static_scratch(const EptqLayer* layer, const uint16_t* x,
+                                       uint16_t* y, int B, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
