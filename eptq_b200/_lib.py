@@ -26,6 +26,8 @@ EXPORTS = {
     "eptq_e8d4_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _sz, _vp]),
     "eptq_linear_forward": (_i, [_vp, _vp, _vp, _i, _vp, _sz, _vp]),
     "eptq_dequantize": (_i, [_vp, _vp, _vp]),
+    "eptq_group_workspace_bytes": (_sz, [_vp, _i, _i]),
+    "eptq_linear_forward_group": (_i, [_vp, _i, _vp, _vp, _i, _vp, _sz, _vp]),
     "eptq_static_scratch_bytes": (_sz, []),
     "eptq_linear_forward_static_scratch": (_i, [_vp, _vp, _vp, _i, _vp]),
 }
@@ -38,7 +40,7 @@ class EptqLayer(C.Structure):
         ("n_masked", C.c_int32), ("qb_size", C.c_int32), ("table_rows", C.c_int32),
         ("Q", _vp), ("table32", _vp), ("table16", _vp), ("g", _vp), ("h", _vp),
         ("O_vals", _vp), ("O_col", _vp), ("O_row_ptr", _vp), ("bias", _vp), ("S_group", _vp),
-        ("table8", _vp), ("table8_scale", C.c_float),
+        ("table8", _vp), ("table8_scale", C.c_float), ("h_absmax", C.c_float),
     ]
 
 

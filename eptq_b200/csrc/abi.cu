@@ -19,6 +19,11 @@ size_t mma_workspace_bytes(int M, int N, int B);
 int launch_gemv_mma(const EptqLayer& L, const uint16_t* x, uint16_t* y, int B,
                     void* workspace, size_t workspace_bytes, cudaStream_t stream);
 
+bool group_gemv_supported(const EptqLayer* layers, int n, int B);
+size_t group_workspace_bytes(const EptqLayer* layers, int n, int B, int n_sms);
+int launch_gemv_group(const EptqLayer* layers, int n, const uint16_t* const* xs, uint16_t* const* ys, int B,
+                      void* workspace, size_t workspace_bytes, cudaStream_t stream);
+
 namespace {
 
 int check_layer_common(const EptqLayer* L) {
@@ -50,6 +55,13 @@ int forward_checked(const EptqLayer& L, const uint16_t* x, uint16_t* y, int B,
     if (!aligned16(L.table16)) return EPTQ_ERR_ALIGN;
     if ((L.N % 8) == 0 && !aligned16(x)) return EPTQ_ERR_ALIGN;
     if (workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return EPTQ_ERR_ALIGN;
+    if (group_gemv_supported(&L, 1, B) && aligned16(y)) {
+        const uint16_t* xs[1] = {x};
+        uint16_t* ys[1] = {y};
+        const size_t need = group_workspace_bytes(&L, 1, B, 0);
+        if (need != 0 && workspace != nullptr && workspace_bytes >= need)
+            return launch_gemv_group(&L, 1, xs, ys, B, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+    }
     if (mma_gemv_supported(L, B) && aligned16(L.g) && (L.bias == nullptr || aligned16(L.bias)) && aligned16(y))
         return launch_gemv_mma(L, x, y, B, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
     return launch_gemv_simt(L, x, y, B, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
@@ -112,7 +124,34 @@ size_t eptq_workspace_bytes(int M, int N, int B) {
         const size_t mma = mma_workspace_bytes(M, N, B);
         if (mma > bytes) bytes = mma;
     }
+    if (B <= 2 && (N % 32) == 0) {
+        EptqLayer shape = {};
+        shape.M = M; shape.N = N;
+        const size_t grp = group_workspace_bytes(&shape, 1, B, 0);
+        if (grp > bytes) bytes = grp;
+    }
     return (bytes + 255) & ~static_cast<size_t>(255);
+}
+
+size_t eptq_group_workspace_bytes(const EptqLayer* layers, int n_layers, int B) {
+    if (!group_gemv_supported(layers, n_layers, B)) return 0;
+    return (group_workspace_bytes(layers, n_layers, B, 0) + 255) & ~static_cast<size_t>(255);
+}
+
+int eptq_linear_forward_group(const EptqLayer* layers, int n_layers,
+                              const uint16_t* const* xs, uint16_t* const* ys, int B,
+                              void* workspace, size_t workspace_bytes, void* stream) {
+    if (layers == nullptr || xs == nullptr || ys == nullptr) return EPTQ_ERR_NULL;
+    if (n_layers < 1 || B < 1) return EPTQ_ERR_SHAPE;
+    for (int i = 0; i < n_layers; ++i) {
+        const int st = check_layer_common(&layers[i]);
+        if (st != EPTQ_OK) return st;
+        if (xs[i] == nullptr || ys[i] == nullptr) return EPTQ_ERR_NULL;
+        if (!aligned16(xs[i])) return EPTQ_ERR_ALIGN;
+    }
+    if (!group_gemv_supported(layers, n_layers, B)) return EPTQ_ERR_UNSUPPORTED;
+    if (workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return EPTQ_ERR_ALIGN;
+    return launch_gemv_group(layers, n_layers, xs, ys, B, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
 int eptq_prepare_d4_table8(const float* table, uint8_t* out, float* scale) {

@@ -1,0 +1,644 @@
+// Persistent E8-D4 decode GEMV over a group of independent layers (batch 1..2).
+//
+// One launch, one block of 16 warps per SM, covers up to kMaxGroupLayers layers
+// whose inputs are all ready (q/k/v, gate/up, the experts of a mixture, or a
+// single layer).  At B200 speed one 4096x4096 layer is 0.7 us of HBM traffic,
+// less than a kernel launch and one DRAM round trip, so per-layer launches are
+// latency-bound; here table build, launch and pipeline fill are paid once per
+// group and every warp streams a long contiguous run of work.
+//
+// Arithmetic (same as gemv_mma.cu): every 8-byte half-codeword read from the
+// shared-memory table is an A-fragment register pair of mma.sync.m16n8k16; the
+// activations enter as fp16 high part + fp16 remainder in separate B columns.
+//
+// Work split ("stream-K"): all 16-row x 32-column strips of all layers form one
+// sequence (layer, row tile, strip); main warp w takes the contiguous range
+// [w*W/nw, (w+1)*W/nw).  Inside a row tile the accumulators stay in registers;
+// at a row-tile boundary the warp writes its partial into the tile's slot
+// (slot = warp index - first warp of the tile) and takes a ticket; the last
+// arrival adds the slots in order, applies g and bias, writes fp16.  Each warp
+// works alone: Q arrives through a 3-deep register ring of 128-bit loads, the
+// activation pieces through a 512-byte warp-private slab, no block-wide barrier
+// after the table is built.
+//
+// Table addressing: the 64 KB replicated table sits at shared-window address
+// 0x10000, so the byte address of a half-codeword is a single logic operation
+// on the raw index bits: (q & 0xFF80) | (8*(lane%16) | 0x10000).
+//
+// Critical blocks: two warps per block walk the CSR in units of 4 Q rows and add
+// sum (O[i] - code[65535]) * h*x as one more partial per row tile.
+//
+// Reference counterpart: e8d4_fused_kernel_t (csrc/eptq_kernels.cu:161-292),
+// one launch per layer and batch row there.
+
+#include <cmath>
+#include <mutex>
+
+#include "common.cuh"
+
+namespace eptq {
+
+constexpr int kMaxGroupLayers = 32;
+
+struct GroupLayer {
+    const int16_t* Q;
+    const __half* g;
+    const __half* h;
+    const __half* x;
+    const __half* O_vals;
+    const int* O_col;
+    const int* O_row_ptr;
+    const __half* bias;
+    __half* y;
+    long long strip0;       // index of this layer's first strip in the global sequence
+    long long partial_off;  // float offset of this layer's partial sums
+    int M, N;
+    int ns;                 // strips per row tile = N / 32
+    int row_tiles;          // ceil(M / 16)
+    int tile0;              // index of this layer's first row tile (counters)
+    int corr0;              // index of this layer's first correction unit (4 Q rows each)
+    int slots;              // partial slots per row tile; the last one holds the corrections
+    float x_scale;          // power of two, <= 1 / max|h|
+    float x_inv_scale;
+};
+
+struct GroupArgs {
+    GroupLayer L[kMaxGroupLayers];
+    const uint2* table16;
+    float* partial;
+    unsigned* counters;
+    long long W;            // total strips
+    int n_layers;
+    int B;
+    int nw;                 // total main warps
+    int corr_units;         // total correction units
+    int n_corr_warps;
+};
+
+namespace {
+
+constexpr int kMainWarps = 14;
+constexpr int kCorrWarps = 2;
+constexpr int kGroupThreads = (kMainWarps + kCorrWarps) * 32;
+constexpr unsigned kTableAddr = 0x10000u;                       // shared-window address of the table
+constexpr int kGroupSmemBytes = 2 * 65536 - 1024;               // window [0x400, 0x20000)
+constexpr int kRing = 3;                                        // Q strips in flight per warp
+
+__device__ __forceinline__ unsigned smem_addr(const void* p) {
+    return static_cast<unsigned>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ uint2 table_lds(unsigned addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ unsigned prmt(unsigned a, unsigned b, unsigned sel) {
+    unsigned d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+__device__ __forceinline__ void mma_f16(float (&c)[4], const uint2& a01, const uint2& a23, unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a01.x), "r"(a01.y), "r"(a23.x), "r"(a23.y), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint4 ldg_stream(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ unsigned split_pieces(float v) {
+    const __half hi = __float2half_rn(v);
+    const __half lo = __float2half_rn(v - __half2float(hi));
+    return static_cast<unsigned>(__half_as_ushort(hi)) | (static_cast<unsigned>(__half_as_ushort(lo)) << 16);
+}
+// Shared-window addresses of the two half-codewords of the index in the low 16 bits of q.
+__device__ __forceinline__ void code_addrs(unsigned q, unsigned lane_tab, unsigned& ai, unsigned& aj) {
+    ai = (q & 0xFF80u) | lane_tab;
+    aj = ((q << 7) & 0x3F80u) | ((q & 0xC000u) | lane_tab);
+}
+
+// Warp that owns global strip s when warp w owns [w*W/nw, (w+1)*W/nw).
+__device__ __forceinline__ int owner_warp(long long s, long long W, int nw) {
+    int w = static_cast<int>((s * nw) / W);
+    while (w + 1 < nw && (static_cast<long long>(w + 1) * W) / nw <= s) ++w;
+    while (w > 0 && (static_cast<long long>(w) * W) / nw > s) --w;
+    return w;
+}
+
+struct Affine { float g[4]; float b[4]; };
+
+__device__ __forceinline__ Affine load_affine(const GroupLayer& L, int rt, int lane) {
+    Affine a;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { a.g[i] = 0.f; a.b[i] = 0.f; }
+    const int row = rt * 16 + (lane >> 1);
+    if (row < L.M) {
+        const int o = row * 8 + (lane & 1) * 4;
+        const uint2 graw = __ldg(reinterpret_cast<const uint2*>(L.g + o));
+        const float2 g01 = __half22float2(*reinterpret_cast<const __half2*>(&graw.x));
+        const float2 g23 = __half22float2(*reinterpret_cast<const __half2*>(&graw.y));
+        a.g[0] = g01.x; a.g[1] = g01.y; a.g[2] = g23.x; a.g[3] = g23.y;
+        if (L.bias != nullptr) {
+            const uint2 braw = __ldg(reinterpret_cast<const uint2*>(L.bias + o));
+            const float2 b01 = __half22float2(*reinterpret_cast<const __half2*>(&braw.x));
+            const float2 b23 = __half22float2(*reinterpret_cast<const __half2*>(&braw.y));
+            a.b[0] = b01.x; a.b[1] = b01.y; a.b[2] = b23.x; a.b[3] = b23.y;
+        }
+    }
+    return a;
+}
+
+// Take a ticket for row tile rt of layer L; the last of `expected` arrivals adds
+// the partial slots [0, n_main) and the correction slot and writes y.
+__device__ __forceinline__ void arrive_and_finalize(const GroupArgs& p, const GroupLayer& L, int rt, int n_main,
+                                                    int lane, const Affine& aff) {
+    __syncwarp();
+    unsigned ticket = 0;
+    unsigned* ctr = p.counters + L.tile0 + rt;
+    if (lane == 0)
+        asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(ticket) : "l"(ctr) : "memory");
+    ticket = __shfl_sync(0xffffffffu, ticket, 0);
+    if (ticket != static_cast<unsigned>(n_main) + 3u) return;       // n_main GEMV partials + 4 correction quarters
+    if (lane == 0) *ctr = 0u;
+    const int row = rt * 16 + (lane >> 1);
+    if (row >= L.M) return;
+    const int o = row * 8 + (lane & 1) * 4;
+    for (int b = 0; b < p.B; ++b) {
+        const float* base = p.partial + L.partial_off + (static_cast<size_t>(rt) * L.slots * p.B + b) * 128 + lane * 4;
+        float4 s = __ldcg(reinterpret_cast<const float4*>(base + static_cast<size_t>(L.slots - 1) * p.B * 128));
+        for (int k = 0; k < n_main; ++k) {
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(base + static_cast<size_t>(k) * p.B * 128));
+            s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+        }
+        const __half2 o01 = __floats2half2_rn(fmaf(s.x, aff.g[0], aff.b[0]), fmaf(s.y, aff.g[1], aff.b[1]));
+        const __half2 o23 = __floats2half2_rn(fmaf(s.z, aff.g[2], aff.b[2]), fmaf(s.w, aff.g[3], aff.b[3]));
+        uint2 outv;
+        outv.x = *reinterpret_cast<const unsigned*>(&o01);
+        outv.y = *reinterpret_cast<const unsigned*>(&o23);
+        *reinterpret_cast<uint2*>(L.y + static_cast<size_t>(b) * 8 * L.M + o) = outv;
+    }
+}
+
+// Number of main warps that contribute to row tile rt of layer L, and the first of them.
+__device__ __forceinline__ int tile_contributors(const GroupArgs& p, const GroupLayer& L, int rt, int& first) {
+    const long long s0 = L.strip0 + static_cast<long long>(rt) * L.ns;
+    first = owner_warp(s0, p.W, p.nw);
+    return owner_warp(s0 + L.ns - 1, p.W, p.nw) - first + 1;
+}
+
+}  // namespace
+}  // namespace eptq
+
+namespace eptq {
+namespace {
+
+// Correction of 4 consecutive Q rows (8 lanes per row, 4 entries per lane and pass).
+// Weight-side loads (row pointers, columns, O, h) are issued before `wait_dep`, x after.
+template <typename WaitFn>
+__device__ __forceinline__ void correction_unit(const GroupArgs& p, const GroupLayer& L, int qt, int lane,
+                                                float cstar0, float cstar1, float cstar2, float cstar3,
+                                                WaitFn wait_dep) {
+    const int row = qt * 4 + (lane >> 3);
+    const int sub = lane & 7;
+    const int rt = qt >> 2;
+    const Affine aff = load_affine(L, rt, lane);
+    const float cstar[4] = {cstar0, cstar1, cstar2, cstar3};
+    float acc[2][8];
+#pragma unroll
+    for (int b = 0; b < 2; ++b)
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[b][k] = 0.f;
+    int lo = 0, hi = 0;
+    if (row < L.M) {
+        lo = __ldg(L.O_row_ptr + row);
+        hi = __ldg(L.O_row_ptr + row + 1);
+    }
+    bool first = true;
+    for (int i = lo + sub; __any_sync(0xffffffffu, i < hi) || first; i += 32) {
+        int col[4];
+        float hv[4];
+        uint4 ov[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) col[j] = (i + 8 * j < hi) ? __ldg(L.O_col + i + 8 * j) : -1;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (col[j] >= 0) {
+                hv[j] = __half2float(__ldg(L.h + col[j]));
+                ov[j] = ldg128(L.O_vals + static_cast<size_t>(i + 8 * j) * 8);
+            } else {
+                hv[j] = 0.f;
+                ov[j] = make_uint4(0, 0, 0, 0);
+            }
+        }
+        if (first) { wait_dep(); first = false; }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float o8[8];
+            unpack8(ov[j], o8);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) o8[k] -= cstar[k & 3];
+#pragma unroll
+            for (int b = 0; b < 2; ++b) {
+                if (b < p.B) {
+                    const float xv = (col[j] >= 0) ? hv[j] * __half2float(__ldg(L.x + static_cast<size_t>(b) * L.N + col[j])) : 0.f;
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) acc[b][k] = fmaf(o8[k], xv, acc[b][k]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+        if (b < p.B) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                acc[b][k] += __shfl_xor_sync(0xffffffffu, acc[b][k], 1);
+                acc[b][k] += __shfl_xor_sync(0xffffffffu, acc[b][k], 2);
+                acc[b][k] += __shfl_xor_sync(0xffffffffu, acc[b][k], 4);
+            }
+            if (sub == 0) {
+                float* dst = p.partial + L.partial_off + ((static_cast<size_t>(rt) * L.slots + (L.slots - 1)) * p.B + b) * 128
+                           + ((qt & 3) * 4 + (lane >> 3)) * 8;
+                __stcg(reinterpret_cast<float4*>(dst), make_float4(acc[b][0], acc[b][1], acc[b][2], acc[b][3]));
+                __stcg(reinterpret_cast<float4*>(dst + 4), make_float4(acc[b][4], acc[b][5], acc[b][6], acc[b][7]));
+            }
+        }
+    }
+    int first_warp;
+    const int n_main = tile_contributors(p, L, rt, first_warp);
+    arrive_and_finalize(p, L, rt, n_main, lane, aff);
+}
+
+// Position in the global strip sequence.
+struct StripIter {
+    long long s;      // global strip index
+    int l, rt, strip;
+    __device__ __forceinline__ void seek(const GroupArgs& p, long long pos) {
+        s = pos;
+        l = 0;
+        while (l + 1 < p.n_layers && p.L[l + 1].strip0 <= pos) ++l;
+        const long long local = pos - p.L[l].strip0;
+        rt = static_cast<int>(local / p.L[l].ns);
+        strip = static_cast<int>(local - static_cast<long long>(rt) * p.L[l].ns);
+    }
+    // returns true when the step crossed into a new row tile (or layer)
+    __device__ __forceinline__ bool advance(const GroupArgs& p) {
+        ++s;
+        if (++strip < p.L[l].ns) return false;
+        strip = 0;
+        if (++rt == p.L[l].row_tiles) { rt = 0; ++l; }
+        return true;
+    }
+};
+
+__global__ void __launch_bounds__(kGroupThreads, 1) gemv_group_kernel(const __grid_constant__ GroupArgs p) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const unsigned base = smem_addr(smem_raw);                 // 0x400 on sm_100: the first KB is reserved
+    unsigned char* tab = smem_raw + (kTableAddr - base);       // generic pointer to shared address 0x10000
+
+    asm volatile("griddepcontrol.launch_dependents;");
+
+    // Replicated table; entry order follows the raw stored bits (true index ^ 0x100 on 9 bits).
+    {
+        const int chunk = threadIdx.x & 7;
+        for (int e = threadIdx.x >> 3; e < 512; e += kGroupThreads / 8) {
+            const uint2 v = __ldg(p.table16 + (e ^ 0x100));
+            *reinterpret_cast<uint4*>(tab + e * 128 + chunk * 16) = make_uint4(v.x, v.y, v.x, v.y);
+        }
+    }
+
+    if (warp >= kMainWarps) {
+        // ---- correction warps
+        const uint2 craw = __ldg(p.table16 + 511);      // what the main loop adds for a marker: entry (3,127), both halves
+        const float2 c01 = __half22float2(*reinterpret_cast<const __half2*>(&craw.x));
+        const float2 c23 = __half22float2(*reinterpret_cast<const __half2*>(&craw.y));
+        __syncthreads();
+        bool waited = false;
+        const int cw = blockIdx.x * kCorrWarps + (warp - kMainWarps);
+        int l = 0;
+        for (int u = cw; u < p.corr_units; u += p.n_corr_warps) {
+            while (l + 1 < p.n_layers && p.L[l + 1].corr0 <= u) ++l;
+            correction_unit(p, p.L[l], u - p.L[l].corr0, lane, c01.x, c01.y, c23.x, c23.y, [&]() {
+                if (!waited) { asm volatile("griddepcontrol.wait;" ::: "memory"); waited = true; }
+            });
+        }
+        return;
+    }
+
+    // ---- main warps
+    const int g = lane >> 2, t = lane & 3;
+    const int gw = blockIdx.x * kMainWarps + warp;
+    const long long s_begin = (static_cast<long long>(gw) * p.W) / p.nw;
+    const long long s_end = (static_cast<long long>(gw + 1) * p.W) / p.nw;
+
+    unsigned* slab = reinterpret_cast<unsigned*>(smem_raw) + warp * 128;     // [parity][batch][32] words
+    slab[lane] = 0u; slab[32 + lane] = 0u; slab[64 + lane] = 0u; slab[96 + lane] = 0u;
+
+    // Q ring: rows g and g+8 of the tile, 8 columns per lane.  h/x ring: column `lane` of the strip.
+    uint4 qa[kRing], qb[kRing];
+    __half hr[kRing], xr0[kRing], xr1[kRing];
+    StripIter pf;                                      // prefetch position
+    pf.seek(p, s_begin < p.W ? s_begin : 0);
+    auto q_ptrs = [&](const StripIter& it, const int16_t*& pa, const int16_t*& pb) {
+        const GroupLayer& L = p.L[it.l];
+        const int ra = min(it.rt * 16 + g, L.M - 1), rb = min(it.rt * 16 + g + 8, L.M - 1);
+        const int col = it.strip * 32 + 8 * t;
+        pa = L.Q + static_cast<size_t>(ra) * L.N + col;
+        pb = L.Q + static_cast<size_t>(rb) * L.N + col;
+    };
+#pragma unroll
+    for (int i = 0; i < kRing; ++i) {
+        qa[i] = make_uint4(0, 0, 0, 0); qb[i] = make_uint4(0, 0, 0, 0);
+        hr[i] = __ushort_as_half(0); xr0[i] = __ushort_as_half(0); xr1[i] = __ushort_as_half(0);
+    }
+    {
+        StripIter it = pf;
+#pragma unroll
+        for (int i = 0; i < kRing; ++i) {
+            if (it.s < s_end) {
+                const int16_t *pa, *pb;
+                q_ptrs(it, pa, pb);
+                qa[i] = ldg_stream(pa);
+                qb[i] = ldg_stream(pb);
+                hr[i] = __ldg(p.L[it.l].h + it.strip * 32 + lane);
+                it.advance(p);
+            }
+        }
+    }
+    __syncthreads();                                   // table complete (all 16 warps reach this once)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    {
+        StripIter it = pf;
+#pragma unroll
+        for (int i = 0; i < kRing; ++i) {
+            if (it.s < s_end) {
+                const GroupLayer& L = p.L[it.l];
+                xr0[i] = __ldg(L.x + it.strip * 32 + lane);
+                if (p.B > 1) xr1[i] = __ldg(L.x + L.N + it.strip * 32 + lane);
+                it.advance(p);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < kRing; ++i) if (pf.s < s_end) pf.advance(p);     // pf now points kRing strips ahead
+    }
+    if (s_begin >= s_end) return;
+
+    const unsigned lane_tab = 8u * (lane & 15) | kTableAddr;
+    // B column g = (batch g>>2, piece (g>>1)&1, dd' = g&1): the piece goes to the low or high half.
+    const unsigned pbyte = 2u * ((g >> 1) & 1);
+    const unsigned sel = (g & 1) ? ((((pbyte + 1) << 12) | (pbyte << 8)) | 0x0044u) : (0x4400u | ((pbyte + 1) << 4) | pbyte);
+    const unsigned* my_slab = slab + (g >> 2) * 32 + 8 * t;
+
+    StripIter cur;
+    cur.seek(p, s_begin);
+    Affine aff = load_affine(p.L[cur.l], cur.rt, lane);
+    int par = 0;
+    float acc[2][2][4];                                // [row group g / g+8][half i / j][dims]
+#pragma unroll
+    for (int a = 0; a < 2; ++a)
+#pragma unroll
+        for (int b = 0; b < 2; ++b)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[a][b][c] = 0.f;
+
+    auto flush = [&](int l, int rt) {
+        const GroupLayer& L = p.L[l];
+        int first_warp;
+        const int n_main = tile_contributors(p, L, rt, first_warp);
+        const float inv = L.x_inv_scale;
+        const int b = t >> 1;
+        float* dst = p.partial + L.partial_off + ((static_cast<size_t>(rt) * L.slots + (gw - first_warp)) * p.B + b) * 128;
+#pragma unroll
+        for (int rg = 0; rg < 2; ++rg)
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {
+                float tot[4];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const float own = acc[rg][hf][c] * inv;
+                    tot[c] = own + __shfl_xor_sync(0xffffffffu, own, 1);
+                    acc[rg][hf][c] = 0.f;
+                }
+                if ((t & 1) == 0 && b < p.B)
+                    __stcg(reinterpret_cast<float4*>(dst + (g + 8 * rg) * 8 + hf * 4), make_float4(tot[0], tot[1], tot[2], tot[3]));
+            }
+        arrive_and_finalize(p, L, rt, n_main, lane, aff);
+    };
+
+#define EPTQ_GROUP_STEP(I)                                                                                   \
+    {                                                                                                        \
+        if (cur.s >= s_end) break;                                                                           \
+        const GroupLayer& L = p.L[cur.l];                                                                    \
+        const uint4 ca = qa[I], cb = qb[I];                                                                  \
+        const float hx = __half2float(hr[I]) * L.x_scale;                                                    \
+        unsigned* wslab = slab + par * 64;                                                                   \
+        wslab[lane] = split_pieces(__half2float(xr0[I]) * hx);                                               \
+        if (p.B > 1) wslab[32 + lane] = split_pieces(__half2float(xr1[I]) * hx);                             \
+        if (pf.s < s_end) {                                                                                  \
+            const int16_t *pa, *pb;                                                                          \
+            q_ptrs(pf, pa, pb);                                                                              \
+            qa[I] = ldg_stream(pa);                                                                          \
+            qb[I] = ldg_stream(pb);                                                                          \
+            const GroupLayer& PL = p.L[pf.l];                                                                \
+            hr[I] = __ldg(PL.h + pf.strip * 32 + lane);                                                      \
+            xr0[I] = __ldg(PL.x + pf.strip * 32 + lane);                                                     \
+            if (p.B > 1) xr1[I] = __ldg(PL.x + PL.N + pf.strip * 32 + lane);                                 \
+            pf.advance(p);                                                                                   \
+        }                                                                                                    \
+        __syncwarp();                                                                                        \
+        const uint4 w0 = *reinterpret_cast<const uint4*>(my_slab + par * 64);                                \
+        const uint4 w1 = *reinterpret_cast<const uint4*>(my_slab + par * 64 + 4);                            \
+        par ^= 1;                                                                                            \
+        const unsigned wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};                             \
+        const unsigned qav[4] = {ca.x, ca.y, ca.z, ca.w};                                                    \
+        const unsigned qbv[4] = {cb.x, cb.y, cb.z, cb.w};                                                    \
+        _Pragma("unroll")                                                                                    \
+        for (int m = 0; m < 4; ++m) {                                                                        \
+            unsigned i0, j0, i1, j1;                                                                         \
+            code_addrs(qav[m], lane_tab, i0, j0);                                                            \
+            code_addrs(qav[m] >> 16, lane_tab, i1, j1);                                                      \
+            const uint2 ai0 = table_lds(i0), aj0 = table_lds(j0), ai1 = table_lds(i1), aj1 = table_lds(j1);  \
+            code_addrs(qbv[m], lane_tab, i0, j0);                                                            \
+            code_addrs(qbv[m] >> 16, lane_tab, i1, j1);                                                      \
+            const uint2 bi0 = table_lds(i0), bj0 = table_lds(j0), bi1 = table_lds(i1), bj1 = table_lds(j1);  \
+            const unsigned b0 = prmt(wv[2 * m], 0u, sel), b1 = prmt(wv[2 * m + 1], 0u, sel);                 \
+            mma_f16(acc[0][0], ai0, ai1, b0, b1);                                                            \
+            mma_f16(acc[0][1], aj0, aj1, b0, b1);                                                            \
+            mma_f16(acc[1][0], bi0, bi1, b0, b1);                                                            \
+            mma_f16(acc[1][1], bj0, bj1, b0, b1);                                                            \
+        }                                                                                                    \
+        const int l_done = cur.l, rt_done = cur.rt;                                                          \
+        const bool crossed = cur.advance(p);                                                                 \
+        if (crossed || cur.s >= s_end) {                                                                     \
+            flush(l_done, rt_done);                                                                          \
+            if (cur.s < s_end) aff = load_affine(p.L[cur.l], cur.rt, lane);                                  \
+        }                                                                                                    \
+    }
+
+    for (;;) {
+        EPTQ_GROUP_STEP(0)
+        EPTQ_GROUP_STEP(1)
+        EPTQ_GROUP_STEP(2)
+    }
+#undef EPTQ_GROUP_STEP
+}
+
+}  // namespace
+}  // namespace eptq
+
+namespace eptq {
+
+namespace {
+
+struct GroupPlan {
+    long long W = 0;
+    int nw = 0;
+    int n_sms = 0;
+    int tiles = 0;
+    int corr_units = 0;
+    size_t partial_floats = 0;
+    int slots[kMaxGroupLayers] = {};
+};
+
+int cached_sm_count() {
+    static int sms[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+    if (sms[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+        sms[dev] = n;
+    }
+    return sms[dev];
+}
+
+// Shapes only: how many strips, warps, slots and scratch floats a group needs.
+bool plan_group(const EptqLayer* layers, int n, int B, int n_sms, GroupPlan& plan) {
+    if (n < 1 || n > kMaxGroupLayers || B < 1 || B > 2 || n_sms < 1) return false;
+    plan = GroupPlan();
+    plan.n_sms = n_sms;
+    plan.nw = n_sms * kMainWarps;
+    for (int i = 0; i < n; ++i) {
+        const int row_tiles = (layers[i].M + 15) / 16;
+        plan.W += static_cast<long long>(row_tiles) * (layers[i].N / 32);
+        plan.tiles += row_tiles;
+        plan.corr_units += row_tiles * 4;
+    }
+    if (plan.W < 1 || plan.tiles > kMaxCounters) return false;
+    const long long per_warp = plan.W / plan.nw > 0 ? plan.W / plan.nw : 1;
+    for (int i = 0; i < n; ++i) {
+        const int ns = layers[i].N / 32;
+        long long contributors = (ns + per_warp - 1) / per_warp + 1;
+        if (contributors > ns) contributors = ns;
+        plan.slots[i] = static_cast<int>(contributors) + 1;                 // + the correction slot
+        plan.partial_floats += static_cast<size_t>((layers[i].M + 15) / 16) * plan.slots[i] * B * 128;
+    }
+    return true;
+}
+
+bool group_layer_supported(const EptqLayer& L) {
+    return L.quantizer == EPTQ_E8D4 && L.table16 != nullptr && L.S_group == nullptr && L.M > 0 && L.N > 0 &&
+           (L.N % 32) == 0 && L.h_absmax > 0.f && L.Q != nullptr && L.g != nullptr && L.h != nullptr &&
+           L.O_row_ptr != nullptr && (L.n_masked == 0 || (L.O_vals != nullptr && L.O_col != nullptr)) &&
+           aligned16(L.Q) && aligned16(L.table16) && aligned16(L.g) && (L.bias == nullptr || aligned16(L.bias)) &&
+           (L.n_masked == 0 || aligned16(L.O_vals));
+}
+
+}  // namespace
+
+bool group_gemv_supported(const EptqLayer* layers, int n, int B) {
+    if (layers == nullptr || n < 1 || n > kMaxGroupLayers || B < 1 || B > 2) return false;
+    for (int i = 0; i < n; ++i) {
+        if (!group_layer_supported(layers[i])) return false;
+        if (layers[i].table16 != layers[0].table16) return false;          // one codebook per launch
+    }
+    return true;
+}
+
+size_t group_workspace_bytes(const EptqLayer* layers, int n, int B, int n_sms) {
+    GroupPlan plan;
+    if (n_sms <= 0) n_sms = 148;
+    if (!plan_group(layers, n, B, n_sms, plan)) return 0;
+    return kCounterBytes + plan.partial_floats * sizeof(float);
+}
+
+int launch_gemv_group(const EptqLayer* layers, int n, const uint16_t* const* xs, uint16_t* const* ys, int B,
+                      void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+    const int n_sms = cached_sm_count();
+    GroupPlan plan;
+    if (!plan_group(layers, n, B, n_sms, plan)) return EPTQ_ERR_UNSUPPORTED;
+    const size_t need = kCounterBytes + plan.partial_floats * sizeof(float);
+    if (workspace == nullptr || workspace_bytes < need) return EPTQ_ERR_WORKSPACE;
+
+    static GroupArgs args;                     // large: keep it off the stack; filled under a lock
+    static std::mutex args_mutex;
+    std::lock_guard<std::mutex> lock(args_mutex);
+    GroupArgs& a = args;
+    a.table16 = reinterpret_cast<const uint2*>(layers[0].table16);
+    a.counters = reinterpret_cast<unsigned*>(workspace);
+    a.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + kCounterBytes);
+    a.W = plan.W;
+    a.n_layers = n;
+    a.B = B;
+    a.nw = plan.nw;
+    a.corr_units = plan.corr_units;
+    a.n_corr_warps = n_sms * kCorrWarps;
+    long long strip0 = 0, poff = 0;
+    int tile0 = 0, corr0 = 0;
+    for (int i = 0; i < n; ++i) {
+        const EptqLayer& L = layers[i];
+        GroupLayer& G = a.L[i];
+        if (xs[i] == nullptr || ys[i] == nullptr) return EPTQ_ERR_NULL;
+        if (!aligned16(ys[i])) return EPTQ_ERR_ALIGN;
+        G.Q = L.Q;
+        G.g = reinterpret_cast<const __half*>(L.g);
+        G.h = reinterpret_cast<const __half*>(L.h);
+        G.x = reinterpret_cast<const __half*>(xs[i]);
+        G.O_vals = reinterpret_cast<const __half*>(L.O_vals);
+        G.O_col = L.O_col;
+        G.O_row_ptr = L.O_row_ptr;
+        G.bias = reinterpret_cast<const __half*>(L.bias);
+        G.y = reinterpret_cast<__half*>(ys[i]);
+        G.M = L.M; G.N = L.N;
+        G.ns = L.N / 32;
+        G.row_tiles = (L.M + 15) / 16;
+        G.strip0 = strip0; G.partial_off = poff; G.tile0 = tile0; G.corr0 = corr0;
+        G.slots = plan.slots[i];
+        int e = 0;
+        std::frexp(L.h_absmax, &e);            // h_absmax = m * 2^e, m in [0.5, 1)  =>  2^-e <= 1/h_absmax
+        G.x_scale = std::ldexp(1.0f, -e);
+        G.x_inv_scale = std::ldexp(1.0f, e);
+        strip0 += static_cast<long long>(G.row_tiles) * G.ns;
+        poff += static_cast<long long>(G.row_tiles) * G.slots * B * 128;
+        tile0 += G.row_tiles;
+        corr0 += G.row_tiles * 4;
+    }
+
+    static bool attr_done[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return EPTQ_ERR_LAUNCH;
+    if (!attr_done[dev]) {
+        if (cudaFuncSetAttribute(gemv_group_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGroupSmemBytes) != cudaSuccess)
+            return EPTQ_ERR_LAUNCH;
+        attr_done[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n_sms);
+    cfg.blockDim = dim3(kGroupThreads);
+    cfg.dynamicSmemBytes = kGroupSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t err = cudaLaunchKernelEx(&cfg, gemv_group_kernel, a);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return err == cudaSuccess ? EPTQ_OK : EPTQ_ERR_LAUNCH;
+}
+
+}  // namespace eptq

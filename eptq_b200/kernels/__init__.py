@@ -22,7 +22,8 @@ import torch
 
 from .. import _lib
 
-__all__ = ["e8_forward", "e8d4_forward", "linear_forward", "dequantize_layer", "workspace_for"]
+__all__ = ["e8_forward", "e8d4_forward", "linear_forward", "linear_forward_group", "dequantize_layer",
+           "workspace_for"]
 
 _workspaces: Dict[Tuple[int, int], torch.Tensor] = {}
 
@@ -149,6 +150,22 @@ def d4_table8(table: torch.Tensor) -> Optional[Tuple[torch.Tensor, float]]:
     return res
 
 
+_absmax_cache: Dict[tuple, float] = {}
+
+
+def h_absmax(h: torch.Tensor) -> float:
+    """max |h| of a column-scale vector, computed once per tensor (one device sync) and cached.
+    The persistent GEMV derives its activation scale from it."""
+    key = (h.data_ptr(), h.device, h.numel(), h._version)
+    v = _absmax_cache.get(key)
+    if v is None:
+        v = float(h.abs().max().item()) if h.numel() else 0.0
+        if len(_absmax_cache) > 4096:
+            _absmax_cache.clear()
+        _absmax_cache[key] = v
+    return v
+
+
 def _make_desc(quantizer_type: str, Q, table32, table16, g, h, O_vals, O_col, O_row_ptr, bias, S_group,
                qb_size: int) -> _lib.EptqLayer:
     d = _lib.EptqLayer()
@@ -165,6 +182,7 @@ def _make_desc(quantizer_type: str, Q, table32, table16, g, h, O_vals, O_col, O_
     d.O_vals, d.O_col, d.O_row_ptr = _ptr(O_vals), _ptr(O_col), O_row_ptr.data_ptr()
     d.bias, d.S_group = _ptr(bias), _ptr(S_group)
     d.table8, d.table8_scale = None, 0.0
+    d.h_absmax = h_absmax(h) if (quantizer_type == "e8_d4" and Q.is_cuda) else 0.0
     if quantizer_type == "e8_d4" and Q.is_cuda:
         t8 = d4_table8(table32 if table32 is not None else table16)
         if t8 is not None:
@@ -200,6 +218,28 @@ def linear_forward(x: torch.Tensor, Q: torch.Tensor, table16: torch.Tensor, tabl
 @linear_forward.register_fake
 def _(x, Q, table16, table32, g, h, O_vals, O_col, O_row_ptr, bias, S_group, quantizer_type, qb_size):
     return x.new_empty(x.shape[0], Q.shape[0] * 8, dtype=torch.float16)
+
+
+def linear_forward_group(descs, xs, out_features, workspace: Optional[torch.Tensor] = None):
+    """Several independent layers in one launch (eptq_linear_forward_group).  `descs` are EptqLayer
+    descriptors (see EPTQLinear.descriptor), `xs` contiguous fp16 CUDA tensors (B, in_i) with one B;
+    returns the list of (B, out_i) fp16 outputs.  Raises if the group is not eligible."""
+    lib = _lib.load()
+    n = len(descs)
+    B = xs[0].shape[0]
+    dev = xs[0].device
+    ys = [torch.empty((B, o), dtype=torch.float16, device=dev) for o in out_features]
+    arr = (_lib.EptqLayer * n)(*descs)
+    need = lib.eptq_group_workspace_bytes(arr, n, B)
+    if need == 0:
+        raise RuntimeError("eptq_b200: this set of layers cannot run as one group launch")
+    ws = workspace if workspace is not None else workspace_for(dev, need)
+    xp = (C.c_void_p * n)(*[x.data_ptr() for x in xs])
+    yp = (C.c_void_p * n)(*[y.data_ptr() for y in ys])
+    with torch.cuda.device(dev):
+        st = lib.eptq_linear_forward_group(arr, n, xp, yp, B, ws.data_ptr(), ws.numel(), _stream(dev))
+    _lib.check(st, "eptq group forward")
+    return ys
 
 
 def dequantize_layer(Q: torch.Tensor, table32: torch.Tensor, g: torch.Tensor, h: torch.Tensor,

@@ -21,7 +21,7 @@ from typing import Optional
 import torch
 import torch.nn as nn
 
-from . import dequantize_layer, linear_forward
+from . import _make_desc, dequantize_layer, linear_forward, linear_forward_group
 
 MARKER = 32767     # int16 value that marks a critical block (index 65535 - 32768)
 
@@ -162,9 +162,29 @@ class EPTQLinear(nn.Module):
         return dequantize_layer(self.Q, self._codebook32, self.g, self.h, self.O_vals, self.O_col,
                                 self.O_row_ptr, self.S_group, self.quantizer_type, self.qb_size)
 
+    def descriptor(self):
+        """The C-ABI description (struct EptqLayer) of this layer's device buffers."""
+        return _make_desc(self.quantizer_type, self.Q, self._codebook32, self._codebook, self.g, self.h,
+                          self.O_vals, self.O_col, self.O_row_ptr, self.bias, self.S_group, self.qb_size)
+
     def extra_repr(self) -> str:
         return (f"in={self.in_features}, out={self.out_features}, quantizer={self.quantizer_type}, "
                 f"n_masked={self.O_col.shape[0]}")
+
+
+def forward_group(layers, xs):
+    """Apply several independent EPTQLinear layers in one kernel launch: layers[i](xs[i]) for all i.
+    Inputs need one common leading shape; returns the list of outputs.  Meant for q/k/v and gate/up."""
+    lead = xs[0].shape[:-1]
+    x2 = []
+    for lin, x in zip(layers, xs):
+        if not x.is_cuda:
+            raise RuntimeError("EPTQLinear runs on CUDA tensors only (there is no CPU path)")
+        v = x.reshape(-1, lin.in_features)
+        v = v if v.dtype == torch.float16 else v.half()
+        x2.append(v if v.is_contiguous() else v.contiguous())
+    ys = linear_forward_group([lin.descriptor() for lin in layers], x2, [lin.out_features for lin in layers])
+    return [y.to(x.dtype).reshape(*lead, lin.out_features) for y, x, lin in zip(ys, xs, layers)]
 
 
 QuantizedLinear = EPTQLinear

@@ -82,6 +82,7 @@ typedef struct EptqLayer {
     const uint16_t* S_group;
     const uint8_t* table8;
     float table8_scale;
+    float h_absmax;           /* max |h|, or 0 if not known (then the persistent GEMV is not used) */
 } EptqLayer;
 
 /* ABI version of the loaded library (EPTQ_ABI_VERSION at build time). */
@@ -153,6 +154,22 @@ int eptq_e8d4_forward(const int16_t* Q, const uint16_t* codes,
 int eptq_linear_forward(const EptqLayer* layer, const uint16_t* x, uint16_t* y,
                         int B, void* workspace, size_t workspace_bytes,
                         void* stream);
+
+/*
+ * Forward of `n_layers` (1..32) independent layers in ONE launch: y[i] (B, 8*M_i)
+ * = layer i applied to x[i] (B, N_i).  For layers whose inputs are all ready --
+ * q/k/v or gate/up of a decoder layer (the reference calls them one by one,
+ * kernels/linear.py:154-212), the experts of a mixture, or a single layer.
+ * Requirements: E8-D4 layers sharing one table16, no group scales, N % 32 == 0,
+ * h_absmax set, B = 1 or 2; otherwise EPTQ_ERR_UNSUPPORTED (call
+ * eptq_linear_forward per layer instead).  `xs` / `ys` are host arrays of
+ * device pointers.  Scratch as for eptq_linear_forward, size from
+ * eptq_group_workspace_bytes.
+ */
+size_t eptq_group_workspace_bytes(const EptqLayer* layers, int n_layers, int B);
+int eptq_linear_forward_group(const EptqLayer* layers, int n_layers,
+                              const uint16_t* const* xs, uint16_t* const* ys, int B,
+                              void* workspace, size_t workspace_bytes, void* stream);
 
 /*
  * Reconstruct the fp16 weight (8M, N) row-major, bit-for-bit what the

@@ -1,0 +1,58 @@
+"""Several independent layers in one launch (eptq_linear_forward_group) against the oracle."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from eptq_b200.kernels.linear import EPTQLinear, forward_group
+from eptq_b200.synthetic import make_activations, make_layer
+from tests import util
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+TABLE = torch.from_numpy(oracle.d4_table(1.75))
+
+
+def reference(qd, x):
+    W16 = oracle.dequantize_layer(util.qld_arrays(qd), oracle.d4_table(1.75))
+    return oracle.linear_reference(x.cpu().numpy(), W16, None if qd.bias is None else qd.bias.numpy())
+
+
+@pytest.mark.parametrize("batch", [1, 2])
+@pytest.mark.parametrize("shapes", [
+    [(4096, 4096)] * 3,                                   # q, k, v
+    [(11008, 4096), (11008, 4096)],                       # gate, up
+    [(4096, 4096), (1024, 4096), (1024, 4096)],           # grouped-query attention
+    [(40, 96), (8, 32), (264, 2752), (136, 160)],         # ragged row counts, tiny layers
+    [(4096, 11008)],
+    [(4096, 4096)] * 4 + [(11008, 4096)] * 2 + [(4096, 11008)],   # a whole decoder layer's linears
+])
+def test_group_matches_oracle(shapes, batch):
+    qds = [make_layer(o, i, seed=11 * k + o + i, outlier_frac=0.004, bias=(k % 2 == 0)) for k, (o, i) in enumerate(shapes)]
+    lins = [EPTQLinear.from_quantized_data(qd, TABLE, "e8_d4").to(DEV) for qd in qds]
+    xs = [make_activations(batch, i, seed=31 + k) for k, (_, i) in enumerate(shapes)]
+    ys = forward_group(lins, [x.to(DEV) for x in xs])
+    for qd, x, y in zip(qds, xs, ys):
+        assert util.max_rel_err(y.float().cpu().numpy(), reference(qd, x)) <= util.REL_TOL
+
+
+def test_group_equals_single_calls_and_repeats():
+    shapes = [(4096, 4096), (11008, 4096), (4096, 11008)]
+    lins = [EPTQLinear.from_quantized_data(make_layer(o, i, seed=o + i), TABLE, "e8_d4").to(DEV) for o, i in shapes]
+    xs = [make_activations(1, i, seed=i).to(DEV) for _, i in shapes]
+    singles = [lin(x) for lin, x in zip(lins, xs)]
+    first = forward_group(lins, xs)
+    for a, b in zip(first, singles):
+        assert float((a.float() - b.float()).abs().max() / b.float().abs().max()) <= util.REL_TOL
+    for _ in range(3):
+        for a, b in zip(forward_group(lins, xs), first):
+            assert torch.equal(a, b)
+
+
+def test_group_rejects_ineligible_sets():
+    e8 = EPTQLinear.from_quantized_data(make_layer(64, 64, seed=1), torch.from_numpy(oracle.e8_table(1.6)), "e8_lattice").to(DEV)
+    with pytest.raises(RuntimeError):
+        forward_group([e8], [make_activations(1, 64).to(DEV)])
+    d4 = EPTQLinear.from_quantized_data(make_layer(64, 64, seed=1), TABLE, "e8_d4").to(DEV)
+    with pytest.raises(RuntimeError):
+        forward_group([d4], [make_activations(3, 64).to(DEV)])        # batch 3 is not a group batch
