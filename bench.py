@@ -9,10 +9,14 @@ so every step streams from HBM).  One step = one pass over all 224 linears at
 batch B (default 1), i.e. the quantized-linear work of one decode token.
 
   value     algorithmic GB/s with everything resident in HBM (step replayed
-            from a CUDA graph of C-ABI calls, CUDA-event timed)
-  e2e       the same GB/s through EPTQLinear.forward with the activations in
-            pinned HOST memory: H2D copy of x, 224 module calls, D2H copy of the
-            last output inside the timed region of every step
+            from a CUDA graph of C-ABI calls, CUDA-event timed).  The linears
+            have fixed, independent inputs, so the seven linears of a decoder
+            layer go into one eptq_linear_forward_group launch (--group 7);
+            `one_launch_per_linear` reports the same pass with --group 1.
+  e2e       the same GB/s through the Python module API (forward_group over
+            EPTQLinear modules) with the activations in pinned HOST memory:
+            H2D copy of x, all module calls, D2H copy of the last output inside
+            the timed region of every step
   roofline  achieved GB/s of the GEMV launches against the measured HBM peak
   cpu_baseline  the reconstruct-then-matmul CPU path (numpy port of the
             reference's dequantize_layer, torch CPU matmul) on a bounded sample
@@ -171,8 +175,7 @@ def run_gpu_arm(args):
 
     from eptq_b200 import _lib
     from eptq_b200.build import build_library
-    from eptq_b200.kernels import _make_desc
-    from eptq_b200.kernels.linear import EPTQLinear
+    from eptq_b200.kernels.linear import EPTQLinear, forward_group
     from eptq_b200.parallel import shard_layer, ROW_PARALLEL
     from eptq_b200.quantizers import E8D4Quantizer
     from eptq_b200.synthetic import LLAMA2_7B_LINEARS, make_layer
@@ -207,44 +210,48 @@ def run_gpu_arm(args):
             layers.append((name, lin))
     torch.cuda.synchronize()
 
-    # Device-resident arm: C-ABI calls captured once, replayed per step.
+    # Device-resident arm: C-ABI calls captured once, replayed per step.  The seven linears of a
+    # decoder layer have fixed, independent inputs here, so each decoder layer is one group launch
+    # (--group 7); --group 1 issues one launch per linear.
+    group = max(1, min(args.group, 32))
     xs = {n: torch.randn(B, n, device=dev).half() for n in {l.in_features for _, l in layers}}
-    ws_bytes = max(lib.eptq_workspace_bytes(l.Q.shape[0], l.Q.shape[1], B) for _, l in layers)
-    n_streams = max(1, args.streams) if world == 1 else 1
-    wss = [torch.zeros(ws_bytes, dtype=torch.uint8, device=dev) for _ in range(n_streams)]
-    ysets = [{m: torch.empty(B, m, device=dev, dtype=torch.float16) for m in {l.out_features for _, l in layers}}
-             for _ in range(n_streams)]
-    descs = [_make_desc(l.quantizer_type, l.Q, l._codebook32, l._codebook, l.g, l.h, l.O_vals, l.O_col,
-                        l.O_row_ptr, l.bias, l.S_group, l.qb_size) for _, l in layers]
+    ys = [torch.empty(B, l.out_features, device=dev, dtype=torch.float16) for _, l in layers]
+    descs = [l.descriptor() for _, l in layers]
 
-    def launch(idx, lane):
-        (name, l), d = layers[idx], descs[idx]
-        y = ysets[lane][l.out_features]
-        st = lib.eptq_linear_forward(C.byref(d), xs[l.in_features].data_ptr(), y.data_ptr(), B,
-                                     wss[lane].data_ptr(), wss[lane].numel(), torch.cuda.current_stream().cuda_stream)
-        if st != 0:
-            raise RuntimeError(lib.eptq_strerror(st).decode())
-        if l.tp_row_parallel:
-            dist.all_reduce(y)
+    def make_calls(gsize):
+        calls, need = [], 0
+        for i in range(0, len(layers), gsize):
+            n = min(gsize, len(layers) - i)
+            arr = (_lib.EptqLayer * n)(*descs[i:i + n])
+            xp = (C.c_void_p * n)(*[xs[l.in_features].data_ptr() for _, l in layers[i:i + n]])
+            yp = (C.c_void_p * n)(*[y.data_ptr() for y in ys[i:i + n]])
+            reduce_ys = [ys[i + k] for k in range(n) if layers[i + k][1].tp_row_parallel]
+            grouped = lib.eptq_group_workspace_bytes(arr, n, B) > 0 and (gsize > 1)
+            need = max(need, lib.eptq_group_workspace_bytes(arr, n, B),
+                       *[lib.eptq_workspace_bytes(l.Q.shape[0], l.Q.shape[1], B) for _, l in layers[i:i + n]])
+            calls.append((arr, n, xp, yp, reduce_ys, grouped, i))
+        return calls, need
 
-    branch_streams = [torch.cuda.Stream(device=dev) for _ in range(n_streams)] if n_streams > 1 else []
+    calls, ws_bytes = make_calls(group)
+    calls1, ws_bytes1 = make_calls(1)
+    ws = torch.zeros(max(ws_bytes, ws_bytes1), dtype=torch.uint8, device=dev)
 
-    def step_abi(n_lanes=None):
-        """One pass over every linear.  The calls are independent (fixed inputs, separate outputs), so
-        with more than one lane they are spread round-robin over that many streams, each with its own
-        scratch and outputs; calls on one stream stay ordered."""
-        n_lanes = n_streams if n_lanes is None else n_lanes
-        if n_lanes == 1:
-            for idx in range(len(layers)):
-                launch(idx, 0)
-            return
-        main = torch.cuda.current_stream()
-        for k in range(n_lanes):
-            branch_streams[k].wait_stream(main)
-            with torch.cuda.stream(branch_streams[k]):
-                for idx in range(k, len(layers), n_lanes):
-                    launch(idx, k)
-            main.wait_stream(branch_streams[k])
+    def step_abi(call_list=None):
+        stream = torch.cuda.current_stream().cuda_stream
+        for arr, n, xp, yp, reduce_ys, grouped, i0 in (calls if call_list is None else call_list):
+            if grouped:
+                st = lib.eptq_linear_forward_group(arr, n, xp, yp, B, ws.data_ptr(), ws.numel(), stream)
+                if st != 0:
+                    raise RuntimeError(lib.eptq_strerror(st).decode())
+            else:
+                for k in range(n):
+                    l = layers[i0 + k][1]
+                    st = lib.eptq_linear_forward(C.byref(descs[i0 + k]), xs[l.in_features].data_ptr(),
+                                                 ys[i0 + k].data_ptr(), B, ws.data_ptr(), ws.numel(), stream)
+                    if st != 0:
+                        raise RuntimeError(lib.eptq_strerror(st).decode())
+            for y in reduce_ys:
+                dist.all_reduce(y)
 
     side = torch.cuda.Stream(device=dev)
     with torch.cuda.stream(side):
@@ -283,11 +290,13 @@ def run_gpu_arm(args):
 
     ms_dev, clocks = timed(graph.replay, args.steps, args.warmup)
     ms_chain = None
-    if n_streams > 1:
+    if group > 1:
         with torch.cuda.stream(side):
+            step_abi(calls1)
+            torch.cuda.synchronize()
             graph1 = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph1, stream=side):
-                step_abi(1)
+                step_abi(calls1)
         torch.cuda.synchronize()
         ms_chain, _ = timed(graph1.replay, args.steps, args.warmup)
     if clocks["samples"] < 5:
@@ -310,10 +319,16 @@ def run_gpu_arm(args):
         for n in x_dev:
             x_dev[n].copy_(x_host[n], non_blocking=True)
         y = None
-        for name, l in layers:
-            y = l(x_dev[l.in_features])
-            if l.tp_row_parallel:
-                dist.all_reduce(y)
+        for i in range(0, len(layers), group):
+            chunk = [l for _, l in layers[i:i + group]]
+            if group > 1:
+                outs = forward_group(chunk, [x_dev[l.in_features] for l in chunk])
+            else:
+                outs = [l(x_dev[l.in_features]) for l in chunk]
+            for l, o in zip(chunk, outs):
+                if l.tp_row_parallel:
+                    dist.all_reduce(o)
+            y = outs[-1]
         y_host.copy_(y, non_blocking=True)
 
     with torch.cuda.stream(side):
@@ -341,7 +356,7 @@ def run_gpu_arm(args):
     value = total_bytes / (step_ms * 1e-3) / 1e9
     e2e_value = total_bytes / (ms_e2e / args.steps * 1e-3) / 1e9
     peak, peak_kind = measured_peaks()
-    n_calls = len(layers)
+    n_calls = max(1, int(launches_per_step))
     per_launch_bytes = total_bytes / world / n_calls
     per_launch_us = step_ms * 1e3 / n_calls
     achieved = per_launch_bytes / (per_launch_us * 1e-6) / 1e9
@@ -350,9 +365,9 @@ def run_gpu_arm(args):
         "ms_per_step": step_ms, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
         "vs_baseline": None, "dtype": "f16", "data": "synthetic",
         "config": {"workload": "llama2-7b decode layer set, E8-D4 r=1.75, 0.2% critical blocks",
-                   "batch": B, "layers": n_layers, "linears_per_step": n_calls,
+                   "batch": B, "layers": n_layers, "linears_per_step": len(layers),
                    "l2_policy": "inputs larger than L2 (1.66 GB of indices per step)" if n_layers >= 8 else "reduced layer count: may be L2-resident",
-                   "streams": n_streams,
+                   "launch_granularity": f"{group} independent linears per launch" if group > 1 else "one launch per linear",
                    "parallelism": f"tp{world}" if world > 1 else "single"},
         "decode_tokens_per_s_linears_only": 1e3 / step_ms * B,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
@@ -361,10 +376,10 @@ def run_gpu_arm(args):
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": ms_e2e / args.steps},
         "gpu_launches": int(launches_per_step * args.steps),
-        "single_stream": None if ms_chain is None else {
+        "one_launch_per_linear": None if ms_chain is None else {
             "value": total_bytes / (ms_chain / args.steps * 1e-3) / 1e9, "unit": UNIT,
             "ms_per_step": ms_chain / args.steps,
-            "note": "the same pass with every call ordered on one stream (each launch waits for the previous one)"},
+            "note": "the same pass through eptq_linear_forward, one launch per linear, each ordered after the previous"},
         "clocks": clocks,
     }
     if not args.no_cpu_baseline and world == 1:
@@ -383,8 +398,8 @@ def main():
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--layers", type=int, default=N_LAYERS)
-    ap.add_argument("--streams", type=int, default=1,
-                    help="independent linears are spread over this many streams (1 = strictly ordered)")
+    ap.add_argument("--group", type=int, default=7,
+                    help="independent linears per launch (7 = one decoder layer's linears, 1 = one launch each)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.warmup < 3:

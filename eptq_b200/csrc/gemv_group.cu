@@ -283,14 +283,6 @@ struct StripIter {
         rt = static_cast<int>(local / p.L[l].ns);
         strip = static_cast<int>(local - static_cast<long long>(rt) * p.L[l].ns);
     }
-    // returns true when the step crossed into a new row tile (or layer)
-    __device__ __forceinline__ bool advance(const GroupArgs& p) {
-        ++s;
-        if (++strip < p.L[l].ns) return false;
-        strip = 0;
-        if (++rt == p.L[l].row_tiles) { rt = 0; ++l; }
-        return true;
-    }
 };
 
 __global__ void __launch_bounds__(kGroupThreads, 1) gemv_group_kernel(const __grid_constant__ GroupArgs p) {
@@ -332,60 +324,77 @@ __global__ void __launch_bounds__(kGroupThreads, 1) gemv_group_kernel(const __gr
     // ---- main warps
     const int g = lane >> 2, t = lane & 3;
     const int gw = blockIdx.x * kMainWarps + warp;
-    const long long s_begin = (static_cast<long long>(gw) * p.W) / p.nw;
-    const long long s_end = (static_cast<long long>(gw + 1) * p.W) / p.nw;
+    const long long s_begin = gw < p.nw ? (static_cast<long long>(gw) * p.W) / p.nw : p.W;
+    const long long s_end = gw < p.nw ? (static_cast<long long>(gw + 1) * p.W) / p.nw : p.W;
+    const int n_total = static_cast<int>(s_end - s_begin);
 
     unsigned* slab = reinterpret_cast<unsigned*>(smem_raw) + warp * 128;     // [parity][batch][32] words
     slab[lane] = 0u; slab[32 + lane] = 0u; slab[64 + lane] = 0u; slab[96 + lane] = 0u;
 
-    // Q ring: rows g and g+8 of the tile, 8 columns per lane.  h/x ring: column `lane` of the strip.
+    // Cursor over the strip sequence: which row tile, how many strips are left in it, and this
+    // lane's addresses (Q rows g and g+8 at its 8 columns; h and x at column `lane` of the strip).
+    struct Cursor {
+        int l, rt, left, N;
+        const int16_t *pa, *pb;
+        const __half *ph, *px;
+    };
+    auto place = [&](Cursor& c, int strip) {
+        const GroupLayer& L = p.L[c.l];
+        const int ra = min(c.rt * 16 + g, L.M - 1), rb = min(c.rt * 16 + g + 8, L.M - 1);
+        c.N = L.N;
+        c.left = L.ns - strip;
+        c.pa = L.Q + static_cast<size_t>(ra) * L.N + strip * 32 + 8 * t;
+        c.pb = L.Q + static_cast<size_t>(rb) * L.N + strip * 32 + 8 * t;
+        c.ph = L.h + strip * 32 + lane;
+        c.px = L.x + strip * 32 + lane;
+    };
+    auto step = [&](Cursor& c) {
+        c.pa += 32; c.pb += 32; c.ph += 32; c.px += 32;
+        if (--c.left == 0) {
+            if (++c.rt == p.L[c.l].row_tiles) { c.rt = 0; ++c.l; }
+            if (c.l < p.n_layers) place(c, 0);
+        }
+    };
+
+    Cursor pf;                                           // prefetch position
+    {
+        StripIter it;
+        it.seek(p, n_total > 0 ? s_begin : 0);
+        pf.l = it.l; pf.rt = it.rt;
+        place(pf, it.strip);
+    }
+    const int cur_l0 = pf.l, cur_rt0 = pf.rt, cur_left0 = pf.left;
+    Cursor xfirst = pf;                                  // for the x loads that must follow the dependency wait
+
     uint4 qa[kRing], qb[kRing];
     __half hr[kRing], xr0[kRing], xr1[kRing];
-    StripIter pf;                                      // prefetch position
-    pf.seek(p, s_begin < p.W ? s_begin : 0);
-    auto q_ptrs = [&](const StripIter& it, const int16_t*& pa, const int16_t*& pb) {
-        const GroupLayer& L = p.L[it.l];
-        const int ra = min(it.rt * 16 + g, L.M - 1), rb = min(it.rt * 16 + g + 8, L.M - 1);
-        const int col = it.strip * 32 + 8 * t;
-        pa = L.Q + static_cast<size_t>(ra) * L.N + col;
-        pb = L.Q + static_cast<size_t>(rb) * L.N + col;
-    };
 #pragma unroll
     for (int i = 0; i < kRing; ++i) {
         qa[i] = make_uint4(0, 0, 0, 0); qb[i] = make_uint4(0, 0, 0, 0);
         hr[i] = __ushort_as_half(0); xr0[i] = __ushort_as_half(0); xr1[i] = __ushort_as_half(0);
     }
-    {
-        StripIter it = pf;
+    int pf_todo = n_total;
 #pragma unroll
-        for (int i = 0; i < kRing; ++i) {
-            if (it.s < s_end) {
-                const int16_t *pa, *pb;
-                q_ptrs(it, pa, pb);
-                qa[i] = ldg_stream(pa);
-                qb[i] = ldg_stream(pb);
-                hr[i] = __ldg(p.L[it.l].h + it.strip * 32 + lane);
-                it.advance(p);
-            }
+    for (int i = 0; i < kRing; ++i) {
+        if (pf_todo > 0) {
+            qa[i] = ldg_stream(pf.pa);
+            qb[i] = ldg_stream(pf.pb);
+            hr[i] = __ldg(pf.ph);
+            step(pf);
+            --pf_todo;
         }
     }
     __syncthreads();                                   // table complete (all 16 warps reach this once)
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    {
-        StripIter it = pf;
+    if (n_total <= 0) return;
 #pragma unroll
-        for (int i = 0; i < kRing; ++i) {
-            if (it.s < s_end) {
-                const GroupLayer& L = p.L[it.l];
-                xr0[i] = __ldg(L.x + it.strip * 32 + lane);
-                if (p.B > 1) xr1[i] = __ldg(L.x + L.N + it.strip * 32 + lane);
-                it.advance(p);
-            }
+    for (int i = 0; i < kRing; ++i) {
+        if (i < n_total) {
+            xr0[i] = __ldg(xfirst.px);
+            if (p.B > 1) xr1[i] = __ldg(xfirst.px + xfirst.N);
+            step(xfirst);
         }
-#pragma unroll
-        for (int i = 0; i < kRing; ++i) if (pf.s < s_end) pf.advance(p);     // pf now points kRing strips ahead
     }
-    if (s_begin >= s_end) return;
 
     const unsigned lane_tab = 8u * (lane & 15) | kTableAddr;
     // B column g = (batch g>>2, piece (g>>1)&1, dd' = g&1): the piece goes to the low or high half.
@@ -393,9 +402,9 @@ __global__ void __launch_bounds__(kGroupThreads, 1) gemv_group_kernel(const __gr
     const unsigned sel = (g & 1) ? ((((pbyte + 1) << 12) | (pbyte << 8)) | 0x0044u) : (0x4400u | ((pbyte + 1) << 4) | pbyte);
     const unsigned* my_slab = slab + (g >> 2) * 32 + 8 * t;
 
-    StripIter cur;
-    cur.seek(p, s_begin);
-    Affine aff = load_affine(p.L[cur.l], cur.rt, lane);
+    int cl = cur_l0, crt = cur_rt0, cleft = cur_left0;   // compute position: layer, row tile, strips left in it
+    float cscale = p.L[cl].x_scale;
+    int todo = n_total;
     int par = 0;
     float acc[2][2][4];                                // [row group g / g+8][half i / j][dims]
 #pragma unroll
@@ -407,6 +416,7 @@ __global__ void __launch_bounds__(kGroupThreads, 1) gemv_group_kernel(const __gr
 
     auto flush = [&](int l, int rt) {
         const GroupLayer& L = p.L[l];
+        const Affine aff = load_affine(L, rt, lane);   // in flight while the ticket travels
         int first_warp;
         const int n_main = tile_contributors(p, L, rt, first_warp);
         const float inv = L.x_inv_scale;
@@ -431,23 +441,20 @@ __global__ void __launch_bounds__(kGroupThreads, 1) gemv_group_kernel(const __gr
 
 #define EPTQ_GROUP_STEP(I)                                                                                   \
     {                                                                                                        \
-        if (cur.s >= s_end) break;                                                                           \
-        const GroupLayer& L = p.L[cur.l];                                                                    \
+        if (todo == 0) break;                                                                                \
         const uint4 ca = qa[I], cb = qb[I];                                                                  \
-        const float hx = __half2float(hr[I]) * L.x_scale;                                                    \
+        const float hx = __half2float(hr[I]) * cscale;                                                       \
         unsigned* wslab = slab + par * 64;                                                                   \
         wslab[lane] = split_pieces(__half2float(xr0[I]) * hx);                                               \
         if (p.B > 1) wslab[32 + lane] = split_pieces(__half2float(xr1[I]) * hx);                             \
-        if (pf.s < s_end) {                                                                                  \
-            const int16_t *pa, *pb;                                                                          \
-            q_ptrs(pf, pa, pb);                                                                              \
-            qa[I] = ldg_stream(pa);                                                                          \
-            qb[I] = ldg_stream(pb);                                                                          \
-            const GroupLayer& PL = p.L[pf.l];                                                                \
-            hr[I] = __ldg(PL.h + pf.strip * 32 + lane);                                                      \
-            xr0[I] = __ldg(PL.x + pf.strip * 32 + lane);                                                     \
-            if (p.B > 1) xr1[I] = __ldg(PL.x + PL.N + pf.strip * 32 + lane);                                 \
-            pf.advance(p);                                                                                   \
+        if (pf_todo > 0) {                                                                                   \
+            qa[I] = ldg_stream(pf.pa);                                                                       \
+            qb[I] = ldg_stream(pf.pb);                                                                       \
+            hr[I] = __ldg(pf.ph);                                                                            \
+            xr0[I] = __ldg(pf.px);                                                                           \
+            if (p.B > 1) xr1[I] = __ldg(pf.px + pf.N);                                                       \
+            step(pf);                                                                                        \
+            --pf_todo;                                                                                       \
         }                                                                                                    \
         __syncwarp();                                                                                        \
         const uint4 w0 = *reinterpret_cast<const uint4*>(my_slab + par * 64);                                \
@@ -471,11 +478,13 @@ __global__ void __launch_bounds__(kGroupThreads, 1) gemv_group_kernel(const __gr
             mma_f16(acc[1][0], bi0, bi1, b0, b1);                                                            \
             mma_f16(acc[1][1], bj0, bj1, b0, b1);                                                            \
         }                                                                                                    \
-        const int l_done = cur.l, rt_done = cur.rt;                                                          \
-        const bool crossed = cur.advance(p);                                                                 \
-        if (crossed || cur.s >= s_end) {                                                                     \
-            flush(l_done, rt_done);                                                                          \
-            if (cur.s < s_end) aff = load_affine(p.L[cur.l], cur.rt, lane);                                  \
+        --todo;                                                                                              \
+        if (--cleft == 0 || todo == 0) {                                                                     \
+            flush(cl, crt);                                                                                  \
+            if (cleft == 0) {                                                                                \
+                if (++crt == p.L[cl].row_tiles) { crt = 0; ++cl; }                                           \
+                if (cl < p.n_layers) { cleft = p.L[cl].ns; cscale = p.L[cl].x_scale; }                       \
+            }                                                                                                \
         }                                                                                                    \
     }
 
@@ -529,6 +538,7 @@ bool plan_group(const EptqLayer* layers, int n, int B, int n_sms, GroupPlan& pla
         plan.corr_units += row_tiles * 4;
     }
     if (plan.W < 1 || plan.tiles > kMaxCounters) return false;
+    if (plan.nw > plan.W) plan.nw = static_cast<int>(plan.W);          // every warp range non-empty
     const long long per_warp = plan.W / plan.nw > 0 ? plan.W / plan.nw : 1;
     for (int i = 0; i < n; ++i) {
         const int ns = layers[i].N / 32;
