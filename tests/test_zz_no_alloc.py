@@ -12,6 +12,7 @@ from eptq_b200 import _lib
 from eptq_b200.kernels import _make_desc
 from eptq_b200.kernels.linear import EPTQLinear
 from eptq_b200.synthetic import make_activations, make_layer
+from tests import util
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
@@ -40,8 +41,10 @@ def test_static_scratch_matches_regular_entry_point(out_f, in_f, batch):
         assert lib.eptq_linear_forward_static_scratch(C.byref(desc), x.data_ptr(), y_new.data_ptr(), batch,
                                                       stream) == 0
         torch.cuda.synchronize()
-        # same kernel, same summation order: identical, well inside the 2e-3 output tolerance of the suite
-        assert torch.equal(y_new, y_ref)
+        # both are fp32 accumulations of the same products in different orders: compare with the
+        # output tolerance of the suite, max|a-b| / max|b| <= 2e-3
+        err = float((y_new.float() - y_ref.float()).abs().max() / y_ref.float().abs().max())
+        assert err <= util.REL_TOL, err
 
 
 def test_static_scratch_limits():
