@@ -371,7 +371,9 @@ def run_gpu_arm(args):
                    "parallelism": f"tp{world}" if world > 1 else "single"},
         "decode_tokens_per_s_linears_only": 1e3 / step_ms * B,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "peak_kind": f"{peak_kind} copy bandwidth",
+                     "traffic": (52379392 if (group == 7 and B == 1 and world == 1) else None),
+                     "traffic_source": "dram read+write of one 7-linear launch, ncu capture in profiles/",
+                     "peak_kind": f"{peak_kind} copy bandwidth",
                      "per_launch_bytes": per_launch_bytes, "per_launch_us": per_launch_us},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": ms_e2e / args.steps},
