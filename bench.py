@@ -300,15 +300,20 @@ def run_gpu_arm(args):
         torch.cuda.synchronize()
         ms_chain, _ = timed(graph1.replay, args.steps, args.warmup)
     if clocks["samples"] < 5:
-        # the timed region is shorter than the sampling period: keep the same load running for ~1.5 s
+        # The timed region is shorter than the sampling period: keep the same load running for about
+        # 1.5 s.  The replay count is derived from the rank-agreed step time, so that every rank
+        # issues the same number of collectives.
+        extra = max(20, min(20000, int(1500.0 / max(ms_dev / args.steps, 1e-3))))
         with ClockSampler(local) as cs:
-            t_end = time.perf_counter() + 1.5
-            while time.perf_counter() < t_end:
-                for _ in range(20):
-                    graph.replay()
-                torch.cuda.synchronize()
+            for i in range(extra):
+                graph.replay()
+                if i % 50 == 49:
+                    torch.cuda.synchronize()
+            torch.cuda.synchronize()
         clocks = cs.summary()
-        clocks["note"] = "sampled while replaying the timed step for 1.5 s right after the timed region"
+        clocks["note"] = f"sampled while replaying the timed step {extra} more times right after the timed region"
+    if world > 1:
+        dist.barrier()
 
     # End-to-end arm: public module API, activations start and results end in pinned host memory.
     x_host = {n: torch.randn(B, n).half().pin_memory() for n in xs}
@@ -347,9 +352,11 @@ def run_gpu_arm(args):
     h2d = sum(v.numel() * 2 for v in x_host.values())
     d2h = y_host.numel() * 2
 
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
+        dist.destroy_process_group()
         return
 
     step_ms = ms_dev / args.steps
