@@ -356,8 +356,10 @@ def run_gpu_arm(args):
         dist.barrier()
         torch.cuda.synchronize()
     if rank != 0:
-        dist.destroy_process_group()
-        return
+        # CUDA graphs that captured NCCL kernels are still alive; tearing the communicator down under
+        # them can block, so worker ranks leave without the teardown.
+        sys.stdout.flush()
+        os._exit(0)
 
     step_ms = ms_dev / args.steps
     value = total_bytes / (step_ms * 1e-3) / 1e9
@@ -396,7 +398,8 @@ def run_gpu_arm(args):
         line["cpu_baseline"] = {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")}
     print(json.dumps(line))
     if world > 1:
-        dist.destroy_process_group()
+        sys.stdout.flush()
+        os._exit(0)
 
 
 def main():
