@@ -51,3 +51,58 @@ def make_activations(batch: int, in_features: int, seed: int = 43, device: str =
     gen = torch.Generator(device=torch.device(device))
     gen.manual_seed(seed)
     return torch.randn((batch, in_features), generator=gen, device=device).to(torch.float16)
+
+
+def write_quantized_dir(path, hf_config, quantizer, quantizer_type: str, seed: int = 42, outlier_frac: float = 0.002,
+                        dtype=torch.float16, init_std: float = 0.02):
+    """Write a random-init model in the layout the reference's quantizer produces (quantize.py:36-127):
+    config.json, quant_config.json, quantizer.pt, non_quantized_params.pt, layer_<i>/<linear>.pt and
+    layer_<i>/non_quantized.pt.  Linears are synthetic layers (make_layer); norms are ones, embeddings
+    and lm_head are N(0, init_std).  Returns {(layer index, linear name): QuantizedLayerData}."""
+    import json
+    from pathlib import Path
+
+    from transformers import AutoModelForCausalLM
+
+    from .kernels.patch import _parameters_on_meta, decoder_layers, linear_layers
+
+    path = Path(path)
+    path.mkdir(parents=True, exist_ok=True)
+    hf_config.save_pretrained(path)
+    (path / "quant_config.json").write_text(json.dumps({"quantizer_type": quantizer_type, "model_name": ""}))
+    raw = quantizer._raw_points if quantizer_type == "e8_lattice" else quantizer._raw_codes
+    torch.save({"quantizer_type": quantizer_type, "raw_codes": raw.float().cpu(), "radius": quantizer._radius,
+                "warp_alpha": 1.0}, path / "quantizer.pt")
+    with _parameters_on_meta():
+        model = AutoModelForCausalLM.from_config(hf_config, dtype=dtype)
+    gen = torch.Generator().manual_seed(seed)
+    layers = decoder_layers(model)
+    out = {}
+    layer_param_names = set()
+    for lid, layer in enumerate(layers):
+        ldir = path / f"layer_{lid}"
+        ldir.mkdir(exist_ok=True)
+        for k, (name, lin) in enumerate(linear_layers(layer).items()):
+            qd = make_layer(lin.out_features, lin.in_features, seed=seed + 1000 * lid + k, outlier_frac=outlier_frac,
+                            bias=lin.bias is not None, scale_sigma=0.05)
+            qd.g = (qd.g.float() * (init_std * 1.5)).to(torch.float16)        # keep activations O(1) through the stack
+            qd.save(ldir / f"{name}.pt")
+            out[(lid, name)] = qd
+        norms = {}
+        for name, module in layer.named_modules():
+            if "norm" in name.lower():
+                for pn, p in module.named_parameters(recurse=False):
+                    full = f"{name}.{pn}" if name else pn
+                    norms[full] = torch.zeros(p.shape, dtype=dtype) if pn == "bias" else torch.ones(p.shape, dtype=dtype)
+        torch.save(norms, ldir / "non_quantized.pt")
+    layer_ids = {id(p) for layer in layers for p in layer.parameters()}
+    glob = {}
+    for name, p in model.named_parameters():
+        if id(p) in layer_ids:
+            continue
+        if "norm" in name.lower():
+            glob[name] = torch.zeros(p.shape, dtype=dtype) if name.endswith("bias") else torch.ones(p.shape, dtype=dtype)
+        else:
+            glob[name] = (torch.randn(p.shape, generator=gen) * init_std).to(dtype)
+    torch.save(glob, path / "non_quantized_params.pt")
+    return out
