@@ -21,7 +21,10 @@ from typing import Optional
 import torch
 import torch.nn as nn
 
-from . import _make_desc, dequantize_layer, linear_forward, linear_forward_group
+import ctypes as C
+
+from .. import _lib
+from . import _make_desc, dequantize_layer, linear_forward, linear_forward_group, workspace_for
 
 MARKER = 32767     # int16 value that marks a critical block (index 65535 - 32768)
 
@@ -86,9 +89,11 @@ class EPTQLinear(nn.Module):
         # Shared between layers, therefore plain attributes, not buffers.
         self._codebook = codebook
         self._codebook32 = codebook32
+        self._desc = None            # cached C-ABI descriptor, dropped whenever the buffers may have moved
 
     def _apply(self, fn, *args, **kwargs):
         super()._apply(fn, *args, **kwargs)
+        self._desc = None
         self._codebook = self._move_shared(self._codebook, fn)
         if self._codebook32 is not None:
             moved = self._move_shared(self._codebook32, fn)
@@ -147,12 +152,38 @@ class EPTQLinear(nn.Module):
             x2 = x2.half()
         if not x2.is_contiguous():
             x2 = x2.contiguous()
-        y = linear_forward(x2, self.Q, self._codebook, self._codebook32, self.g, self.h,
-                           self.O_vals, self.O_col, self.O_row_ptr, self.bias, self.S_group,
-                           self.quantizer_type, self.qb_size)
+        if torch.compiler.is_compiling():
+            # traced: go through the registered custom op (one graph node, has a fake implementation)
+            y = linear_forward(x2, self.Q, self._codebook, self._codebook32, self.g, self.h,
+                               self.O_vals, self.O_col, self.O_row_ptr, self.bias, self.S_group,
+                               self.quantizer_type, self.qb_size)
+        else:
+            y = self._forward_direct(x2)
         if out_dtype != torch.float16:
             y = y.to(out_dtype)
         return y.reshape(*lead, self.out_features)
+
+    def _forward_direct(self, x2: torch.Tensor) -> torch.Tensor:
+        """Eager path: cached descriptor, one ctypes call, no dispatcher in between."""
+        lib = _lib.load()
+        d = self._desc
+        if d is None or d.Q != self.Q.data_ptr() or d.h != self.h.data_ptr() or d.g != self.g.data_ptr():
+            d = self._desc = self.descriptor()
+        B = x2.shape[0]
+        y = torch.empty((B, self.out_features), dtype=torch.float16, device=x2.device)
+        if B == 0:
+            return y
+        ws = workspace_for(x2.device, lib.eptq_workspace_bytes(self.Q.shape[0], self.Q.shape[1], B))
+        if x2.device.index is not None and x2.device.index != torch.cuda.current_device():
+            with torch.cuda.device(x2.device):
+                st = lib.eptq_linear_forward(C.byref(self._desc), x2.data_ptr(), y.data_ptr(), B, ws.data_ptr(),
+                                             ws.numel(), torch.cuda.current_stream(x2.device).cuda_stream)
+        else:
+            st = lib.eptq_linear_forward(C.byref(self._desc), x2.data_ptr(), y.data_ptr(), B, ws.data_ptr(),
+                                         ws.numel(), torch.cuda.current_stream(x2.device).cuda_stream)
+        if st != 0:
+            _lib.check(st, "eptq linear forward")
+        return y
 
     def dequantize(self) -> torch.Tensor:
         """fp16 (out, in) weight reconstructed on the GPU, bit-identical to the
