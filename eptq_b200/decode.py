@@ -15,6 +15,10 @@ def decode(model, input_ids: torch.Tensor, max_new_tokens: int, top_k: int = 0,
            temperature: float = 1.0) -> Tuple[torch.Tensor, Dict[str, float]]:
     """Returns (generated ids (batch, max_new_tokens), {"prefill_s", "decode_s", "tokens_per_s"})."""
     device = input_ids.device
+    if device.type == "cuda":
+        # cuDNN attention re-plans for every new key length (about 10 ms per call on B200 with this
+        # PyTorch), which would swamp a per-token loop; the flash / memory-efficient kernels do not.
+        torch.backends.cuda.enable_cudnn_sdp(False)
     sync = torch.cuda.synchronize if device.type == "cuda" else (lambda: None)
     sync()
     t0 = time.perf_counter()
