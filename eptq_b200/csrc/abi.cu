@@ -19,6 +19,8 @@ size_t mma_workspace_bytes(int M, int N, int B);
 int launch_gemv_mma(const EptqLayer& L, const uint16_t* x, uint16_t* y, int B,
                     void* workspace, size_t workspace_bytes, cudaStream_t stream);
 
+bool gemm_supported(const EptqLayer& L, int T);
+int launch_gemm_tcgen05(const EptqLayer& L, const uint16_t* x, uint16_t* y, int T, int* status, cudaStream_t stream);
 bool group_gemv_supported(const EptqLayer* layers, int n, int B);
 size_t group_workspace_bytes(const EptqLayer* layers, int n, int B, int n_sms);
 int launch_gemv_group(const EptqLayer* layers, int n, const uint16_t* const* xs, uint16_t* const* ys, int B,
@@ -55,6 +57,11 @@ int forward_checked(const EptqLayer& L, const uint16_t* x, uint16_t* y, int B,
     if (!aligned16(L.table16)) return EPTQ_ERR_ALIGN;
     if ((L.N % 8) == 0 && !aligned16(x)) return EPTQ_ERR_ALIGN;
     if (workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return EPTQ_ERR_ALIGN;
+    if (B > kGemmMinBatch && gemm_supported(L, B) && aligned16(y) && (L.bias == nullptr || aligned16(L.bias)) &&
+        workspace != nullptr && workspace_bytes >= kCounterBytes) {
+        int* status = reinterpret_cast<int*>(workspace) + (kMaxCounters - 1);     // last counter word: never a tile
+        return launch_gemm_tcgen05(L, x, y, B, status, static_cast<cudaStream_t>(stream));
+    }
     if (group_gemv_supported(&L, 1, B) && aligned16(y)) {
         const uint16_t* xs[1] = {x};
         uint16_t* ys[1] = {y};

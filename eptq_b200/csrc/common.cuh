@@ -30,6 +30,9 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 //   [kCounterBytes, ...)            float partial sums [split][batch][8*M]
 constexpr size_t kCounterBytes = 4096;
 constexpr int kMaxCounters = static_cast<int>(kCounterBytes / sizeof(unsigned));
+constexpr int kGemmMinBatch = 16;           // batches above this run on the tensor-core GEMM
+// The last counter word is the GEMM's status word (EPTQ_ERR_TIMEOUT if a bounded wait ran out), so
+// GEMV plans may use at most kMaxCounters - 1 counters.
 
 __device__ __forceinline__ uint4 ldg128(const void* p) {
     return __ldg(reinterpret_cast<const uint4*>(p));

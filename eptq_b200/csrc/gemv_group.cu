@@ -537,7 +537,7 @@ bool plan_group(const EptqLayer* layers, int n, int B, int n_sms, GroupPlan& pla
         plan.tiles += row_tiles;
         plan.corr_units += row_tiles * 4;
     }
-    if (plan.W < 1 || plan.tiles > kMaxCounters) return false;
+    if (plan.W < 1 || plan.tiles > kMaxCounters - 1) return false;
     if (plan.nw > plan.W) plan.nw = static_cast<int>(plan.W);          // every warp range non-empty
     const long long per_warp = plan.W / plan.nw > 0 ? plan.W / plan.nw : 1;
     for (int i = 0; i < n; ++i) {

@@ -601,13 +601,13 @@ int mma_plan(int M, int N, int* wc_out, int* col_blocks, int* groups, int* corr_
 size_t mma_workspace_bytes(int M, int N, int B) {
     int wc, cb, gy, cg;
     const int row_tiles = mma_plan(M, N, &wc, &cb, &gy, &cg);
-    if (row_tiles > kMaxCounters) return 0;
+    if (row_tiles >= kMaxCounters) return 0;
     return kCounterBytes + static_cast<size_t>(row_tiles) * (cb + 1) * B * 128 * sizeof(float);
 }
 
 bool mma_gemv_supported(const EptqLayer& L, int B) {
     return L.quantizer == EPTQ_E8D4 && L.table16 != nullptr && L.S_group == nullptr && B >= 1 && B <= kMaxBatch &&
-           (L.N % 32) == 0 && (L.M + 15) / 16 <= kMaxCounters && aligned16(L.Q) && aligned16(L.table16);
+           (L.N % 32) == 0 && (L.M + 15) / 16 < kMaxCounters && aligned16(L.Q) && aligned16(L.table16);
 }
 
 int launch_gemv_mma(const EptqLayer& L, const uint16_t* x, uint16_t* y, int B,

@@ -255,7 +255,7 @@ int simt_plan_splits(int M, int N, int B, int* cols_per_split) {
     const int max_by_cols = (N + 511) / 512;
     if (splits > max_by_cols) splits = max_by_cols;
     if (splits > kMaxSplits) splits = kMaxSplits;
-    if (splits < 1 || denom > kMaxCounters) splits = 1;
+    if (splits < 1 || denom >= kMaxCounters) splits = 1;
     int cols = (N + splits - 1) / splits;
     cols = (cols + 7) & ~7;
     splits = (N + cols - 1) / cols;
