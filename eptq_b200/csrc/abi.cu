@@ -21,6 +21,8 @@ int launch_gemv_mma(const EptqLayer& L, const uint16_t* x, uint16_t* y, int B,
 
 bool gemm_supported(const EptqLayer& L, int T);
 int launch_gemm_tcgen05(const EptqLayer& L, const uint16_t* x, uint16_t* y, int T, int* status, cudaStream_t stream);
+bool gemm_ws_supported(const EptqLayer& L, const void* x, int T);
+int launch_gemm_tcgen05_ws(const EptqLayer& L, const uint16_t* x, uint16_t* y, int T, int* status, cudaStream_t stream);
 bool group_gemv_supported(const EptqLayer* layers, int n, int B);
 size_t group_workspace_bytes(const EptqLayer* layers, int n, int B, int n_sms);
 int launch_gemv_group(const EptqLayer* layers, int n, const uint16_t* const* xs, uint16_t* const* ys, int B,
@@ -60,6 +62,8 @@ int forward_checked(const EptqLayer& L, const uint16_t* x, uint16_t* y, int B,
     if (B > kGemmMinBatch && gemm_supported(L, B) && aligned16(y) && (L.bias == nullptr || aligned16(L.bias)) &&
         workspace != nullptr && workspace_bytes >= kCounterBytes) {
         int* status = reinterpret_cast<int*>(workspace) + (kMaxCounters - 1);     // last counter word: never a tile
+        if (gemm_ws_supported(L, x, B))
+            return launch_gemm_tcgen05_ws(L, x, y, B, status, static_cast<cudaStream_t>(stream));
         return launch_gemm_tcgen05(L, x, y, B, status, static_cast<cudaStream_t>(stream));
     }
     if (group_gemv_supported(&L, 1, B) && aligned16(y)) {

@@ -1,0 +1,434 @@
+// Prefill dequantise + GEMM, warp-specialised and pipelined (tcgen05 + TMEM + TMA), sm_100a.
+//
+// Same arithmetic as gemm_tcgen05.cu (bit-exact fp16 weight tiles, fp32
+// accumulation in tensor memory), organised so that the tensor cores are not
+// left waiting for the reconstruction:
+//
+//   tile      TM*128 tokens x 128 outputs per block (TM = 1, 2 or 4 accumulators of
+//             128 TMEM columns each).  Reconstructing a weight tile costs ~35
+//             instructions per index and is repeated for every token tile, so the
+//             token tile is made as tall as tensor memory allows (512 tokens).
+//   warp 0    TMA producer: per 64-wide K chunk, TM bulk-tensor loads of a
+//             128-token x 64-column activation box (128-byte swizzle) into the
+//             stage's A tiles, completion counted on the stage's `full` barrier.
+//   warp 1    MMA issuer: waits for `full`, issues TM x 4 tcgen05.mma
+//             (M=128, N=128, K=16) and commits them to the stage's `empty`
+//             barrier; the last commit also signals `acc_ready`.
+//   warps 2-9 reconstruct the stage's 128-output x 64-column weight tile into the
+//             no-swizzle core-matrix layout (4 indices per thread), make it visible
+//             to the async proxy and arrive on `full`; afterwards they are the
+//             epilogue: tcgen05.ld, bias, fp16, 256 contiguous bytes per token.
+//
+// No cluster, no multicast; every wait is bounded and ends in a status word.
+//
+// Reference counterpart: e8d4_wmma_v2_kernel (csrc/eptq_kernels.cu:309-461).
+
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include "common.cuh"
+
+namespace eptq {
+
+struct GemmWsArgs {
+    EptqLayer L;
+    __half* y;             // (T, 8M)
+    int* status;
+    int T;
+};
+
+namespace {
+
+constexpr int kStages = 2;
+constexpr int kChunkK = 64;
+constexpr int kTileOuts = 128;
+constexpr int kATileBytes = 128 * kChunkK * 2;          // 16 KB: 128 tokens x 64 columns, 128-byte rows
+constexpr int kBTileBytes = 128 * kChunkK * 2;          // 16 KB: 128 outputs x 64 columns, core matrices
+constexpr unsigned kB_LBO = 128;                        // B tile: bytes between core matrices adjacent in K
+constexpr unsigned kB_SBO = (kChunkK / 8) * 128;        // B tile: bytes between 8-row groups
+constexpr int kProducerWarps = 8;
+constexpr int kWsThreads = (2 + kProducerWarps) * 32;   // 320
+constexpr int kSpinLimit = 20000000;
+
+__host__ __device__ constexpr int ws_smem_bytes(int tm) { return kStages * (tm * kATileBytes + kBTileBytes) + 1024; }
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) {
+    return static_cast<unsigned>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(unsigned bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(unsigned bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
+    for (int it = 0; it < kSpinLimit; ++it) {
+        unsigned done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
+// A tile: K-major, 128-byte swizzle (what the bulk-tensor load writes): 8-row groups 1024 B apart.
+__device__ __forceinline__ uint64_t desc_a_sw128(unsigned addr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((addr & 0x3FFFFu) >> 4);
+    d |= static_cast<uint64_t>(1) << 16;                  // leading byte offset: unused with swizzled K-major
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;                  // SWIZZLE_128B
+    return d;
+}
+// B tile: K-major, no swizzle, core matrices of 8 rows x 16 bytes.
+__device__ __forceinline__ uint64_t desc_b_plain(unsigned addr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((addr & 0x3FFFFu) >> 4);
+    d |= static_cast<uint64_t>(kB_LBO >> 4) << 16;
+    d |= static_cast<uint64_t>(kB_SBO >> 4) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    return d;
+}
+constexpr uint32_t kInstrDesc = (1u << 4) | ((kTileOuts >> 3) << 17) | ((128u >> 4) << 24);
+
+__device__ __forceinline__ int marker_rank(const int* __restrict__ O_col, int lo, int hi, int n) {
+    while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (__ldg(O_col + mid) < n) lo = mid + 1; else hi = mid;
+    }
+    return lo;
+}
+
+// W16[8m .. 8m+7, n], bit-for-bit the reference's reconstruction (see gemm_tcgen05.cu).
+template <int KIND>
+__device__ __forceinline__ void reconstruct8(const EptqLayer& L, const float4* tab_s, int m, int n, unsigned q16,
+                                             const float (&gk)[8], float hn, float sg, __half (&out)[8]) {
+    const unsigned idx = q16 ^ 0x8000u;
+    float v[8];
+    if (idx == kMarkerIndex) {
+        const int lo = __ldg(L.O_row_ptr + m), hi = __ldg(L.O_row_ptr + m + 1);
+        const int r = marker_rank(L.O_col, lo, hi, n);
+        unpack8(ldg128(reinterpret_cast<const __half*>(L.O_vals) + static_cast<size_t>(r) * 8), v);
+    } else {
+        float4 a, b;
+        if (KIND == EPTQ_E8) {
+            const float4* t = reinterpret_cast<const float4*>(L.table32 + static_cast<size_t>(idx) * 8);
+            a = __ldg(t); b = __ldg(t + 1);
+        } else {
+            const unsigned ct = (idx >> 14) & 3u;
+            a = tab_s[ct * 128 + ((idx >> 7) & 127u)];
+            b = tab_s[ct * 128 + (idx & 127u)];
+        }
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+        if (L.S_group != nullptr) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) v[k] = __fmul_rn(v[k], sg);
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) out[k] = __float2half_rn(__fmul_rn(__fmul_rn(v[k], gk[k]), hn));
+}
+
+
+template <int KIND, int TM>
+__global__ void __launch_bounds__(kWsThreads, 1)
+gemm_tcgen05_ws_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmWsArgs p) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    __shared__ __align__(16) float4 tab_s[KIND == EPTQ_E8D4 ? 512 : 1];
+    __shared__ __align__(8) unsigned long long bar_full[kStages], bar_empty[kStages], bar_acc;
+    __shared__ unsigned tmem_base_slot;
+
+    constexpr int kStageBytes = TM * kATileBytes + kBTileBytes;
+    constexpr unsigned kTmemCols = TM * 128 < 32 ? 32 : TM * 128;
+    const EptqLayer& L = p.L;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int N = L.N, out_dim = 8 * L.M;
+    const int t0 = blockIdx.y * (TM * 128);
+    const int m0 = blockIdx.x * (kTileOuts / 8);
+    const int n_chunks = (N + kChunkK - 1) / kChunkK;
+    // dynamic shared memory may start at an address that is not 1024-aligned: align by hand
+    unsigned char* tiles = smem + ((1024u - (smem_u32(smem) & 1023u)) & 1023u);
+
+    if (KIND == EPTQ_E8D4)
+        for (int i = tid; i < 512; i += kWsThreads) tab_s[i] = __ldg(reinterpret_cast<const float4*>(L.table32) + i);
+    if (tid == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(smem_u32(&bar_full[s]), 1 + kProducerWarps);
+            mbar_init(smem_u32(&bar_empty[s]), 1);
+        }
+        mbar_init(smem_u32(&bar_acc), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" :: "l"(reinterpret_cast<uint64_t>(&tmap_x)) : "memory");
+    }
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     :: "r"(smem_u32(&tmem_base_slot)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const unsigned tmem_acc = tmem_base_slot;
+    bool ok = true;
+
+    if (warp == 0) {
+        // ---------------- TMA producer
+        if (lane == 0) {
+            for (int c = 0; c < n_chunks && ok; ++c) {
+                const int s = c % kStages;
+                const unsigned phase = (c / kStages) & 1u;
+                ok = mbar_wait(smem_u32(&bar_empty[s]), phase ^ 1u);
+                if (!ok) break;
+                const unsigned full = smem_u32(&bar_full[s]);
+                mbar_arrive_expect_tx(full, TM * kATileBytes);
+#pragma unroll
+                for (int j = 0; j < TM; ++j) {
+                    const unsigned dst = smem_u32(tiles + s * kStageBytes + j * kATileBytes);
+                    asm volatile(
+                        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                        :: "r"(dst), "l"(reinterpret_cast<uint64_t>(&tmap_x)), "r"(c * kChunkK), "r"(t0 + j * 128), "r"(full)
+                        : "memory");
+                }
+            }
+            if (!ok) atomicExch(p.status, EPTQ_ERR_TIMEOUT);
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer
+        if (lane == 0) {
+            for (int c = 0; c < n_chunks && ok; ++c) {
+                const int s = c % kStages;
+                const unsigned phase = (c / kStages) & 1u;
+                ok = mbar_wait(smem_u32(&bar_full[s]), phase);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint64_t db = desc_b_plain(smem_u32(tiles + s * kStageBytes + TM * kATileBytes));
+#pragma unroll
+                for (int j = 0; j < TM; ++j) {
+                    const uint64_t da = desc_a_sw128(smem_u32(tiles + s * kStageBytes + j * kATileBytes));
+#pragma unroll
+                    for (int k = 0; k < kChunkK / 16; ++k) {
+                        const unsigned accumulate = (c > 0 || k > 0) ? 1u : 0u;
+                        asm volatile(
+                            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                            :: "r"(tmem_acc + j * 128), "l"(da + static_cast<uint64_t>((k * 32) >> 4)),
+                               "l"(db + static_cast<uint64_t>((k * 2 * kB_LBO) >> 4)), "r"(kInstrDesc), "r"(accumulate)
+                            : "memory");
+                    }
+                }
+                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                             :: "r"(smem_u32(&bar_empty[s])) : "memory");
+            }
+            if (ok)
+                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                             :: "r"(smem_u32(&bar_acc)) : "memory");
+            else
+                atomicExch(p.status, EPTQ_ERR_TIMEOUT);
+        }
+    } else {
+        // ---------------- weight-tile producers (256 threads), then epilogue
+        const int pid = tid - 64;
+        const int qrow = pid >> 4, c4 = pid & 15;
+        const int bm = m0 + qrow;
+        const bool b_valid = bm < L.M;
+        float gk[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+            gk[k] = b_valid ? __half2float(__ldg(reinterpret_cast<const __half*>(L.g) + 8 * bm + k)) : 0.f;
+        const __half* srow = (L.S_group != nullptr && b_valid)
+            ? reinterpret_cast<const __half*>(L.S_group) + static_cast<size_t>((8 * bm) / L.qb_size) * N : nullptr;
+        const unsigned b_off = qrow * kB_SBO + (c4 >> 1) * kB_LBO + (c4 & 1) * 8;
+
+        for (int c = 0; c < n_chunks && ok; ++c) {
+            const int s = c % kStages;
+            const unsigned phase = (c / kStages) & 1u;
+            const int n0 = c * kChunkK + c4 * 4;
+            // fetch this thread's 4 indices and scales before waiting for the stage
+            uint2 qv = make_uint2(0, 0), hv = make_uint2(0, 0), sv = make_uint2(0x3c003c00u, 0x3c003c00u);
+            const bool live = b_valid && n0 < N;          // N % 8 == 0, so 4 columns are in or out together
+            if (live) {
+                qv = __ldg(reinterpret_cast<const uint2*>(L.Q + static_cast<size_t>(bm) * N + n0));
+                hv = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(L.h) + n0));
+                if (srow != nullptr) sv = __ldg(reinterpret_cast<const uint2*>(srow + n0));
+            }
+            ok = mbar_wait(smem_u32(&bar_empty[s]), phase ^ 1u);
+            if (!ok) break;
+            __half blk[4][8];
+            if (live) {
+                const unsigned qw[2] = {qv.x, qv.y};
+                const float2 h01 = __half22float2(*reinterpret_cast<const __half2*>(&hv.x));
+                const float2 h23 = __half22float2(*reinterpret_cast<const __half2*>(&hv.y));
+                const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(&sv.x));
+                const float2 s23 = __half22float2(*reinterpret_cast<const __half2*>(&sv.y));
+                const float hf[4] = {h01.x, h01.y, h23.x, h23.y};
+                const float sf[4] = {s01.x, s01.y, s23.x, s23.y};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const unsigned q16 = (e & 1) ? (qw[e >> 1] >> 16) : (qw[e >> 1] & 0xffffu);
+                    reconstruct8<KIND>(L, tab_s, bm, n0 + e, q16, gk, hf[e], sf[e], blk[e]);
+                }
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) blk[e][k] = __float2half_rn(0.f);
+            }
+            unsigned char* dst = tiles + s * kStageBytes + TM * kATileBytes + b_off;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const __half2 lo = __halves2half2(blk[0][k], blk[1][k]), hi = __halves2half2(blk[2][k], blk[3][k]);
+                uint2 row;
+                row.x = *reinterpret_cast<const unsigned*>(&lo);
+                row.y = *reinterpret_cast<const unsigned*>(&hi);
+                *reinterpret_cast<uint2*>(dst + k * 16) = row;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bar_full[s]));
+        }
+        if (!ok && lane == 0) atomicExch(p.status, EPTQ_ERR_TIMEOUT);
+
+        // ---------------- epilogue
+        if (ok) ok = mbar_wait(smem_u32(&bar_acc), 0u);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (ok) {
+            const int quarter = warp & 3;                    // TMEM lanes this warp may read
+            const int half = (warp - 2) >> 2;
+            constexpr int kSub = TM >= 2 ? TM / 2 : 1;       // token sub-tiles per half
+            for (int jj = 0; jj < kSub; ++jj) {
+                const int j = (TM >= 2) ? half * kSub + jj : 0;
+                if (TM == 1 && half != 0) break;
+                const int token = t0 + j * 128 + quarter * 32 + lane;
+                const unsigned lane_addr = tmem_acc + (static_cast<unsigned>(quarter * 32) << 16) + j * 128;
+#pragma unroll
+                for (int part = 0; part < kTileOuts / 32; ++part) {
+                    unsigned r[32];
+                    asm volatile(
+                        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+                        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                        : "r"(lane_addr + part * 32) : "memory");
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (token < p.T) {
+                        const int o0 = blockIdx.x * kTileOuts + part * 32;
+                        __half* dsty = p.y + static_cast<size_t>(token) * out_dim + o0;
+#pragma unroll
+                        for (int v8 = 0; v8 < 4; ++v8) {
+                            if (o0 + v8 * 8 < out_dim) {
+                                __half2 h2[4];
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    float f0 = __uint_as_float(r[v8 * 8 + 2 * e]), f1 = __uint_as_float(r[v8 * 8 + 2 * e + 1]);
+                                    if (L.bias != nullptr) {
+                                        f0 += __half2float(__ldg(reinterpret_cast<const __half*>(L.bias) + o0 + v8 * 8 + 2 * e));
+                                        f1 += __half2float(__ldg(reinterpret_cast<const __half*>(L.bias) + o0 + v8 * 8 + 2 * e + 1));
+                                    }
+                                    h2[e] = __floats2half2_rn(f0, f1);
+                                }
+                                uint4 ov;
+                                ov.x = *reinterpret_cast<unsigned*>(&h2[0]);
+                                ov.y = *reinterpret_cast<unsigned*>(&h2[1]);
+                                ov.z = *reinterpret_cast<unsigned*>(&h2[2]);
+                                ov.w = *reinterpret_cast<unsigned*>(&h2[3]);
+                                *reinterpret_cast<uint4*>(dsty + v8 * 8) = ov;
+                            }
+                        }
+                    }
+                }
+            }
+        } else if (lane == 0) {
+            atomicExch(p.status, EPTQ_ERR_TIMEOUT);
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_acc), "r"(kTmemCols) : "memory");
+    }
+}
+
+PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() {
+    static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
+    }
+    return fn;
+}
+
+template <int KIND, int TM>
+int launch_ws(const CUtensorMap& tmap, const GemmWsArgs& a, dim3 grid, cudaStream_t stream) {
+    static bool attr_done[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return EPTQ_ERR_LAUNCH;
+    if (!attr_done[dev]) {
+        if (cudaFuncSetAttribute(gemm_tcgen05_ws_kernel<KIND, TM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 ws_smem_bytes(TM)) != cudaSuccess)
+            return EPTQ_ERR_LAUNCH;
+        attr_done[dev] = true;
+    }
+    gemm_tcgen05_ws_kernel<KIND, TM><<<grid, kWsThreads, ws_smem_bytes(TM), stream>>>(tmap, a);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return cudaPeekAtLastError() == cudaSuccess ? EPTQ_OK : EPTQ_ERR_LAUNCH;
+}
+
+template <int KIND>
+int launch_ws_tm(int tm, const CUtensorMap& tmap, const GemmWsArgs& a, dim3 grid, cudaStream_t stream) {
+    switch (tm) {
+        case 1: return launch_ws<KIND, 1>(tmap, a, grid, stream);
+        case 2: return launch_ws<KIND, 2>(tmap, a, grid, stream);
+        default: return launch_ws<KIND, 4>(tmap, a, grid, stream);
+    }
+}
+
+}  // namespace
+
+// The pipelined kernel needs a tensor map over x: base 16-byte aligned, row pitch a multiple of 16 bytes.
+bool gemm_ws_supported(const EptqLayer& L, const void* x, int T) {
+    return T >= 1 && L.table32 != nullptr && (L.N % 8) == 0 && aligned16(x) && aligned16(L.Q) && aligned16(L.h) &&
+           aligned16(L.table32) && (L.n_masked == 0 || aligned16(L.O_vals)) &&
+           (L.S_group == nullptr || (L.qb_size > 0 && L.qb_size % 8 == 0 && aligned16(L.S_group))) &&
+           tensor_map_encoder() != nullptr;
+}
+
+int launch_gemm_tcgen05_ws(const EptqLayer& L, const uint16_t* x, uint16_t* y, int T, int* status, cudaStream_t stream) {
+    const int tm = T <= 128 ? 1 : (T <= 256 ? 2 : 4);
+    CUtensorMap tmap;
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(L.N), static_cast<cuuint64_t>(T)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(L.N) * 2};
+    const cuuint32_t box[2] = {kChunkK, 128};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult res = tensor_map_encoder()(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<uint16_t*>(x), dims, strides,
+                                              box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (res != CUDA_SUCCESS) return EPTQ_ERR_LAUNCH;
+    GemmWsArgs a;
+    a.L = L;
+    a.y = reinterpret_cast<__half*>(y);
+    a.status = status;
+    a.T = T;
+    const dim3 grid((8 * L.M + kTileOuts - 1) / kTileOuts, (T + tm * 128 - 1) / (tm * 128));
+    if (grid.y > 65535u) return EPTQ_ERR_SHAPE;
+    return L.quantizer == EPTQ_E8 ? launch_ws_tm<EPTQ_E8>(tm, tmap, a, grid, stream)
+                                  : launch_ws_tm<EPTQ_E8D4>(tm, tmap, a, grid, stream);
+}
+
+}  // namespace eptq
