@@ -39,18 +39,20 @@ struct GemmWsArgs {
 
 namespace {
 
-constexpr int kStages = 2;
+constexpr int kMaxStages = 3;
 constexpr int kChunkK = 64;
-constexpr int kTileOuts = 128;
 constexpr int kATileBytes = 128 * kChunkK * 2;          // 16 KB: 128 tokens x 64 columns, 128-byte rows
-constexpr int kBTileBytes = 128 * kChunkK * 2;          // 16 KB: 128 outputs x 64 columns, core matrices
+// B tile: NT outputs x 64 columns as core matrices, NT * 128 bytes
 constexpr unsigned kB_LBO = 128;                        // B tile: bytes between core matrices adjacent in K
 constexpr unsigned kB_SBO = (kChunkK / 8) * 128;        // B tile: bytes between 8-row groups
 constexpr int kProducerWarps = 8;
 constexpr int kWsThreads = (2 + kProducerWarps) * 32;   // 320
 constexpr int kSpinLimit = 20000000;
 
-__host__ __device__ constexpr int ws_smem_bytes(int tm) { return kStages * (tm * kATileBytes + kBTileBytes) + 1024; }
+// Stages that fit in 227 KB next to the 8 KB table: 2 for 512x128 tiles (80 KB each), 3 for 256x256 (64 KB each).
+__host__ __device__ constexpr int ws_stage_bytes(int tm, int nt) { return tm * kATileBytes + nt * kChunkK * 2; }
+__host__ __device__ constexpr int ws_stages(int tm, int nt) { return ws_stage_bytes(tm, nt) > 65536 ? 2 : 3; }
+__host__ __device__ constexpr int ws_smem_bytes(int tm, int nt) { return ws_stages(tm, nt) * ws_stage_bytes(tm, nt) + 1024; }
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) {
     return static_cast<unsigned>(__cvta_generic_to_shared(p));
@@ -96,7 +98,7 @@ __device__ __forceinline__ uint64_t desc_b_plain(unsigned addr) {
     d |= static_cast<uint64_t>(1) << 46;
     return d;
 }
-constexpr uint32_t kInstrDesc = (1u << 4) | ((kTileOuts >> 3) << 17) | ((128u >> 4) << 24);
+__host__ __device__ constexpr uint32_t instr_desc(int nt) { return (1u << 4) | (static_cast<uint32_t>(nt >> 3) << 17) | ((128u >> 4) << 24); }
 
 __device__ __forceinline__ int marker_rank(const int* __restrict__ O_col, int lo, int hi, int n) {
     while (lo < hi) {
@@ -137,16 +139,19 @@ __device__ __forceinline__ void reconstruct8(const EptqLayer& L, const float4* t
 }
 
 
-template <int KIND, int TM>
+template <int KIND, int TM, int NT>
 __global__ void __launch_bounds__(kWsThreads, 1)
 gemm_tcgen05_ws_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmWsArgs p) {
     extern __shared__ __align__(1024) unsigned char smem[];
     __shared__ __align__(16) float4 tab_s[KIND == EPTQ_E8D4 ? 512 : 1];
-    __shared__ __align__(8) unsigned long long bar_full[kStages], bar_empty[kStages], bar_acc;
+    __shared__ __align__(8) unsigned long long bar_full[kMaxStages], bar_empty[kMaxStages], bar_acc;
     __shared__ unsigned tmem_base_slot;
 
-    constexpr int kStageBytes = TM * kATileBytes + kBTileBytes;
-    constexpr unsigned kTmemCols = TM * 128 < 32 ? 32 : TM * 128;
+    constexpr int kStages = ws_stages(TM, NT);
+    constexpr int kStageBytes = ws_stage_bytes(TM, NT);
+    constexpr unsigned kTmemCols = TM * NT;               // 128, 256 or 512: a power of two >= 32
+    constexpr int kTileOuts = NT;
+    constexpr uint32_t kInstrDesc = instr_desc(NT);
     const EptqLayer& L = p.L;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int N = L.N, out_dim = 8 * L.M;
@@ -219,7 +224,7 @@ gemm_tcgen05_ws_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmWsA
                         asm volatile(
                             "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
                             "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                            :: "r"(tmem_acc + j * 128), "l"(da + static_cast<uint64_t>((k * 32) >> 4)),
+                            :: "r"(tmem_acc + j * NT), "l"(da + static_cast<uint64_t>((k * 32) >> 4)),
                                "l"(db + static_cast<uint64_t>((k * 2 * kB_LBO) >> 4)), "r"(kInstrDesc), "r"(accumulate)
                             : "memory");
                     }
@@ -235,8 +240,11 @@ gemm_tcgen05_ws_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmWsA
         }
     } else {
         // ---------------- weight-tile producers (256 threads), then epilogue
+        // NT/8 Q rows x 64 columns per chunk over 256 threads: CPT = 4 (NT=128) or 8 (NT=256) columns each
+        constexpr int CPT = NT / 32;
+        constexpr int kThreadsPerRow = kChunkK / CPT;
         const int pid = tid - 64;
-        const int qrow = pid >> 4, c4 = pid & 15;
+        const int qrow = pid / kThreadsPerRow, c4 = pid % kThreadsPerRow;
         const int bm = m0 + qrow;
         const bool b_valid = bm < L.M;
         float gk[8];
@@ -245,50 +253,63 @@ gemm_tcgen05_ws_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmWsA
             gk[k] = b_valid ? __half2float(__ldg(reinterpret_cast<const __half*>(L.g) + 8 * bm + k)) : 0.f;
         const __half* srow = (L.S_group != nullptr && b_valid)
             ? reinterpret_cast<const __half*>(L.S_group) + static_cast<size_t>((8 * bm) / L.qb_size) * N : nullptr;
-        const unsigned b_off = qrow * kB_SBO + (c4 >> 1) * kB_LBO + (c4 & 1) * 8;
+        const unsigned b_off = qrow * kB_SBO + ((c4 * CPT) >> 3) * kB_LBO + ((c4 * CPT) & 7) * 2;
 
+        // this thread's indices, column scales and group scales of one chunk; loaded one chunk ahead
+        struct Inputs { unsigned q[CPT / 2], h[CPT / 2], s[CPT / 2]; };
+        auto fetch = [&](int c, Inputs& in) {
+            const int n0 = c * kChunkK + c4 * CPT;
+#pragma unroll
+            for (int i = 0; i < CPT / 2; ++i) { in.q[i] = 0u; in.h[i] = 0u; in.s[i] = 0x3c003c00u; }
+            if (b_valid && n0 < N && c < n_chunks) {          // N % 8 == 0: CPT columns are in or out together
+                const unsigned* qp = reinterpret_cast<const unsigned*>(L.Q + static_cast<size_t>(bm) * N + n0);
+                const unsigned* hp = reinterpret_cast<const unsigned*>(reinterpret_cast<const __half*>(L.h) + n0);
+#pragma unroll
+                for (int i = 0; i < CPT / 2; ++i) { in.q[i] = __ldg(qp + i); in.h[i] = __ldg(hp + i); }
+                if (srow != nullptr) {
+                    const unsigned* sp = reinterpret_cast<const unsigned*>(srow + n0);
+#pragma unroll
+                    for (int i = 0; i < CPT / 2; ++i) in.s[i] = __ldg(sp + i);
+                }
+            }
+        };
+        Inputs nxt;
+        fetch(0, nxt);
         for (int c = 0; c < n_chunks && ok; ++c) {
             const int s = c % kStages;
             const unsigned phase = (c / kStages) & 1u;
-            const int n0 = c * kChunkK + c4 * 4;
-            // fetch this thread's 4 indices and scales before waiting for the stage
-            uint2 qv = make_uint2(0, 0), hv = make_uint2(0, 0), sv = make_uint2(0x3c003c00u, 0x3c003c00u);
-            const bool live = b_valid && n0 < N;          // N % 8 == 0, so 4 columns are in or out together
-            if (live) {
-                qv = __ldg(reinterpret_cast<const uint2*>(L.Q + static_cast<size_t>(bm) * N + n0));
-                hv = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(L.h) + n0));
-                if (srow != nullptr) sv = __ldg(reinterpret_cast<const uint2*>(srow + n0));
-            }
+            const int n0 = c * kChunkK + c4 * CPT;
+            const Inputs cur = nxt;
+            const bool live = b_valid && n0 < N;
+            fetch(c + 1, nxt);
             ok = mbar_wait(smem_u32(&bar_empty[s]), phase ^ 1u);
             if (!ok) break;
-            __half blk[4][8];
+            __half blk[CPT][8];
             if (live) {
-                const unsigned qw[2] = {qv.x, qv.y};
-                const float2 h01 = __half22float2(*reinterpret_cast<const __half2*>(&hv.x));
-                const float2 h23 = __half22float2(*reinterpret_cast<const __half2*>(&hv.y));
-                const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(&sv.x));
-                const float2 s23 = __half22float2(*reinterpret_cast<const __half2*>(&sv.y));
-                const float hf[4] = {h01.x, h01.y, h23.x, h23.y};
-                const float sf[4] = {s01.x, s01.y, s23.x, s23.y};
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const unsigned q16 = (e & 1) ? (qw[e >> 1] >> 16) : (qw[e >> 1] & 0xffffu);
-                    reconstruct8<KIND>(L, tab_s, bm, n0 + e, q16, gk, hf[e], sf[e], blk[e]);
+                for (int e = 0; e < CPT; ++e) {
+                    const unsigned q16 = (e & 1) ? (cur.q[e >> 1] >> 16) : (cur.q[e >> 1] & 0xffffu);
+                    const float2 h2f = __half22float2(*reinterpret_cast<const __half2*>(&cur.h[e >> 1]));
+                    const float2 s2f = __half22float2(*reinterpret_cast<const __half2*>(&cur.s[e >> 1]));
+                    reconstruct8<KIND>(L, tab_s, bm, n0 + e, q16, gk, (e & 1) ? h2f.y : h2f.x, (e & 1) ? s2f.y : s2f.x, blk[e]);
                 }
             } else {
 #pragma unroll
-                for (int e = 0; e < 4; ++e)
+                for (int e = 0; e < CPT; ++e)
 #pragma unroll
                     for (int k = 0; k < 8; ++k) blk[e][k] = __float2half_rn(0.f);
             }
             unsigned char* dst = tiles + s * kStageBytes + TM * kATileBytes + b_off;
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                const __half2 lo = __halves2half2(blk[0][k], blk[1][k]), hi = __halves2half2(blk[2][k], blk[3][k]);
-                uint2 row;
-                row.x = *reinterpret_cast<const unsigned*>(&lo);
-                row.y = *reinterpret_cast<const unsigned*>(&hi);
-                *reinterpret_cast<uint2*>(dst + k * 16) = row;
+            for (int k = 0; k < 8; ++k) {                     // row k of the core matrix: CPT consecutive columns
+                unsigned w[CPT / 2];
+#pragma unroll
+                for (int i = 0; i < CPT / 2; ++i) {
+                    const __half2 pr = __halves2half2(blk[2 * i][k], blk[2 * i + 1][k]);
+                    w[i] = *reinterpret_cast<const unsigned*>(&pr);
+                }
+                if (CPT == 8) *reinterpret_cast<uint4*>(dst + k * 16) = make_uint4(w[0], w[1], w[CPT / 2 - 2], w[CPT / 2 - 1]);
+                else *reinterpret_cast<uint2*>(dst + k * 16) = make_uint2(w[0], w[1]);
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
@@ -307,7 +328,7 @@ gemm_tcgen05_ws_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmWsA
                 const int j = (TM >= 2) ? half * kSub + jj : 0;
                 if (TM == 1 && half != 0) break;
                 const int token = t0 + j * 128 + quarter * 32 + lane;
-                const unsigned lane_addr = tmem_acc + (static_cast<unsigned>(quarter * 32) << 16) + j * 128;
+                const unsigned lane_addr = tmem_acc + (static_cast<unsigned>(quarter * 32) << 16) + j * NT;
 #pragma unroll
                 for (int part = 0; part < kTileOuts / 32; ++part) {
                     unsigned r[32];
@@ -374,28 +395,29 @@ PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() {
     return fn;
 }
 
-template <int KIND, int TM>
+template <int KIND, int TM, int NT>
 int launch_ws(const CUtensorMap& tmap, const GemmWsArgs& a, dim3 grid, cudaStream_t stream) {
     static bool attr_done[64] = {};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return EPTQ_ERR_LAUNCH;
     if (!attr_done[dev]) {
-        if (cudaFuncSetAttribute(gemm_tcgen05_ws_kernel<KIND, TM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 ws_smem_bytes(TM)) != cudaSuccess)
+        if (cudaFuncSetAttribute(gemm_tcgen05_ws_kernel<KIND, TM, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 ws_smem_bytes(TM, NT)) != cudaSuccess)
             return EPTQ_ERR_LAUNCH;
         attr_done[dev] = true;
     }
-    gemm_tcgen05_ws_kernel<KIND, TM><<<grid, kWsThreads, ws_smem_bytes(TM), stream>>>(tmap, a);
+    gemm_tcgen05_ws_kernel<KIND, TM, NT><<<grid, kWsThreads, ws_smem_bytes(TM, NT), stream>>>(tmap, a);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return cudaPeekAtLastError() == cudaSuccess ? EPTQ_OK : EPTQ_ERR_LAUNCH;
 }
 
 template <int KIND>
-int launch_ws_tm(int tm, const CUtensorMap& tmap, const GemmWsArgs& a, dim3 grid, cudaStream_t stream) {
+int launch_ws_shape(int tm, int nt, const CUtensorMap& tmap, const GemmWsArgs& a, dim3 grid, cudaStream_t stream) {
+    if (nt == 256) return tm == 1 ? launch_ws<KIND, 1, 256>(tmap, a, grid, stream) : launch_ws<KIND, 2, 256>(tmap, a, grid, stream);
     switch (tm) {
-        case 1: return launch_ws<KIND, 1>(tmap, a, grid, stream);
-        case 2: return launch_ws<KIND, 2>(tmap, a, grid, stream);
-        default: return launch_ws<KIND, 4>(tmap, a, grid, stream);
+        case 1: return launch_ws<KIND, 1, 128>(tmap, a, grid, stream);
+        case 2: return launch_ws<KIND, 2, 128>(tmap, a, grid, stream);
+        default: return launch_ws<KIND, 4, 128>(tmap, a, grid, stream);
     }
 }
 
@@ -410,7 +432,11 @@ bool gemm_ws_supported(const EptqLayer& L, const void* x, int T) {
 }
 
 int launch_gemm_tcgen05_ws(const EptqLayer& L, const uint16_t* x, uint16_t* y, int T, int* status, cudaStream_t stream) {
-    const int tm = T <= 128 ? 1 : (T <= 256 ? 2 : 4);
+    // Tile shape: 256 outputs x 256 tokens halves the activation bytes each SM has to pull from L2 per MAC
+    // (the limit of the 128-output tile); narrow layers keep 128 outputs to have enough blocks.
+    const int out_dim = 8 * L.M;
+    const int nt = (out_dim >= 2048 && T > 128) ? 256 : 128;
+    const int tm = nt == 256 ? (T <= 128 ? 1 : 2) : (T <= 128 ? 1 : (T <= 256 ? 2 : 4));
     CUtensorMap tmap;
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(L.N), static_cast<cuuint64_t>(T)};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(L.N) * 2};
@@ -425,10 +451,10 @@ int launch_gemm_tcgen05_ws(const EptqLayer& L, const uint16_t* x, uint16_t* y, i
     a.y = reinterpret_cast<__half*>(y);
     a.status = status;
     a.T = T;
-    const dim3 grid((8 * L.M + kTileOuts - 1) / kTileOuts, (T + tm * 128 - 1) / (tm * 128));
+    const dim3 grid((out_dim + nt - 1) / nt, (T + tm * 128 - 1) / (tm * 128));
     if (grid.y > 65535u) return EPTQ_ERR_SHAPE;
-    return L.quantizer == EPTQ_E8 ? launch_ws_tm<EPTQ_E8>(tm, tmap, a, grid, stream)
-                                  : launch_ws_tm<EPTQ_E8D4>(tm, tmap, a, grid, stream);
+    return L.quantizer == EPTQ_E8 ? launch_ws_shape<EPTQ_E8>(tm, nt, tmap, a, grid, stream)
+                                  : launch_ws_shape<EPTQ_E8D4>(tm, nt, tmap, a, grid, stream);
 }
 
 }  // namespace eptq

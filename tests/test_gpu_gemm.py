@@ -29,7 +29,7 @@ def timeout_flag():
 @pytest.mark.parametrize("out_f,in_f,tokens,bias,qb", [
     (128, 64, 128, False, None), (256, 256, 128, True, None), (136, 72, 130, False, None),
     (1024, 4096, 256, False, 128), (4096, 1024, 17, True, None), (264, 2752, 300, True, 8),
-    (512, 512, 2048, False, None),
+    (512, 512, 2048, False, None), (2048, 512, 300, True, None), (4104, 256, 1000, False, 8),
 ])
 def test_gemm_vs_oracle(kind, radius, out_f, in_f, tokens, bias, qb):
     qd = make_layer(out_f, in_f, seed=out_f + in_f + tokens, outlier_frac=0.004, bias=bias, qb_size=qb)
