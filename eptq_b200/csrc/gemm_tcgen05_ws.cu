@@ -42,15 +42,16 @@ namespace {
 constexpr int kMaxStages = 3;
 constexpr int kChunkK = 64;
 constexpr int kATileBytes = 128 * kChunkK * 2;          // 16 KB: 128 tokens x 64 columns, 128-byte rows
-// B tile: NT outputs x 64 columns as core matrices, NT * 128 bytes
-constexpr unsigned kB_LBO = 128;                        // B tile: bytes between core matrices adjacent in K
-constexpr unsigned kB_SBO = (kChunkK / 8) * 128;        // B tile: bytes between 8-row groups
-constexpr int kProducerWarps = 8;
-constexpr int kWsThreads = (2 + kProducerWarps) * 32;   // 320
+// B tile: core matrices (8 rows x 16 B = 128 contiguous bytes) adjacent in K are placed 144 bytes apart instead of
+// 128, so that the threads of a warp, which write the same row of neighbouring core matrices, hit different banks.
+constexpr unsigned kB_LBO = 144;                        // bytes between core matrices adjacent in K
+constexpr unsigned kB_SBO = (kChunkK / 8) * kB_LBO;     // bytes between 8-row groups (1152)
+constexpr int kProducerWarps = 16;                      // reconstruction is latency-bound: many warps
+constexpr int kWsThreads = (2 + kProducerWarps) * 32;   // 576
 constexpr int kSpinLimit = 20000000;
 
 // Stages that fit in 227 KB next to the 8 KB table: 2 for 512x128 tiles (80 KB each), 3 for 256x256 (64 KB each).
-__host__ __device__ constexpr int ws_stage_bytes(int tm, int nt) { return tm * kATileBytes + nt * kChunkK * 2; }
+__host__ __device__ constexpr int ws_stage_bytes(int tm, int nt) { return tm * kATileBytes + (nt / 8) * static_cast<int>(kB_SBO); }
 __host__ __device__ constexpr int ws_stages(int tm, int nt) { return ws_stage_bytes(tm, nt) > 65536 ? 2 : 3; }
 __host__ __device__ constexpr int ws_smem_bytes(int tm, int nt) { return ws_stages(tm, nt) * ws_stage_bytes(tm, nt) + 1024; }
 
@@ -240,8 +241,8 @@ gemm_tcgen05_ws_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmWsA
         }
     } else {
         // ---------------- weight-tile producers (256 threads), then epilogue
-        // NT/8 Q rows x 64 columns per chunk over 256 threads: CPT = 4 (NT=128) or 8 (NT=256) columns each
-        constexpr int CPT = NT / 32;
+        // NT/8 Q rows x 64 columns per chunk over 512 threads: CPT = 2 (NT=128) or 4 (NT=256) columns each
+        constexpr int CPT = (NT / 8) * kChunkK / (kProducerWarps * 32);
         constexpr int kThreadsPerRow = kChunkK / CPT;
         const int pid = tid - 64;
         const int qrow = pid / kThreadsPerRow, c4 = pid % kThreadsPerRow;
@@ -309,7 +310,8 @@ gemm_tcgen05_ws_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmWsA
                     w[i] = *reinterpret_cast<const unsigned*>(&pr);
                 }
                 if (CPT == 8) *reinterpret_cast<uint4*>(dst + k * 16) = make_uint4(w[0], w[1], w[CPT / 2 - 2], w[CPT / 2 - 1]);
-                else *reinterpret_cast<uint2*>(dst + k * 16) = make_uint2(w[0], w[1]);
+                else if (CPT == 4) *reinterpret_cast<uint2*>(dst + k * 16) = make_uint2(w[0], w[CPT / 2 - 1]);
+                else *reinterpret_cast<unsigned*>(dst + k * 16) = w[0];
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
@@ -321,16 +323,19 @@ gemm_tcgen05_ws_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmWsA
         if (ok) ok = mbar_wait(smem_u32(&bar_acc), 0u);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (ok) {
+            // The accumulators occupy TMEM columns [0, TM*NT): sub-tile j (128 tokens) at columns [j*NT, (j+1)*NT).
+            // Four groups of four warps (one warp per lane quarter) each take a quarter of those columns.
             const int quarter = warp & 3;                    // TMEM lanes this warp may read
-            const int half = (warp - 2) >> 2;
-            constexpr int kSub = TM >= 2 ? TM / 2 : 1;       // token sub-tiles per half
-            for (int jj = 0; jj < kSub; ++jj) {
-                const int j = (TM >= 2) ? half * kSub + jj : 0;
-                if (TM == 1 && half != 0) break;
+            const int group = (warp - 2) >> 2;
+            constexpr int kColsPerGroup = TM * NT / 4;       // 32 .. 128, a multiple of 32
+            {
+                const int acc_col0 = group * kColsPerGroup;
+                const int j = acc_col0 / NT;
+                const int col0 = acc_col0 % NT;              // first output column (inside the tile) of this group
                 const int token = t0 + j * 128 + quarter * 32 + lane;
-                const unsigned lane_addr = tmem_acc + (static_cast<unsigned>(quarter * 32) << 16) + j * NT;
+                const unsigned lane_addr = tmem_acc + (static_cast<unsigned>(quarter * 32) << 16) + acc_col0;
 #pragma unroll
-                for (int part = 0; part < kTileOuts / 32; ++part) {
+                for (int part = 0; part < kColsPerGroup / 32; ++part) {
                     unsigned r[32];
                     asm volatile(
                         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -343,7 +348,7 @@ gemm_tcgen05_ws_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmWsA
                         : "r"(lane_addr + part * 32) : "memory");
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                     if (token < p.T) {
-                        const int o0 = blockIdx.x * kTileOuts + part * 32;
+                        const int o0 = blockIdx.x * kTileOuts + col0 + part * 32;
                         __half* dsty = p.y + static_cast<size_t>(token) * out_dim + o0;
 #pragma unroll
                         for (int v8 = 0; v8 < 4; ++v8) {
@@ -432,10 +437,8 @@ bool gemm_ws_supported(const EptqLayer& L, const void* x, int T) {
 }
 
 int launch_gemm_tcgen05_ws(const EptqLayer& L, const uint16_t* x, uint16_t* y, int T, int* status, cudaStream_t stream) {
-    // Tile shape: 256 outputs x 256 tokens halves the activation bytes each SM has to pull from L2 per MAC
-    // (the limit of the 128-output tile); narrow layers keep 128 outputs to have enough blocks.
     const int out_dim = 8 * L.M;
-    const int nt = (out_dim >= 2048 && T > 128) ? 256 : 128;
+    const int nt = 128;      // measured: 256-output tiles double the reconstruction per stage and run ~20 % slower
     const int tm = nt == 256 ? (T <= 128 ? 1 : 2) : (T <= 128 ? 1 : (T <= 256 ? 2 : 4));
     CUtensorMap tmap;
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(L.N), static_cast<cuuint64_t>(T)};
