@@ -1,0 +1,329 @@
+"""Decode engine for LLaMA-architecture models whose decoder linears are EPTQLinear modules.
+
+The reference decodes through the HuggingFace forward wrapped in torch.compile and CUDA graphs
+(bench_decode.py:35-83, 149).  Here the per-token step is written out once with static shapes --
+RMSNorm, one grouped launch for q/k/v, rotary embedding, append to a preallocated key/value cache,
+attention over the cache with a position mask, o projection, RMSNorm, one grouped launch for gate/up,
+SiLU*up, down projection, final norm, lm_head, greedy pick -- and captured into ONE CUDA graph that
+also advances the position and feeds the picked token back, so a decoded token costs one graph launch
+and no host work.  The same step runs eagerly for the prefill (many tokens: the linears then take the
+tensor-core GEMM path).
+
+Tensor parallelism: with a process group, q/k/v/gate/up hold this rank's output rows (its attention
+heads) and o/down this rank's input columns; their partial outputs are all-reduced (NCCL, captured in
+the graph).  Embedding, norms and lm_head are replicated.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass
+from typing import Callable, Dict, List, Optional, Sequence, Tuple
+
+import torch
+import torch.nn.functional as F
+
+from .kernels.linear import EPTQLinear, forward_group
+
+
+@dataclass
+class DecoderLayerWeights:
+    """The seven linears (any callables mapping (T, in) -> (T, out)) and two norm weights of one layer."""
+    q: Callable
+    k: Callable
+    v: Callable
+    o: Callable
+    gate: Callable
+    up: Callable
+    down: Callable
+    input_norm: torch.Tensor
+    post_norm: torch.Tensor
+
+
+def apply_group(layers: Sequence[Callable], x: torch.Tensor) -> List[torch.Tensor]:
+    """layers[i](x) for all i; one kernel launch when the layers are E8-D4 EPTQLinear modules and the
+    batch is small enough for the persistent GEMV, otherwise one call per layer."""
+    if (x.is_cuda and x.shape[0] <= 2 and all(isinstance(l, EPTQLinear) for l in layers)
+            and all(l.quantizer_type == "e8_d4" and l.S_group is None and l.in_features % 32 == 0 for l in layers)):
+        return forward_group(list(layers), [x] * len(layers))
+    return [l(x) for l in layers]
+
+
+def rotate_half(x: torch.Tensor) -> torch.Tensor:
+    d = x.shape[-1] // 2
+    return torch.cat((-x[..., d:], x[..., :d]), dim=-1)
+
+
+class LlamaDecodeEngine:
+    """Static-shape forward of a LLaMA-style decoder stack with a preallocated key/value cache."""
+
+    def __init__(self, layers: List[DecoderLayerWeights], embed: torch.Tensor, final_norm: torch.Tensor,
+                 lm_head: torch.Tensor, inv_freq: torch.Tensor, rms_eps: float, head_dim: int,
+                 n_heads: int, n_kv_heads: int, max_len: int, batch: int = 1,
+                 rope_scaling: float = 1.0, tp_group=None):
+        self.layers = layers
+        self.embed, self.final_norm, self.lm_head = embed, final_norm, lm_head
+        self.inv_freq = inv_freq.float()
+        self.eps, self.head_dim = float(rms_eps), int(head_dim)
+        self.n_heads, self.n_kv_heads = int(n_heads), int(n_kv_heads)      # per rank
+        self.max_len, self.batch = int(max_len), int(batch)
+        self.rope_scaling = float(rope_scaling)
+        self.tp_group = tp_group
+        dev, dt = embed.device, embed.dtype
+        self.device, self.dtype = dev, dt
+        shape = (len(layers), self.batch, self.n_kv_heads, self.max_len, self.head_dim)
+        self.k_cache = torch.zeros(shape, dtype=dt, device=dev)
+        self.v_cache = torch.zeros(shape, dtype=dt, device=dev)
+        self.key_index = torch.arange(self.max_len, device=dev)
+        # state of the captured step
+        self.token = torch.zeros((self.batch, 1), dtype=torch.long, device=dev)
+        self.position = torch.zeros((1,), dtype=torch.long, device=dev)
+        self.next_token = torch.zeros((self.batch,), dtype=torch.long, device=dev)
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+
+    # ---- construction -------------------------------------------------------------------------
+    @classmethod
+    def from_model(cls, model, max_len: int, batch: int = 1, tp_group=None) -> "LlamaDecodeEngine":
+        """Engine over the modules of a LLaMA-style HuggingFace model (as returned by
+        load_quantized_model); weights are shared, not copied."""
+        core = model.model
+        cfg = model.config
+        head_dim = getattr(cfg, "head_dim", None) or cfg.hidden_size // cfg.num_attention_heads
+        layers = []
+        for layer in core.layers:
+            a, m = layer.self_attn, layer.mlp
+            layers.append(DecoderLayerWeights(a.q_proj, a.k_proj, a.v_proj, a.o_proj, m.gate_proj, m.up_proj,
+                                              m.down_proj, layer.input_layernorm.weight.data,
+                                              layer.post_attention_layernorm.weight.data))
+        q0, k0 = core.layers[0].self_attn.q_proj, core.layers[0].self_attn.k_proj
+        rot = core.rotary_emb
+        return cls(layers, core.embed_tokens.weight.data, core.norm.weight.data, model.lm_head.weight.data,
+                   rot.inv_freq.to(core.embed_tokens.weight.device), cfg.rms_norm_eps, head_dim,
+                   q0.out_features // head_dim, k0.out_features // head_dim, max_len, batch,
+                   rope_scaling=float(getattr(rot, "attention_scaling", 1.0)), tp_group=tp_group)
+
+    # ---- the step -----------------------------------------------------------------------------
+    def _norm(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        return F.rms_norm(x, (x.shape[-1],), w, self.eps)
+
+    def _reduce(self, y: torch.Tensor) -> torch.Tensor:
+        if self.tp_group is not None:
+            torch.distributed.all_reduce(y, group=self.tp_group)
+        return y
+
+    def forward(self, ids: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
+        """ids (B, T) token ids, positions (T,) their cache positions (device tensor).  Writes keys and
+        values at `positions`, attends to every cached position <= its own, returns logits (B, T, V)."""
+        B, T = ids.shape
+        hd, nh, nkv = self.head_dim, self.n_heads, self.n_kv_heads
+        x = F.embedding(ids, self.embed).reshape(B * T, -1)
+        ang = positions.float()[:, None] * self.inv_freq[None, :]                   # (T, hd/2)
+        ang = torch.cat((ang, ang), dim=-1)
+        cos = (ang.cos() * self.rope_scaling).to(self.dtype)[None, None]            # (1, 1, T, hd)
+        sin = (ang.sin() * self.rope_scaling).to(self.dtype)[None, None]
+        mask = (self.key_index[None, :] <= positions[:, None])[None, None]          # (1, 1, T, max_len)
+        for li, L in enumerate(self.layers):
+            hn = self._norm(x, L.input_norm)
+            q, k, v = apply_group((L.q, L.k, L.v), hn)
+            q = q.reshape(B, T, nh, hd).transpose(1, 2)
+            k = k.reshape(B, T, nkv, hd).transpose(1, 2)
+            v = v.reshape(B, T, nkv, hd).transpose(1, 2)
+            q = q * cos + rotate_half(q) * sin
+            k = k * cos + rotate_half(k) * sin
+            kc, vc = self.k_cache[li], self.v_cache[li]
+            kc.index_copy_(2, positions, k)
+            vc.index_copy_(2, positions, v)
+            if nkv != nh:
+                kc = kc.repeat_interleave(nh // nkv, dim=1)
+                vc = vc.repeat_interleave(nh // nkv, dim=1)
+            att = F.scaled_dot_product_attention(q, kc, vc, attn_mask=mask)
+            att = att.transpose(1, 2).reshape(B * T, nh * hd)
+            x = x + self._reduce(L.o(att))
+            hn = self._norm(x, L.post_norm)
+            gate, up = apply_group((L.gate, L.up), hn)
+            x = x + self._reduce(L.down(F.silu(gate) * up))
+        x = self._norm(x, self.final_norm)
+        return F.linear(x, self.lm_head).reshape(B, T, -1)
+
+    # ---- driving it ---------------------------------------------------------------------------
+    @torch.no_grad()
+    def prefill(self, ids: torch.Tensor) -> torch.Tensor:
+        """Run the prompt (B, T) through the stack, fill the cache, set up the decode state; returns the
+        first generated token (greedy)."""
+        B, T = ids.shape
+        if B != self.batch or T >= self.max_len:
+            raise ValueError("prompt does not fit the engine's batch / cache length")
+        pos = torch.arange(T, device=self.device)
+        logits = self.forward(ids, pos)
+        first = logits[:, -1].argmax(dim=-1)
+        self.token.copy_(first[:, None])
+        self.position.fill_(T)
+        return first
+
+    def _step(self) -> None:
+        logits = self.forward(self.token, self.position)
+        nxt = logits[:, -1].argmax(dim=-1)
+        self.next_token.copy_(nxt)
+        self.token.copy_(nxt[:, None])
+        self.position.add_(1)
+
+    @torch.no_grad()
+    def capture(self) -> None:
+        """Capture one decode step into a CUDA graph.  The cache contents and the decode state are
+        restored afterwards, so this may be called between prefill and decode."""
+        saved = (self.token.clone(), self.position.clone())
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):
+            for _ in range(2):                                   # allocate scratch, start NCCL, warm caches
+                self._step()
+                self.token.copy_(saved[0]); self.position.copy_(saved[1])
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self._step()
+        self.graph = graph
+        self.token.copy_(saved[0]); self.position.copy_(saved[1])
+        torch.cuda.synchronize(self.device)
+
+    @torch.no_grad()
+    def decode(self, ids: torch.Tensor, max_new_tokens: int, use_graph: bool = True
+               ) -> Tuple[torch.Tensor, Dict[str, float]]:
+        """Greedy decode.  Returns (tokens (B, max_new_tokens), timings) with the reference's protocol
+        (bench_decode.py:56-71): prefill excluded, tokens/s = (new tokens - 1) * batch / loop time."""
+        if ids.shape[1] + max_new_tokens > self.max_len:
+            raise ValueError("prompt + new tokens exceed the cache length")
+        if use_graph and self.graph is None:
+            self.prefill(ids)                                    # realistic state for the warm-up steps
+            self.capture()
+        torch.cuda.synchronize(self.device)
+        t0 = time.perf_counter()
+        first = self.prefill(ids)
+        torch.cuda.synchronize(self.device)
+        t1 = time.perf_counter()
+        out = torch.empty((self.batch, max_new_tokens), dtype=torch.long, device=self.device)
+        out[:, 0] = first
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for i in range(1, max_new_tokens):
+            if use_graph:
+                self.graph.replay()
+            else:
+                self._step()
+            out[:, i] = self.next_token
+        stop.record()
+        torch.cuda.synchronize(self.device)
+        dev_s = start.elapsed_time(stop) * 1e-3
+        n = max(max_new_tokens - 1, 1) * self.batch
+        return out, {"prefill_s": t1 - t0, "decode_s": dev_s, "tokens_per_s": n / max(dev_s, 1e-9),
+                     "ms_per_token": 1e3 * dev_s / max(max_new_tokens - 1, 1)}
+
+
+def synthetic_llama_engine(hidden: int, intermediate: int, n_layers: int, n_heads: int, n_kv_heads: int,
+                           vocab: int, quantizer_type: str, codebook: torch.Tensor, max_len: int, batch: int = 1,
+                           device: str = "cuda", seed: int = 42, outlier_frac: float = 0.002,
+                           tp_rank: int = 0, tp_size: int = 1, tp_group=None, init_std: float = 0.02,
+                           rope_theta: float = 10000.0, rms_eps: float = 1e-5) -> LlamaDecodeEngine:
+    """Random-init model of a LLaMA architecture, every decoder linear a synthetic quantized layer
+    (make_layer), sharded for this rank when tp_size > 1.  Real checkpoints need the model hub; the
+    shapes and value distributions are what matters for throughput.  Row scales carry an extra factor
+    so that activations stay finite in fp16 through the whole stack; norms are ones, embeddings and
+    lm_head N(0, init_std)."""
+    from .parallel import shard_layer
+    from .synthetic import make_layer
+
+    head_dim = hidden // n_heads
+    shapes = {"q_proj": (n_heads * head_dim, hidden), "k_proj": (n_kv_heads * head_dim, hidden),
+              "v_proj": (n_kv_heads * head_dim, hidden), "o_proj": (hidden, n_heads * head_dim),
+              "gate_proj": (intermediate, hidden), "up_proj": (intermediate, hidden),
+              "down_proj": (hidden, intermediate)}
+    dev = torch.device(device)
+    codebook = codebook.to(dev)
+    layers = []
+    for lid in range(n_layers):
+        mods = {}
+        for k, (name, (o, i)) in enumerate(shapes.items()):
+            qd = make_layer(o, i, seed=seed + 1000 * lid + k, outlier_frac=outlier_frac, device=str(dev),
+                            scale_sigma=0.05)
+            qd.g = (qd.g.float() * (init_std * 1.5)).to(torch.float16)
+            qd = shard_layer(qd, name, tp_rank, tp_size)
+            mods[name] = EPTQLinear.from_quantized_data(qd, codebook, quantizer_type)
+        ones = torch.ones(hidden, dtype=torch.float16, device=dev)
+        layers.append(DecoderLayerWeights(mods["q_proj"], mods["k_proj"], mods["v_proj"], mods["o_proj"],
+                                          mods["gate_proj"], mods["up_proj"], mods["down_proj"], ones, ones.clone()))
+    gen = torch.Generator(device=dev).manual_seed(seed)
+    embed = (torch.randn((vocab, hidden), generator=gen, device=dev) * init_std).to(torch.float16)
+    head = (torch.randn((vocab, hidden), generator=gen, device=dev) * init_std).to(torch.float16)
+    inv_freq = 1.0 / (rope_theta ** (torch.arange(0, head_dim, 2, device=dev).float() / head_dim))
+    return LlamaDecodeEngine(layers, embed, torch.ones(hidden, dtype=torch.float16, device=dev), head, inv_freq,
+                             rms_eps, head_dim, n_heads // tp_size, n_kv_heads // tp_size, max_len, batch,
+                             tp_group=tp_group)
+
+
+ARCHITECTURES = {      # name -> hidden, intermediate, layers, heads, kv heads, vocabulary
+    "llama2-7b": (4096, 11008, 32, 32, 32, 32000),
+    "llama3-8b": (4096, 14336, 32, 32, 8, 128256),
+    "llama2-70b": (8192, 28672, 80, 64, 8, 32000),
+    "tiny": (256, 704, 2, 8, 8, 1024),
+}
+
+
+def _main():
+    """Whole-model greedy decode of a random-init architecture; under torchrun, tensor-parallel over
+    all ranks.  Prints one JSON line (rank 0)."""
+    import argparse
+    import json
+    import os
+
+    from .quantizers import E8D4Quantizer, E8LatticeQuantizer
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--arch", default="llama2-7b", choices=sorted(ARCHITECTURES))
+    ap.add_argument("--layers", type=int, default=None)
+    ap.add_argument("--quantizer", default="e8_d4", choices=["e8_d4", "e8_lattice"])
+    ap.add_argument("--prefill", type=int, default=512)
+    ap.add_argument("--new-tokens", type=int, default=128)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--no-graph", action="store_true")
+    args = ap.parse_args()
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    group = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        group = dist.group.WORLD
+    hidden, inter, n_layers, heads, kv, vocab = ARCHITECTURES[args.arch]
+    n_layers = args.layers or n_layers
+    if args.quantizer == "e8_d4":
+        table = E8D4Quantizer(radius=1.75).codes
+    else:
+        q = E8LatticeQuantizer(radius=1.6)
+        q.remove_last()
+        table = q.points
+    eng = synthetic_llama_engine(hidden, inter, n_layers, heads, kv, vocab, args.quantizer, table,
+                                 max_len=args.prefill + args.new_tokens, batch=args.batch, device=f"cuda:{local}",
+                                 tp_rank=rank, tp_size=world, tp_group=group)
+    ids = torch.randint(0, vocab, (args.batch, args.prefill), generator=torch.Generator().manual_seed(0)).cuda()
+    eng.decode(ids, min(8, args.new_tokens), use_graph=not args.no_graph)          # warm-up (and capture)
+    toks, stats = eng.decode(ids, args.new_tokens, use_graph=not args.no_graph)
+    if world > 1:
+        stat_t = torch.tensor([stats["decode_s"]], device="cuda")
+        torch.distributed.all_reduce(stat_t, op=torch.distributed.ReduceOp.MAX)
+        stats["decode_s"] = float(stat_t.item())
+        stats["tokens_per_s"] = max(args.new_tokens - 1, 1) * args.batch / stats["decode_s"]
+        stats["ms_per_token"] = 1e3 * stats["decode_s"] / max(args.new_tokens - 1, 1)
+    if rank == 0:
+        print(json.dumps({"arch": args.arch, "layers": n_layers, "quantizer": args.quantizer, "batch": args.batch,
+                          "tp": world, "prefill_tokens": args.prefill, "new_tokens": args.new_tokens,
+                          "cuda_graph": not args.no_graph, **stats}), flush=True)
+    if world > 1:
+        torch.cuda.synchronize()
+        os._exit(0)
+
+
+if __name__ == "__main__":
+    _main()
