@@ -352,6 +352,41 @@ def run_gpu_arm(args):
     h2d = sum(v.numel() * 2 for v in x_host.values())
     d2h = y_host.numel() * 2
 
+    # Whole-model decode (the baseline's third configuration): random-init Llama-2-7B architecture,
+    # 512-token prompt, 128 greedy tokens at batch 1, the step captured in one CUDA graph; tensor-
+    # parallel over all ranks.  Reported beside the GEMV figure, not instead of it.
+    decode_stats = {}
+    if not args.no_decode:
+        from eptq_b200.engine import ARCHITECTURES, synthetic_llama_engine
+        from eptq_b200.quantizers import E8LatticeQuantizer
+        del graph2, graph
+        hidden, inter, n_dec, heads, kv, vocab = ARCHITECTURES["llama2-7b"]
+        ids = torch.randint(0, vocab, (1, 512), generator=torch.Generator().manual_seed(0)).to(dev)
+        for qname in ("e8_d4", "e8_lattice"):
+            if qname == "e8_d4":
+                tab = table
+            else:
+                qz = E8LatticeQuantizer(radius=1.6)
+                qz.remove_last()
+                tab = qz.points.to(dev)
+            eng = synthetic_llama_engine(hidden, inter, n_dec, heads, kv, vocab, qname, tab, max_len=512 + 128,
+                                         batch=1, device=str(dev), tp_rank=rank, tp_size=world,
+                                         tp_group=dist.group.WORLD if world > 1 else None)
+            eng.decode(ids, 8)
+            _, st = eng.decode(ids, 128)
+            if world > 1:
+                t = torch.tensor([st["decode_s"]], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                st["decode_s"] = float(t.item())
+                st["tokens_per_s"] = 127 / st["decode_s"]
+                st["ms_per_token"] = 1e3 * st["decode_s"] / 127
+            decode_stats[qname] = {"tokens_per_s": st["tokens_per_s"], "ms_per_token": st["ms_per_token"],
+                                   "prefill_s": st["prefill_s"]}
+            del eng
+            torch.cuda.empty_cache()
+        decode_stats["config"] = ("llama2-7b architecture, random init, 32 layers, 512-token prompt + 128 greedy "
+                                  f"tokens, batch 1, tp{world}, one CUDA graph per token")
+
     if world > 1:
         dist.barrier()
         torch.cuda.synchronize()
@@ -392,6 +427,7 @@ def run_gpu_arm(args):
             "ms_per_step": ms_chain / args.steps,
             "note": "the same pass through eptq_linear_forward, one launch per linear, each ordered after the previous"},
         "clocks": clocks,
+        "decode": decode_stats or None,
     }
     if not args.no_cpu_baseline and world == 1:
         res = cpu_reference_path(B, 10)
@@ -413,6 +449,7 @@ def main():
     ap.add_argument("--group", type=int, default=7,
                     help="independent linears per launch (7 = one decoder layer's linears, 1 = one launch each)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-decode", action="store_true", help="skip the whole-model decode tokens/s arm")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

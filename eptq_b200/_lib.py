@@ -30,6 +30,11 @@ EXPORTS = {
     "eptq_linear_forward_group": (_i, [_vp, _i, _vp, _vp, _i, _vp, _sz, _vp]),
     "eptq_static_scratch_bytes": (_sz, []),
     "eptq_linear_forward_static_scratch": (_i, [_vp, _vp, _vp, _i, _vp]),
+    "eptq_add_rmsnorm": (_i, [_vp, _vp, _vp, _vp, _i, _i, C.c_float, _vp]),
+    "eptq_silu_mul": (_i, [_vp, _vp, _vp, _sz, _vp]),
+    "eptq_rope_append": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, C.c_float, _vp]),
+    "eptq_attention_workspace_bytes": (_sz, [_i, _i, _i, _i]),
+    "eptq_decode_attention": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, C.c_float, _vp, _sz, _vp]),
 }
 
 

@@ -111,8 +111,42 @@ class LlamaDecodeEngine:
         return y
 
     def forward(self, ids: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
-        """ids (B, T) token ids, positions (T,) their cache positions (device tensor).  Writes keys and
-        values at `positions`, attends to every cached position <= its own, returns logits (B, T, V)."""
+        """ids (B, T) token ids, positions (T,) their cache positions (int64 device tensor).  Writes keys
+        and values at `positions`, attends to every cached position <= its own, returns logits (B, T, V).
+        CUDA fp16 only: the elementwise work runs in this package's fused kernels."""
+        if not ids.is_cuda or self.dtype != torch.float16:
+            raise RuntimeError("LlamaDecodeEngine.forward runs on CUDA fp16 weights only "
+                               "(forward_reference is the plain PyTorch statement of the same step)")
+        from .kernels import glue
+        B, T = ids.shape
+        hd, nh, nkv = self.head_dim, self.n_heads, self.n_kv_heads
+        x = F.embedding(ids, self.embed).reshape(B * T, -1)                        # fresh tensor, updated in place
+        fused_attention = T <= 8 and hd in (64, 128)
+        mask = None if fused_attention else (self.key_index[None, :] <= positions[:, None])[None, None]
+        delta = None
+        for li, L in enumerate(self.layers):
+            hn = glue.add_rmsnorm(x, L.input_norm, self.eps, delta)                 # x += previous MLP output
+            q, k, v = apply_group((L.q, L.k, L.v), hn)
+            kc, vc = self.k_cache[li], self.v_cache[li]
+            glue.rope_append(q, k, v, kc, vc, positions, self.inv_freq, B, self.rope_scaling)
+            if fused_attention:
+                att = glue.decode_attention(q, kc, vc, positions, B)
+            else:
+                qh = q.reshape(B, T, nh, hd).transpose(1, 2)
+                if nkv != nh:
+                    kc = kc.repeat_interleave(nh // nkv, dim=1)
+                    vc = vc.repeat_interleave(nh // nkv, dim=1)
+                att = F.scaled_dot_product_attention(qh, kc, vc, attn_mask=mask)
+                att = att.transpose(1, 2).reshape(B * T, nh * hd)
+            hn = glue.add_rmsnorm(x, L.post_norm, self.eps, self._reduce(L.o(att)))
+            gate, up = apply_group((L.gate, L.up), hn)
+            delta = self._reduce(L.down(glue.silu_mul(gate, up)))
+        hn = glue.add_rmsnorm(x, self.final_norm, self.eps, delta)
+        return F.linear(hn, self.lm_head).reshape(B, T, -1)
+
+    def forward_reference(self, ids: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
+        """The same step in plain PyTorch ops, on any device and dtype: what `forward` is tested against,
+        and itself tested against the HuggingFace forward."""
         B, T = ids.shape
         hd, nh, nkv = self.head_dim, self.n_heads, self.n_kv_heads
         x = F.embedding(ids, self.embed).reshape(B * T, -1)
@@ -123,7 +157,7 @@ class LlamaDecodeEngine:
         mask = (self.key_index[None, :] <= positions[:, None])[None, None]          # (1, 1, T, max_len)
         for li, L in enumerate(self.layers):
             hn = self._norm(x, L.input_norm)
-            q, k, v = apply_group((L.q, L.k, L.v), hn)
+            q, k, v = (f(hn) for f in (L.q, L.k, L.v))
             q = q.reshape(B, T, nh, hd).transpose(1, 2)
             k = k.reshape(B, T, nkv, hd).transpose(1, 2)
             v = v.reshape(B, T, nkv, hd).transpose(1, 2)
@@ -139,8 +173,7 @@ class LlamaDecodeEngine:
             att = att.transpose(1, 2).reshape(B * T, nh * hd)
             x = x + self._reduce(L.o(att))
             hn = self._norm(x, L.post_norm)
-            gate, up = apply_group((L.gate, L.up), hn)
-            x = x + self._reduce(L.down(F.silu(gate) * up))
+            x = x + self._reduce(L.down(F.silu(L.gate(hn)) * L.up(hn)))
         x = self._norm(x, self.final_norm)
         return F.linear(x, self.lm_head).reshape(B, T, -1)
 
@@ -153,14 +186,18 @@ class LlamaDecodeEngine:
         if B != self.batch or T >= self.max_len:
             raise ValueError("prompt does not fit the engine's batch / cache length")
         pos = torch.arange(T, device=self.device)
-        logits = self.forward(ids, pos)
+        logits = self._fwd(ids, pos)
         first = logits[:, -1].argmax(dim=-1)
         self.token.copy_(first[:, None])
         self.position.fill_(T)
         return first
 
+    def _fwd(self, ids: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
+        fused = ids.is_cuda and self.dtype == torch.float16
+        return self.forward(ids, positions) if fused else self.forward_reference(ids, positions)
+
     def _step(self) -> None:
-        logits = self.forward(self.token, self.position)
+        logits = self._fwd(self.token, self.position)
         nxt = logits[:, -1].argmax(dim=-1)
         self.next_token.copy_(nxt)
         self.token.copy_(nxt[:, None])
@@ -180,7 +217,7 @@ class LlamaDecodeEngine:
         torch.cuda.current_stream(self.device).wait_stream(side)
         torch.cuda.synchronize(self.device)
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
+        with torch.cuda.graph(graph, stream=side):       # same stream: the scratch made in the warm-up is reused
             self._step()
         self.graph = graph
         self.token.copy_(saved[0]); self.position.copy_(saved[1])

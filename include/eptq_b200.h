@@ -202,6 +202,47 @@ size_t eptq_static_scratch_bytes(void);
 int eptq_linear_forward_static_scratch(const EptqLayer* layer, const uint16_t* x,
                                        uint16_t* y, int B, void* stream);
 
+/*
+ * Decode-step glue (the elementwise work between the quantized linears of a
+ * LLaMA-style decoder layer).  The reference leaves these to the HuggingFace
+ * forward and to torch.compile (bench_decode.py:44-71,149); they are part of
+ * this ABI so that one decoded token is a short, fixed list of launches.
+ * All tensors fp16, contiguous, 16-byte aligned.
+ *
+ * eptq_add_rmsnorm: for each of `rows` rows of length H (multiple of 8):
+ *   if delta != NULL, x += delta (in place, rounded to fp16); then
+ *   out = weight * fp16(x * rsqrt(mean(x^2) + eps))  (LlamaRMSNorm's roundings).
+ * eptq_silu_mul: out[i] = fp16(fp16(silu(gate[i])) * up[i]), n a multiple of 8.
+ * eptq_rope_append: token row r = b*T + t has cache position positions[t]
+ *   (int64, device).  Rotates q (B*T, n_heads*head_dim) in place, writes the
+ *   rotated k (B*T, n_kv_heads*head_dim) and v into the caches
+ *   (B, n_kv_heads, max_len, head_dim) at that position.  Pairs (i, i+head_dim/2),
+ *   angle = position * inv_freq[i] (fp32, device, head_dim/2 entries), cos/sin
+ *   times `scaling` rounded to fp16.  Positions outside [0, max_len) are skipped.
+ * eptq_decode_attention: out (B*T, n_heads*head_dim) = softmax(scale * q K^T) V
+ *   over the cache positions 0..positions[t] of the row's batch entry; grouped
+ *   key/value heads when n_kv_heads < n_heads.  head_dim 64 or 128, else
+ *   EPTQ_ERR_UNSUPPORTED.  Meant for a few query tokens (decode); scratch of
+ *   eptq_attention_workspace_bytes(B*T, n_heads, head_dim, max_len) bytes,
+ *   256-byte aligned, zero-filled once, reusable by calls of any shape that are
+ *   ordered on one stream (take the largest size).  Long contexts are split over
+ *   several blocks per (row, head); that needs B*T*n_heads <= 16384.
+ */
+int eptq_add_rmsnorm(uint16_t* x, const uint16_t* delta, const uint16_t* weight,
+                     uint16_t* out, int rows, int H, float eps, void* stream);
+int eptq_silu_mul(const uint16_t* gate, const uint16_t* up, uint16_t* out,
+                  size_t n, void* stream);
+int eptq_rope_append(uint16_t* q, const uint16_t* k, const uint16_t* v,
+                     uint16_t* k_cache, uint16_t* v_cache, const int64_t* positions,
+                     const float* inv_freq, int B, int T, int n_heads, int n_kv_heads,
+                     int head_dim, int max_len, float scaling, void* stream);
+size_t eptq_attention_workspace_bytes(int rows, int n_heads, int head_dim, int max_len);
+int eptq_decode_attention(const uint16_t* q, const uint16_t* k_cache,
+                          const uint16_t* v_cache, const int64_t* positions,
+                          uint16_t* out, int B, int T, int n_heads, int n_kv_heads,
+                          int head_dim, int max_len, float scale, void* workspace,
+                          size_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -25,10 +25,10 @@ def test_engine_matches_hf_forward_cpu(kv_heads):
     ids = torch.randint(0, 128, (2, 9))
     with torch.no_grad():
         ref = model(input_ids=ids).logits
-        got = eng.forward(ids[:, :6], torch.arange(6))
+        got = eng.forward_reference(ids[:, :6], torch.arange(6))
         assert torch.allclose(got, ref[:, :6], atol=2e-4, rtol=1e-3)
         for p in range(6, 9):                       # token by token over the cache
-            step = eng.forward(ids[:, p:p + 1], torch.tensor([p]))
+            step = eng.forward_reference(ids[:, p:p + 1], torch.tensor([p]))
             assert torch.allclose(step[:, 0], ref[:, p], atol=2e-4, rtol=1e-3)
 
 
@@ -70,11 +70,21 @@ def test_engine_graph_decode_gpu(quantizer_type):
         model, _ = load_quantized_model(d, device="cuda", require_tokenizer=False)
     ids = torch.randint(0, 512, (1, 24), generator=torch.Generator().manual_seed(3)).cuda()
     eng = LlamaDecodeEngine.from_model(model, max_len=64, batch=1)
+    plain = LlamaDecodeEngine.from_model(model, max_len=64, batch=1)
+    pos = torch.arange(24, device="cuda")
     with torch.no_grad():
         ref = model(input_ids=ids).logits.float()
-        got = eng.forward(ids, torch.arange(24, device="cuda")).float()
-    scale = float(ref.abs().max())
-    assert float((got - ref).abs().max()) <= 2e-2 * scale
+        got = eng.forward(ids, pos).float()                       # fused kernels, prompt-sized
+        same = plain.forward_reference(ids, pos).float()          # plain PyTorch statement
+        scale = float(ref.abs().max())
+        assert float((got - ref).abs().max()) <= 2e-2 * scale
+        assert float((same - ref).abs().max()) <= 2e-2 * scale
+        # one more token through the single-query attention kernel against the plain statement
+        nxt = ids[:, :1]
+        p1 = torch.tensor([24], device="cuda")
+        a = eng.forward(nxt, p1).float()
+        b = plain.forward_reference(nxt, p1).float()
+        assert float((a - b).abs().max()) <= 2e-2 * scale
     eager, _ = eng.decode(ids, 12, use_graph=False)
     graphed, stats = eng.decode(ids, 12, use_graph=True)
     assert eng.graph is not None
