@@ -28,6 +28,7 @@ EXPORTS = {
     "eptq_dequantize": (_i, [_vp, _vp, _vp]),
     "eptq_group_workspace_bytes": (_sz, [_vp, _i, _i]),
     "eptq_linear_forward_group": (_i, [_vp, _i, _vp, _vp, _i, _vp, _sz, _vp]),
+    "eptq_linear_forward_group_fused": (_i, [_vp, _i, _vp, _vp, _vp, _i, _vp, _sz, _vp]),
     "eptq_static_scratch_bytes": (_sz, []),
     "eptq_linear_forward_static_scratch": (_i, [_vp, _vp, _vp, _i, _vp]),
     "eptq_add_rmsnorm": (_i, [_vp, _vp, _vp, _vp, _i, _i, C.c_float, _vp]),
@@ -46,6 +47,19 @@ class EptqLayer(C.Structure):
         ("Q", _vp), ("table32", _vp), ("table16", _vp), ("g", _vp), ("h", _vp),
         ("O_vals", _vp), ("O_col", _vp), ("O_row_ptr", _vp), ("bias", _vp), ("S_group", _vp),
         ("table8", _vp), ("table8_scale", C.c_float), ("h_absmax", C.c_float),
+    ]
+
+
+X_PLAIN, X_RMSNORM = 0, 2
+Y_STORE, Y_ADD_RESIDUAL, Y_ROPE, Y_ROPE_TO_CACHE, Y_TO_CACHE = 0, 1, 2, 3, 4
+
+
+class EptqFusion(C.Structure):
+    """struct EptqFusion of include/eptq_b200.h."""
+    _fields_ = [
+        ("x_op", C.c_int32), ("y_op", C.c_int32), ("norm_eps", C.c_float), ("rope_scaling", C.c_float),
+        ("max_len", C.c_int32), ("reserved", C.c_int32),
+        ("residual", _vp), ("position", _vp), ("inv_freq", _vp),
     ]
 
 

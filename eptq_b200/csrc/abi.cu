@@ -25,8 +25,8 @@ bool gemm_ws_supported(const EptqLayer& L, const void* x, int T);
 int launch_gemm_tcgen05_ws(const EptqLayer& L, const uint16_t* x, uint16_t* y, int T, int* status, cudaStream_t stream);
 bool group_gemv_supported(const EptqLayer* layers, int n, int B);
 size_t group_workspace_bytes(const EptqLayer* layers, int n, int B, int n_sms);
-int launch_gemv_group(const EptqLayer* layers, int n, const uint16_t* const* xs, uint16_t* const* ys, int B,
-                      void* workspace, size_t workspace_bytes, cudaStream_t stream);
+int launch_gemv_group(const EptqLayer* layers, int n, const EptqFusion* fusions, const uint16_t* const* xs,
+                      uint16_t* const* ys, int B, void* workspace, size_t workspace_bytes, cudaStream_t stream);
 
 namespace {
 
@@ -71,7 +71,7 @@ int forward_checked(const EptqLayer& L, const uint16_t* x, uint16_t* y, int B,
         uint16_t* ys[1] = {y};
         const size_t need = group_workspace_bytes(&L, 1, B, 0);
         if (need != 0 && workspace != nullptr && workspace_bytes >= need)
-            return launch_gemv_group(&L, 1, xs, ys, B, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+            return launch_gemv_group(&L, 1, nullptr, xs, ys, B, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
     }
     if (mma_gemv_supported(L, B) && aligned16(L.g) && (L.bias == nullptr || aligned16(L.bias)) && aligned16(y))
         return launch_gemv_mma(L, x, y, B, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
@@ -129,7 +129,7 @@ size_t eptq_workspace_bytes(int M, int N, int B) {
     if (M <= 0 || N <= 0 || B <= 0) return 0;
     int cols = 0;
     const int splits = simt_plan_splits(M, N, B, &cols);
-    size_t bytes = kCounterBytes;
+    size_t bytes = kPartialOffset;
     bytes += static_cast<size_t>(splits > 1 ? splits : 1) * B * 8u * M * sizeof(float);
     if (B <= 4 && (N % 32) == 0) {
         const size_t mma = mma_workspace_bytes(M, N, B);
@@ -149,9 +149,9 @@ size_t eptq_group_workspace_bytes(const EptqLayer* layers, int n_layers, int B) 
     return (group_workspace_bytes(layers, n_layers, B, 0) + 255) & ~static_cast<size_t>(255);
 }
 
-int eptq_linear_forward_group(const EptqLayer* layers, int n_layers,
-                              const uint16_t* const* xs, uint16_t* const* ys, int B,
-                              void* workspace, size_t workspace_bytes, void* stream) {
+int eptq_linear_forward_group_fused(const EptqLayer* layers, int n_layers, const EptqFusion* fusions,
+                                    const uint16_t* const* xs, uint16_t* const* ys, int B,
+                                    void* workspace, size_t workspace_bytes, void* stream) {
     if (layers == nullptr || xs == nullptr || ys == nullptr) return EPTQ_ERR_NULL;
     if (n_layers < 1 || B < 1) return EPTQ_ERR_SHAPE;
     for (int i = 0; i < n_layers; ++i) {
@@ -162,7 +162,14 @@ int eptq_linear_forward_group(const EptqLayer* layers, int n_layers,
     }
     if (!group_gemv_supported(layers, n_layers, B)) return EPTQ_ERR_UNSUPPORTED;
     if (workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return EPTQ_ERR_ALIGN;
-    return launch_gemv_group(layers, n_layers, xs, ys, B, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+    return launch_gemv_group(layers, n_layers, fusions, xs, ys, B, workspace, workspace_bytes,
+                             static_cast<cudaStream_t>(stream));
+}
+
+int eptq_linear_forward_group(const EptqLayer* layers, int n_layers,
+                              const uint16_t* const* xs, uint16_t* const* ys, int B,
+                              void* workspace, size_t workspace_bytes, void* stream) {
+    return eptq_linear_forward_group_fused(layers, n_layers, nullptr, xs, ys, B, workspace, workspace_bytes, stream);
 }
 
 int eptq_prepare_d4_table8(const float* table, uint8_t* out, float* scale) {

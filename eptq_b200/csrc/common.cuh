@@ -23,12 +23,14 @@ extern std::atomic<uint64_t> g_launches;    // kernels launched by this library
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-// Scratch layout shared by every GEMV variant.  The counter region has a fixed
-// size so that its position does not depend on the layer: the same scratch is
-// reused by layers of different shapes, and only this region must stay zero.
-//   [0, kCounterBytes)              unsigned arrival counters, zero between calls
-//   [kCounterBytes, ...)            float partial sums [split][batch][8*M]
+// Scratch layout shared by every GEMV variant.  The regions that must stay zero between calls have a
+// fixed position and size, so that the same scratch can serve layers of different shapes and every
+// kernel variant: whoever writes there puts the zeros back before it ends.
+//   [0, kCounterBytes)              unsigned arrival counters
+//   [kCounterBytes, kPartialOffset) fp32 accumulators of the persistent group GEMV (atomic adds)
+//   [kPartialOffset, ...)           float partial sums [split][batch][8*M], overwritten before read
 constexpr size_t kCounterBytes = 4096;
+constexpr size_t kPartialOffset = 1u << 20;
 constexpr int kMaxCounters = static_cast<int>(kCounterBytes / sizeof(unsigned));
 constexpr int kGemmMinBatch = 16;           // batches above this run on the tensor-core GEMM
 // The last counter word is the GEMM's status word (EPTQ_ERR_TIMEOUT if a bounded wait ran out), so

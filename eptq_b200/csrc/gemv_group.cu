@@ -14,9 +14,10 @@
 // Work split ("stream-K"): all 16-row x 32-column strips of all layers form one
 // sequence (layer, row tile, strip); main warp w takes the contiguous range
 // [w*W/nw, (w+1)*W/nw).  Inside a row tile the accumulators stay in registers;
-// at a row-tile boundary the warp writes its partial into the tile's slot
-// (slot = warp index - first warp of the tile) and takes a ticket; the last
-// arrival adds the slots in order, applies g and bias, writes fp16.  Each warp
+// at a row-tile boundary the warp adds its partial to the tile's fp32 accumulator
+// in scratch (red.global.add, so the cost does not grow with the number of warps
+// that share a tile) and takes a ticket; the last arrival reads the accumulator,
+// puts the zeros back, applies g and bias, writes fp16.  Each warp
 // works alone: Q arrives through a 3-deep register ring of 128-bit loads, the
 // activation pieces through a 512-byte warp-private slab, no block-wide barrier
 // after the table is built.
@@ -26,7 +27,7 @@
 // on the raw index bits: (q & 0xFF80) | (8*(lane%16) | 0x10000).
 //
 // Critical blocks: two warps per block walk the CSR in units of 4 Q rows and add
-// sum (O[i] - code[65535]) * h*x as one more partial per row tile.
+// sum (O[i] - code[65535]) * h*x to the same accumulators.
 //
 // Reference counterpart: e8d4_fused_kernel_t (csrc/eptq_kernels.cu:161-292),
 // one launch per layer and batch row there.
@@ -51,21 +52,27 @@ struct GroupLayer {
     const __half* bias;
     __half* y;
     long long strip0;       // index of this layer's first strip in the global sequence
-    long long partial_off;  // float offset of this layer's partial sums
+    long long acc_off;      // float offset of this layer's accumulators: [row tile][batch][128]
     int M, N;
     int ns;                 // strips per row tile = N / 32
     int row_tiles;          // ceil(M / 16)
     int tile0;              // index of this layer's first row tile (counters)
     int corr0;              // index of this layer's first correction unit (4 Q rows each)
-    int slots;              // partial slots per row tile; the last one holds the corrections
     float x_scale;          // power of two, <= 1 / max|h|
     float x_inv_scale;
+    // fused epilogue (EptqFusion): what the finalizing warp does with a finished row tile
+    const __half* residual;     // EPTQ_Y_ADD_RESIDUAL
+    const long long* position;  // rotary angle / cache row (device scalar)
+    const float* inv_freq;      // 64 inverse frequencies
+    int y_op;
+    int max_len;
+    float rope_scaling;
 };
 
 struct GroupArgs {
     GroupLayer L[kMaxGroupLayers];
     const uint2* table16;
-    float* partial;
+    float* acc;             // zero on entry, zero again on exit
     unsigned* counters;
     long long W;            // total strips
     int n_layers;
@@ -73,6 +80,8 @@ struct GroupArgs {
     int nw;                 // total main warps
     int corr_units;         // total correction units
     int n_corr_warps;
+    int x_norm;             // EPTQ_X_RMSNORM: all layers read one x; outputs are scaled by rsqrt(mean(x^2) + eps)
+    float norm_eps;
 };
 
 namespace {
@@ -120,11 +129,16 @@ __device__ __forceinline__ void code_addrs(unsigned q, unsigned lane_tab, unsign
 }
 
 // Warp that owns global strip s when warp w owns [w*W/nw, (w+1)*W/nw).
-__device__ __forceinline__ int owner_warp(long long s, long long W, int nw) {
-    int w = static_cast<int>((s * nw) / W);
-    while (w + 1 < nw && (static_cast<long long>(w + 1) * W) / nw <= s) ++w;
-    while (w > 0 && (static_cast<long long>(w) * W) / nw > s) --w;
-    return w;
+// The host keeps W * nw below 2^32, so unsigned 32-bit arithmetic is exact.
+__device__ __forceinline__ int owner_warp(long long s64, long long W64, int nw) {
+    const unsigned s = static_cast<unsigned>(s64), W = static_cast<unsigned>(W64), n = static_cast<unsigned>(nw);
+    unsigned w = (s * n) / W;
+    while (w + 1 < n && ((w + 1) * W) / n <= s) ++w;
+    while (w > 0 && (w * W) / n > s) --w;
+    return static_cast<int>(w);
+}
+__device__ __forceinline__ void red_add4(float* p, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1,%2,%3,%4};" :: "l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
 struct Affine { float g[4]; float b[4]; };
@@ -150,34 +164,71 @@ __device__ __forceinline__ Affine load_affine(const GroupLayer& L, int rt, int l
     return a;
 }
 
-// Take a ticket for row tile rt of layer L; the last of `expected` arrivals adds
-// the partial slots [0, n_main) and the correction slot and writes y.
+// Take a ticket for row tile rt of layer L; the last of the expected arrivals (n_main GEMV partials and
+// 4 correction quarters) reads the tile's accumulators, zeroes them for the next launch and writes y.
 __device__ __forceinline__ void arrive_and_finalize(const GroupArgs& p, const GroupLayer& L, int rt, int n_main,
-                                                    int lane, const Affine& aff) {
+                                                    int lane, const Affine& aff, const float* inv_rms) {
+    __threadfence();                                                 // this lane's adds are performed before the ticket
     __syncwarp();
     unsigned ticket = 0;
     unsigned* ctr = p.counters + L.tile0 + rt;
     if (lane == 0)
         asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(ticket) : "l"(ctr) : "memory");
     ticket = __shfl_sync(0xffffffffu, ticket, 0);
-    if (ticket != static_cast<unsigned>(n_main) + 3u) return;       // n_main GEMV partials + 4 correction quarters
+    if (ticket != static_cast<unsigned>(n_main) + 3u) return;
     if (lane == 0) *ctr = 0u;
+    __threadfence();
     const int row = rt * 16 + (lane >> 1);
-    if (row >= L.M) return;
     const int o = row * 8 + (lane & 1) * 4;
-    for (int b = 0; b < p.B; ++b) {
-        const float* base = p.partial + L.partial_off + (static_cast<size_t>(rt) * L.slots * p.B + b) * 128 + lane * 4;
-        float4 s = __ldcg(reinterpret_cast<const float4*>(base + static_cast<size_t>(L.slots - 1) * p.B * 128));
-        for (int k = 0; k < n_main; ++k) {
-            const float4 v = __ldcg(reinterpret_cast<const float4*>(base + static_cast<size_t>(k) * p.B * 128));
-            s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+    const bool rope = L.y_op == EPTQ_Y_ROPE || L.y_op == EPTQ_Y_ROPE_TO_CACHE;
+    const bool to_cache = L.y_op == EPTQ_Y_ROPE_TO_CACHE || L.y_op == EPTQ_Y_TO_CACHE;
+    long long pos = 0;
+    float cs[4] = {1.f, 1.f, 1.f, 1.f}, sn[4] = {0.f, 0.f, 0.f, 0.f};
+    if (rope || to_cache) pos = *L.position;
+    if (rope) {
+        // A row tile is one head of 128: this lane holds dimensions 4*lane .. 4*lane+3, the rotation
+        // partner (dimension +-64) sits 16 lanes away.  cos/sin rounded to fp16 as the model code does.
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            float sv, cv;
+            sincosf(static_cast<float>(pos) * L.inv_freq[(lane & 15) * 4 + c], &sv, &cv);
+            cs[c] = __half2float(__float2half_rn(cv * L.rope_scaling));
+            sn[c] = __half2float(__float2half_rn(sv * L.rope_scaling));
+            if (lane < 16) sn[c] = -sn[c];
         }
-        const __half2 o01 = __floats2half2_rn(fmaf(s.x, aff.g[0], aff.b[0]), fmaf(s.y, aff.g[1], aff.b[1]));
-        const __half2 o23 = __floats2half2_rn(fmaf(s.z, aff.g[2], aff.b[2]), fmaf(s.w, aff.g[3], aff.b[3]));
+    }
+    for (int b = 0; b < p.B; ++b) {
+        float* a = p.acc + L.acc_off + (static_cast<size_t>(rt) * p.B + b) * 128 + lane * 4;
+        float4 s = __ldcg(reinterpret_cast<const float4*>(a));
+        __stcg(reinterpret_cast<float4*>(a), make_float4(0.f, 0.f, 0.f, 0.f));
+        if (inv_rms != nullptr) { const float r = inv_rms[b]; s.x *= r; s.y *= r; s.z *= r; s.w *= r; }
+        __half2 o01 = __floats2half2_rn(fmaf(s.x, aff.g[0], aff.b[0]), fmaf(s.y, aff.g[1], aff.b[1]));
+        __half2 o23 = __floats2half2_rn(fmaf(s.z, aff.g[2], aff.b[2]), fmaf(s.w, aff.g[3], aff.b[3]));
+        if (rope) {                                       // every row of the tile exists (checked on the host)
+            const float2 v01 = __half22float2(o01), v23 = __half22float2(o23);
+            const float v[4] = {v01.x, v01.y, v23.x, v23.y};
+            float r[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) r[c] = fmaf(v[c], cs[c], __shfl_xor_sync(0xffffffffu, v[c], 16) * sn[c]);
+            o01 = __floats2half2_rn(r[0], r[1]);
+            o23 = __floats2half2_rn(r[2], r[3]);
+        }
+        if (row >= L.M) continue;
+        __half* dst = L.y + static_cast<size_t>(b) * 8 * L.M + o;
+        if (to_cache) {
+            const int heads = L.M >> 4;
+            dst = L.y + ((static_cast<size_t>(b) * heads + rt) * L.max_len + pos) * 128 + lane * 4;
+            if (pos < 0 || pos >= L.max_len) continue;
+        }
+        if (L.y_op == EPTQ_Y_ADD_RESIDUAL) {
+            const uint2 rv = *reinterpret_cast<const uint2*>(L.residual + static_cast<size_t>(b) * 8 * L.M + o);
+            o01 = __hadd2(*reinterpret_cast<const __half2*>(&rv.x), o01);
+            o23 = __hadd2(*reinterpret_cast<const __half2*>(&rv.y), o23);
+        }
         uint2 outv;
         outv.x = *reinterpret_cast<const unsigned*>(&o01);
         outv.y = *reinterpret_cast<const unsigned*>(&o23);
-        *reinterpret_cast<uint2*>(L.y + static_cast<size_t>(b) * 8 * L.M + o) = outv;
+        *reinterpret_cast<uint2*>(dst) = outv;
     }
 }
 
@@ -199,7 +250,7 @@ namespace {
 template <typename WaitFn>
 __device__ __forceinline__ void correction_unit(const GroupArgs& p, const GroupLayer& L, int qt, int lane,
                                                 float cstar0, float cstar1, float cstar2, float cstar3,
-                                                WaitFn wait_dep) {
+                                                const float* inv_rms, WaitFn wait_dep) {
     const int row = qt * 4 + (lane >> 3);
     const int sub = lane & 7;
     const int rt = qt >> 2;
@@ -258,17 +309,16 @@ __device__ __forceinline__ void correction_unit(const GroupArgs& p, const GroupL
                 acc[b][k] += __shfl_xor_sync(0xffffffffu, acc[b][k], 2);
                 acc[b][k] += __shfl_xor_sync(0xffffffffu, acc[b][k], 4);
             }
-            if (sub == 0) {
-                float* dst = p.partial + L.partial_off + ((static_cast<size_t>(rt) * L.slots + (L.slots - 1)) * p.B + b) * 128
-                           + ((qt & 3) * 4 + (lane >> 3)) * 8;
-                __stcg(reinterpret_cast<float4*>(dst), make_float4(acc[b][0], acc[b][1], acc[b][2], acc[b][3]));
-                __stcg(reinterpret_cast<float4*>(dst + 4), make_float4(acc[b][4], acc[b][5], acc[b][6], acc[b][7]));
+            if (sub == 0 && lo < hi) {
+                float* dst = p.acc + L.acc_off + (static_cast<size_t>(rt) * p.B + b) * 128 + ((qt & 3) * 4 + (lane >> 3)) * 8;
+                red_add4(dst, acc[b][0], acc[b][1], acc[b][2], acc[b][3]);
+                red_add4(dst + 4, acc[b][4], acc[b][5], acc[b][6], acc[b][7]);
             }
         }
     }
     int first_warp;
     const int n_main = tile_contributors(p, L, rt, first_warp);
-    arrive_and_finalize(p, L, rt, n_main, lane, aff);
+    arrive_and_finalize(p, L, rt, n_main, lane, aff, inv_rms);
 }
 
 // Position in the global strip sequence.
@@ -294,36 +344,11 @@ __global__ void __launch_bounds__(kGroupThreads, 1) gemv_group_kernel(const __gr
 
     asm volatile("griddepcontrol.launch_dependents;");
 
-    // Replicated table; entry order follows the raw stored bits (true index ^ 0x100 on 9 bits).
-    {
-        const int chunk = threadIdx.x & 7;
-        for (int e = threadIdx.x >> 3; e < 512; e += kGroupThreads / 8) {
-            const uint2 v = __ldg(p.table16 + (e ^ 0x100));
-            *reinterpret_cast<uint4*>(tab + e * 128 + chunk * 16) = make_uint4(v.x, v.y, v.x, v.y);
-        }
-    }
-
-    if (warp >= kMainWarps) {
-        // ---- correction warps
-        const uint2 craw = __ldg(p.table16 + 511);      // what the main loop adds for a marker: entry (3,127), both halves
-        const float2 c01 = __half22float2(*reinterpret_cast<const __half2*>(&craw.x));
-        const float2 c23 = __half22float2(*reinterpret_cast<const __half2*>(&craw.y));
-        __syncthreads();
-        bool waited = false;
-        const int cw = blockIdx.x * kCorrWarps + (warp - kMainWarps);
-        int l = 0;
-        for (int u = cw; u < p.corr_units; u += p.n_corr_warps) {
-            while (l + 1 < p.n_layers && p.L[l + 1].corr0 <= u) ++l;
-            correction_unit(p, p.L[l], u - p.L[l].corr0, lane, c01.x, c01.y, c23.x, c23.y, [&]() {
-                if (!waited) { asm volatile("griddepcontrol.wait;" ::: "memory"); waited = true; }
-            });
-        }
-        return;
-    }
-
-    // ---- main warps
+    // ---- main warps: find the first strips and start their loads before anything else, so that the DRAM
+    // round trip runs under the table build.  (Correction warps carry the same variables unused.)
+    const bool is_main = warp < kMainWarps;
     const int g = lane >> 2, t = lane & 3;
-    const int gw = blockIdx.x * kMainWarps + warp;
+    const int gw = is_main ? blockIdx.x * kMainWarps + warp : p.nw;
     const long long s_begin = gw < p.nw ? (static_cast<long long>(gw) * p.W) / p.nw : p.W;
     const long long s_end = gw < p.nw ? (static_cast<long long>(gw + 1) * p.W) / p.nw : p.W;
     const int n_total = static_cast<int>(s_end - s_begin);
@@ -384,7 +409,66 @@ __global__ void __launch_bounds__(kGroupThreads, 1) gemv_group_kernel(const __gr
             --pf_todo;
         }
     }
+    // Replicated table; entry order follows the raw stored bits (true index ^ 0x100 on 9 bits).
+    {
+        const int chunk = threadIdx.x & 7;
+        for (int e = threadIdx.x >> 3; e < 512; e += kGroupThreads / 8) {
+            const uint2 v = __ldg(p.table16 + (e ^ 0x100));
+            *reinterpret_cast<uint4*>(tab + e * 128 + chunk * 16) = make_uint4(v.x, v.y, v.x, v.y);
+        }
+    }
+
     __syncthreads();                                   // table complete (all 16 warps reach this once)
+
+    // Fused RMSNorm of the input: every layer of the launch reads the same x; the column weight of the
+    // norm is folded into h by the caller, the row factor rsqrt(mean(x^2) + eps) is applied by the
+    // finalizing warp.  Each block computes it for itself.
+    const float* inv_rms = nullptr;
+    if (p.x_norm) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        float* red = reinterpret_cast<float*>(smem_raw + kGroupThreads / 32 * 512);       // behind the slabs
+        const int N = p.L[0].N;
+        float ss[2] = {0.f, 0.f};
+        for (int b = 0; b < p.B; ++b)
+            for (int c = threadIdx.x * 8; c < N; c += kGroupThreads * 8) {
+                float f[8];
+                unpack8(ldg128(p.L[0].x + static_cast<size_t>(b) * N + c), f);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) ss[b] = fmaf(f[i], f[i], ss[b]);
+            }
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ss[b] += __shfl_xor_sync(0xffffffffu, ss[b], o);
+            if (lane == 0) red[warp * 2 + b] = ss[b];
+        }
+        __syncthreads();
+        if (threadIdx.x < 2) {
+            float tot = 0.f;
+            for (int w = 0; w < kGroupThreads / 32; ++w) tot += red[w * 2 + threadIdx.x];
+            red[64 + threadIdx.x] = rsqrtf(tot / static_cast<float>(N) + p.norm_eps);
+        }
+        __syncthreads();
+        inv_rms = red + 64;
+    }
+
+    if (warp >= kMainWarps) {
+        // ---- correction warps
+        const uint2 craw = __ldg(p.table16 + 511);      // what the main loop adds for a marker: entry (3,127), both halves
+        const float2 c01 = __half22float2(*reinterpret_cast<const __half2*>(&craw.x));
+        const float2 c23 = __half22float2(*reinterpret_cast<const __half2*>(&craw.y));
+        bool waited = false;
+        const int cw = blockIdx.x * kCorrWarps + (warp - kMainWarps);
+        int l = 0;
+        for (int u = cw; u < p.corr_units; u += p.n_corr_warps) {
+            while (l + 1 < p.n_layers && p.L[l + 1].corr0 <= u) ++l;
+            correction_unit(p, p.L[l], u - p.L[l].corr0, lane, c01.x, c01.y, c23.x, c23.y, inv_rms, [&]() {
+                if (!waited) { asm volatile("griddepcontrol.wait;" ::: "memory"); waited = true; }
+            });
+        }
+        return;
+    }
+
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (n_total <= 0) return;
 #pragma unroll
@@ -421,7 +505,7 @@ __global__ void __launch_bounds__(kGroupThreads, 1) gemv_group_kernel(const __gr
         const int n_main = tile_contributors(p, L, rt, first_warp);
         const float inv = L.x_inv_scale;
         const int b = t >> 1;
-        float* dst = p.partial + L.partial_off + ((static_cast<size_t>(rt) * L.slots + (gw - first_warp)) * p.B + b) * 128;
+        float* dst = p.acc + L.acc_off + (static_cast<size_t>(rt) * p.B + b) * 128;
 #pragma unroll
         for (int rg = 0; rg < 2; ++rg)
 #pragma unroll
@@ -434,9 +518,9 @@ __global__ void __launch_bounds__(kGroupThreads, 1) gemv_group_kernel(const __gr
                     acc[rg][hf][c] = 0.f;
                 }
                 if ((t & 1) == 0 && b < p.B)
-                    __stcg(reinterpret_cast<float4*>(dst + (g + 8 * rg) * 8 + hf * 4), make_float4(tot[0], tot[1], tot[2], tot[3]));
+                    red_add4(dst + (g + 8 * rg) * 8 + hf * 4, tot[0], tot[1], tot[2], tot[3]);
             }
-        arrive_and_finalize(p, L, rt, n_main, lane, aff);
+        arrive_and_finalize(p, L, rt, n_main, lane, aff, inv_rms);
     };
 
 #define EPTQ_GROUP_STEP(I)                                                                                   \
@@ -509,8 +593,7 @@ struct GroupPlan {
     int n_sms = 0;
     int tiles = 0;
     int corr_units = 0;
-    size_t partial_floats = 0;
-    int slots[kMaxGroupLayers] = {};
+    size_t acc_floats = 0;
 };
 
 int cached_sm_count() {
@@ -525,7 +608,7 @@ int cached_sm_count() {
     return sms[dev];
 }
 
-// Shapes only: how many strips, warps, slots and scratch floats a group needs.
+// Shapes only: how many strips, warps and accumulator floats a group needs.
 bool plan_group(const EptqLayer* layers, int n, int B, int n_sms, GroupPlan& plan) {
     if (n < 1 || n > kMaxGroupLayers || B < 1 || B > 2 || n_sms < 1) return false;
     plan = GroupPlan();
@@ -539,14 +622,9 @@ bool plan_group(const EptqLayer* layers, int n, int B, int n_sms, GroupPlan& pla
     }
     if (plan.W < 1 || plan.tiles > kMaxCounters - 1) return false;
     if (plan.nw > plan.W) plan.nw = static_cast<int>(plan.W);          // every warp range non-empty
-    const long long per_warp = plan.W / plan.nw > 0 ? plan.W / plan.nw : 1;
-    for (int i = 0; i < n; ++i) {
-        const int ns = layers[i].N / 32;
-        long long contributors = (ns + per_warp - 1) / per_warp + 1;
-        if (contributors > ns) contributors = ns;
-        plan.slots[i] = static_cast<int>(contributors) + 1;                 // + the correction slot
-        plan.partial_floats += static_cast<size_t>((layers[i].M + 15) / 16) * plan.slots[i] * B * 128;
-    }
+    if (plan.W * plan.nw >= (1LL << 32)) return false;                  // owner_warp works in 32 bits
+    plan.acc_floats = static_cast<size_t>(plan.tiles) * B * 128;
+    if (plan.acc_floats * sizeof(float) > kPartialOffset - kCounterBytes) return false;
     return true;
 }
 
@@ -573,15 +651,15 @@ size_t group_workspace_bytes(const EptqLayer* layers, int n, int B, int n_sms) {
     GroupPlan plan;
     if (n_sms <= 0) n_sms = 148;
     if (!plan_group(layers, n, B, n_sms, plan)) return 0;
-    return kCounterBytes + plan.partial_floats * sizeof(float);
+    return kPartialOffset;
 }
 
-int launch_gemv_group(const EptqLayer* layers, int n, const uint16_t* const* xs, uint16_t* const* ys, int B,
-                      void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+int launch_gemv_group(const EptqLayer* layers, int n, const EptqFusion* fusions, const uint16_t* const* xs,
+                      uint16_t* const* ys, int B, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
     const int n_sms = cached_sm_count();
     GroupPlan plan;
     if (!plan_group(layers, n, B, n_sms, plan)) return EPTQ_ERR_UNSUPPORTED;
-    const size_t need = kCounterBytes + plan.partial_floats * sizeof(float);
+    const size_t need = kPartialOffset;
     if (workspace == nullptr || workspace_bytes < need) return EPTQ_ERR_WORKSPACE;
 
     static GroupArgs args;                     // large: keep it off the stack; filled under a lock
@@ -590,13 +668,33 @@ int launch_gemv_group(const EptqLayer* layers, int n, const uint16_t* const* xs,
     GroupArgs& a = args;
     a.table16 = reinterpret_cast<const uint2*>(layers[0].table16);
     a.counters = reinterpret_cast<unsigned*>(workspace);
-    a.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + kCounterBytes);
+    a.acc = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + kCounterBytes);
     a.W = plan.W;
     a.n_layers = n;
     a.B = B;
     a.nw = plan.nw;
     a.corr_units = plan.corr_units;
     a.n_corr_warps = n_sms * kCorrWarps;
+    a.x_norm = 0;
+    a.norm_eps = 0.f;
+    if (fusions != nullptr) {
+        // Fused RMSNorm is a property of the launch: all layers or none, one shared input.
+        int normed = 0;
+        for (int i = 0; i < n; ++i) {
+            if (fusions[i].x_op == EPTQ_X_RMSNORM) ++normed;
+            else if (fusions[i].x_op != EPTQ_X_PLAIN) return EPTQ_ERR_UNSUPPORTED;
+        }
+        if (normed != 0) {
+            if (normed != n) return EPTQ_ERR_UNSUPPORTED;
+            for (int i = 0; i < n; ++i)
+                if (xs[i] != xs[0] || layers[i].N != layers[0].N || fusions[i].norm_eps != fusions[0].norm_eps)
+                    return EPTQ_ERR_UNSUPPORTED;
+            if (xs[0] == nullptr) return EPTQ_ERR_NULL;
+            if (!aligned16(xs[0])) return EPTQ_ERR_ALIGN;
+            a.x_norm = 1;
+            a.norm_eps = fusions[0].norm_eps;
+        }
+    }
     long long strip0 = 0, poff = 0;
     int tile0 = 0, corr0 = 0;
     for (int i = 0; i < n; ++i) {
@@ -616,14 +714,38 @@ int launch_gemv_group(const EptqLayer* layers, int n, const uint16_t* const* xs,
         G.M = L.M; G.N = L.N;
         G.ns = L.N / 32;
         G.row_tiles = (L.M + 15) / 16;
-        G.strip0 = strip0; G.partial_off = poff; G.tile0 = tile0; G.corr0 = corr0;
-        G.slots = plan.slots[i];
+        G.strip0 = strip0; G.acc_off = poff; G.tile0 = tile0; G.corr0 = corr0;
         int e = 0;
         std::frexp(L.h_absmax, &e);            // h_absmax = m * 2^e, m in [0.5, 1)  =>  2^-e <= 1/h_absmax
         G.x_scale = std::ldexp(1.0f, -e);
         G.x_inv_scale = std::ldexp(1.0f, e);
+        G.residual = nullptr; G.position = nullptr; G.inv_freq = nullptr;
+        G.y_op = EPTQ_Y_STORE; G.max_len = 0; G.rope_scaling = 1.f;
+        if (fusions != nullptr) {
+            const EptqFusion& F = fusions[i];
+            G.y_op = F.y_op;
+            switch (F.y_op) {
+                case EPTQ_Y_STORE: break;
+                case EPTQ_Y_ADD_RESIDUAL:
+                    if (F.residual == nullptr) return EPTQ_ERR_NULL;
+                    if ((reinterpret_cast<uintptr_t>(F.residual) & 7u) != 0) return EPTQ_ERR_ALIGN;
+                    G.residual = reinterpret_cast<const __half*>(F.residual);
+                    break;
+                case EPTQ_Y_ROPE: case EPTQ_Y_ROPE_TO_CACHE: case EPTQ_Y_TO_CACHE:
+                    if ((L.M % 16) != 0) return EPTQ_ERR_SHAPE;               // whole heads of 128 outputs
+                    if (F.position == nullptr) return EPTQ_ERR_NULL;
+                    if (F.y_op != EPTQ_Y_TO_CACHE && F.inv_freq == nullptr) return EPTQ_ERR_NULL;
+                    if (F.y_op != EPTQ_Y_ROPE && F.max_len < 1) return EPTQ_ERR_SHAPE;
+                    G.position = reinterpret_cast<const long long*>(F.position);
+                    G.inv_freq = F.inv_freq;
+                    G.max_len = F.max_len;
+                    G.rope_scaling = F.rope_scaling;
+                    break;
+                default: return EPTQ_ERR_UNSUPPORTED;
+            }
+        }
         strip0 += static_cast<long long>(G.row_tiles) * G.ns;
-        poff += static_cast<long long>(G.row_tiles) * G.slots * B * 128;
+        poff += static_cast<long long>(G.row_tiles) * B * 128;
         tile0 += G.row_tiles;
         corr0 += G.row_tiles * 4;
     }

@@ -602,7 +602,7 @@ size_t mma_workspace_bytes(int M, int N, int B) {
     int wc, cb, gy, cg;
     const int row_tiles = mma_plan(M, N, &wc, &cb, &gy, &cg);
     if (row_tiles >= kMaxCounters) return 0;
-    return kCounterBytes + static_cast<size_t>(row_tiles) * (cb + 1) * B * 128 * sizeof(float);
+    return kPartialOffset + static_cast<size_t>(row_tiles) * (cb + 1) * B * 128 * sizeof(float);
 }
 
 bool mma_gemv_supported(const EptqLayer& L, int B) {
@@ -628,7 +628,7 @@ int launch_gemv_mma(const EptqLayer& L, const uint16_t* x, uint16_t* y, int B,
     a.bias = reinterpret_cast<const __half*>(L.bias);
     a.y = reinterpret_cast<__half*>(y);
     a.counters = reinterpret_cast<unsigned*>(workspace);
-    a.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + kCounterBytes);
+    a.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + kPartialOffset);
     a.M = L.M; a.N = L.N; a.B = B;
     a.row_tiles = row_tiles;
     a.row_blocks = (row_tiles + (kWarps / wc) - 1) / (kWarps / wc);

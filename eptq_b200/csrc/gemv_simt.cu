@@ -291,10 +291,10 @@ int launch_gemv_simt(const EptqLayer& L, const uint16_t* x, uint16_t* y, int B,
     a.partial = nullptr;
     a.counters = nullptr;
     if (splits > 1) {
-        const size_t need = kCounterBytes + static_cast<size_t>(splits) * B * 8u * L.M * sizeof(float);
+        const size_t need = kPartialOffset + static_cast<size_t>(splits) * B * 8u * L.M * sizeof(float);
         if (workspace == nullptr || workspace_bytes < need) return EPTQ_ERR_WORKSPACE;
         a.counters = reinterpret_cast<unsigned*>(workspace);
-        a.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + kCounterBytes);
+        a.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + kPartialOffset);
     }
     dim3 grid(row_blocks, splits, batch_blocks);
     if (L.quantizer == EPTQ_E8) return launch_simt_kind<EPTQ_E8>(a, bt, grid, stream);

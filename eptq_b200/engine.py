@@ -79,6 +79,7 @@ class LlamaDecodeEngine:
         self.position = torch.zeros((1,), dtype=torch.long, device=dev)
         self.next_token = torch.zeros((self.batch,), dtype=torch.long, device=dev)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self._fused = None           # descriptors for the fully fused one-token step, False if not eligible
 
     # ---- construction -------------------------------------------------------------------------
     @classmethod
@@ -120,6 +121,8 @@ class LlamaDecodeEngine:
         from .kernels import glue
         B, T = ids.shape
         hd, nh, nkv = self.head_dim, self.n_heads, self.n_kv_heads
+        if T == 1 and B <= 2 and hd == 128 and self.tp_group is None and self._fusable():
+            return self._forward_fused_decode(ids, positions)
         x = F.embedding(ids, self.embed).reshape(B * T, -1)                        # fresh tensor, updated in place
         fused_attention = T <= 8 and hd in (64, 128)
         mask = None if fused_attention else (self.key_index[None, :] <= positions[:, None])[None, None]
@@ -143,6 +146,69 @@ class LlamaDecodeEngine:
             delta = self._reduce(L.down(glue.silu_mul(gate, up)))
         hn = glue.add_rmsnorm(x, self.final_norm, self.eps, delta)
         return F.linear(hn, self.lm_head).reshape(B, T, -1)
+
+    # ---- one token, everything fused into the GEMV launches -----------------------------------------
+    def _fusable(self) -> bool:
+        if self._fused is None:
+            ok = all(isinstance(m, EPTQLinear) and m.quantizer_type == "e8_d4" and m.S_group is None
+                     and m.in_features % 32 == 0 and m.out_features % 128 == 0
+                     for L in self.layers for m in (L.q, L.k, L.v, L.o, L.gate, L.up, L.down))
+            self._fused = self._build_fused() if ok else False
+        return self._fused is not False
+
+    def _build_fused(self):
+        """Per layer: descriptors of q/k/v and gate/up whose column scales carry the norm weight
+        (h' = h * w, so that the kernel only needs the row factor of the RMSNorm), plus o and down."""
+        from .kernels import h_absmax
+        plan = []
+        for L in self.layers:
+            keep = []
+
+            def folded(mods, w):
+                out = []
+                for m in mods:
+                    h2 = (m.h.float() * w.float()).to(torch.float16).contiguous()
+                    d = m.descriptor()
+                    d.h = h2.data_ptr()
+                    d.h_absmax = h_absmax(h2)
+                    keep.append(h2)
+                    out.append(d)
+                return out
+            plan.append({"qkv": folded((L.q, L.k, L.v), L.input_norm), "o": [L.o.descriptor()],
+                         "gate_up": folded((L.gate, L.up), L.post_norm), "down": [L.down.descriptor()],
+                         "keep": keep})
+        return plan
+
+    def _forward_fused_decode(self, ids: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
+        """Five launches per decoder layer: q/k/v (RMSNorm folded in; rotary embedding and the cache
+        append done by the finalizing warps), attention, o (+ residual), gate/up (RMSNorm folded in),
+        SiLU*up, down (+ residual)."""
+        from . import _lib
+        from .kernels import glue, linear_forward_group
+        B = ids.shape[0]
+        hd, nh, nkv = self.head_dim, self.n_heads, self.n_kv_heads
+        x = F.embedding(ids, self.embed).reshape(B, -1).contiguous()                # residual stream, updated in place
+        pos_ptr, freq_ptr = positions.data_ptr(), self.inv_freq.data_ptr()
+
+        def fus(x_op=_lib.X_PLAIN, y_op=_lib.Y_STORE, residual=None):
+            f = _lib.EptqFusion()
+            f.x_op, f.y_op, f.norm_eps, f.rope_scaling, f.max_len = x_op, y_op, self.eps, self.rope_scaling, self.max_len
+            f.residual = None if residual is None else residual.data_ptr()
+            f.position, f.inv_freq = pos_ptr, freq_ptr
+            return f
+        qkv_f = [fus(_lib.X_RMSNORM, _lib.Y_ROPE), fus(_lib.X_RMSNORM, _lib.Y_ROPE_TO_CACHE),
+                 fus(_lib.X_RMSNORM, _lib.Y_TO_CACHE)]
+        gu_f = [fus(_lib.X_RMSNORM), fus(_lib.X_RMSNORM)]
+        res_f = [fus(y_op=_lib.Y_ADD_RESIDUAL, residual=x)]
+        for li, (L, P) in enumerate(zip(self.layers, self._fused)):
+            kc, vc = self.k_cache[li], self.v_cache[li]
+            q = linear_forward_group(P["qkv"], [x, x, x], [nh * hd, 0, 0], fusions=qkv_f, ys=[None, kc, vc])[0]
+            att = glue.decode_attention(q, kc, vc, positions, B)
+            linear_forward_group(P["o"], [att], [0], fusions=res_f, ys=[x])
+            gate, up = linear_forward_group(P["gate_up"], [x, x], [L.gate.out_features, L.up.out_features], fusions=gu_f)
+            linear_forward_group(P["down"], [glue.silu_mul(gate, up)], [0], fusions=res_f, ys=[x])
+        hn = glue.add_rmsnorm(x, self.final_norm, self.eps)
+        return F.linear(hn, self.lm_head).reshape(B, 1, -1)
 
     def forward_reference(self, ids: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
         """The same step in plain PyTorch ops, on any device and dtype: what `forward` is tested against,

@@ -220,15 +220,21 @@ def _(x, Q, table16, table32, g, h, O_vals, O_col, O_row_ptr, bias, S_group, qua
     return x.new_empty(x.shape[0], Q.shape[0] * 8, dtype=torch.float16)
 
 
-def linear_forward_group(descs, xs, out_features, workspace: Optional[torch.Tensor] = None):
-    """Several independent layers in one launch (eptq_linear_forward_group).  `descs` are EptqLayer
+def linear_forward_group(descs, xs, out_features, workspace: Optional[torch.Tensor] = None,
+                         fusions=None, ys=None):
+    """Several independent layers in one launch (eptq_linear_forward_group[_fused]).  `descs` are EptqLayer
     descriptors (see EPTQLinear.descriptor), `xs` contiguous fp16 CUDA tensors (B, in_i) with one B;
-    returns the list of (B, out_i) fp16 outputs.  Raises if the group is not eligible."""
+    returns the list of (B, out_i) fp16 outputs.  `fusions`: optional list of _lib.EptqFusion, one per
+    layer; `ys`: optional list of output tensors to write (None entries are allocated) -- a residual
+    stream updated in place, or a key/value cache.  Raises if the group is not eligible."""
     lib = _lib.load()
     n = len(descs)
     B = xs[0].shape[0]
     dev = xs[0].device
-    ys = [torch.empty((B, o), dtype=torch.float16, device=dev) for o in out_features]
+    ys = list(ys) if ys is not None else [None] * n
+    for i, o in enumerate(out_features):
+        if ys[i] is None:
+            ys[i] = torch.empty((B, o), dtype=torch.float16, device=dev)
     arr = (_lib.EptqLayer * n)(*descs)
     need = lib.eptq_group_workspace_bytes(arr, n, B)
     if need == 0:
@@ -237,7 +243,11 @@ def linear_forward_group(descs, xs, out_features, workspace: Optional[torch.Tens
     xp = (C.c_void_p * n)(*[x.data_ptr() for x in xs])
     yp = (C.c_void_p * n)(*[y.data_ptr() for y in ys])
     with torch.cuda.device(dev):
-        st = lib.eptq_linear_forward_group(arr, n, xp, yp, B, ws.data_ptr(), ws.numel(), _stream(dev))
+        if fusions is None:
+            st = lib.eptq_linear_forward_group(arr, n, xp, yp, B, ws.data_ptr(), ws.numel(), _stream(dev))
+        else:
+            fz = (_lib.EptqFusion * n)(*fusions)
+            st = lib.eptq_linear_forward_group_fused(arr, n, fz, xp, yp, B, ws.data_ptr(), ws.numel(), _stream(dev))
     _lib.check(st, "eptq group forward")
     return ys
 

@@ -110,9 +110,9 @@ int eptq_prepare_d4_table8(const float* table, uint8_t* out, float* scale);
  * eptq_e8d4_forward may need for a layer of this shape at batch B.  The caller
  * allocates it once (256-byte aligned), zero-fills it once, and may reuse it
  * for every call that is ordered on one stream, for layers of any shape (take
- * the maximum of the sizes): the first 4096 bytes hold counters that every
- * kernel returns to zero, the rest is overwritten before it is read.  Calls
- * that may overlap on the GPU need separate scratch.
+ * the maximum of the sizes): the first 1 MiB holds counters and accumulators
+ * that every kernel returns to zero, the rest is overwritten before it is
+ * read.  Calls that may overlap on the GPU need separate scratch.
  */
 size_t eptq_workspace_bytes(int M, int N, int B);
 
@@ -170,6 +170,47 @@ size_t eptq_group_workspace_bytes(const EptqLayer* layers, int n_layers, int B);
 int eptq_linear_forward_group(const EptqLayer* layers, int n_layers,
                               const uint16_t* const* xs, uint16_t* const* ys, int B,
                               void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * The same launch with work fused around each layer (decode-step glue; the
+ * reference leaves it to the HuggingFace forward, bench_decode.py:44-71).
+ * `fusions` has one entry per layer, or is NULL (then identical to
+ * eptq_linear_forward_group).
+ *
+ *   x_op  EPTQ_X_PLAIN    x is used as given.
+ *         EPTQ_X_RMSNORM  the layer sees x * rsqrt(mean(x^2) + norm_eps) per batch
+ *                         row (the column weight of the norm is expected folded
+ *                         into h by the caller).  All layers or none; they must
+ *                         share one x pointer, N and norm_eps.
+ *   y_op  EPTQ_Y_STORE         y (B, 8M) = out
+ *         EPTQ_Y_ADD_RESIDUAL  y = residual + out, both rounded to fp16 as two
+ *                              separate ops would; residual may be y itself.
+ *         EPTQ_Y_ROPE          rotary embedding on heads of 128 outputs (pairs
+ *                              (i, i+64), angle = *position * inv_freq[i], cos/sin
+ *                              times rope_scaling rounded to fp16), stored to y.
+ *         EPTQ_Y_ROPE_TO_CACHE the same, stored into a key cache: y points to fp16
+ *                              (B, 8M/128, max_len, 128), row *position.
+ *         EPTQ_Y_TO_CACHE      no rotation, stored into a value cache likewise.
+ *   The three head-wise ops need 8M a multiple of 128 (M % 16 == 0).
+ */
+enum { EPTQ_X_PLAIN = 0, EPTQ_X_RMSNORM = 2 };
+enum { EPTQ_Y_STORE = 0, EPTQ_Y_ADD_RESIDUAL = 1, EPTQ_Y_ROPE = 2, EPTQ_Y_ROPE_TO_CACHE = 3, EPTQ_Y_TO_CACHE = 4 };
+
+typedef struct EptqFusion {
+    int32_t x_op;
+    int32_t y_op;
+    float norm_eps;
+    float rope_scaling;
+    int32_t max_len;
+    int32_t reserved;
+    const uint16_t* residual;   /* fp16 (B, 8M) */
+    const int64_t* position;    /* device scalar */
+    const float* inv_freq;      /* device, 64 entries */
+} EptqFusion;
+
+int eptq_linear_forward_group_fused(const EptqLayer* layers, int n_layers, const EptqFusion* fusions,
+                                    const uint16_t* const* xs, uint16_t* const* ys, int B,
+                                    void* workspace, size_t workspace_bytes, void* stream);
 
 /*
  * Reconstruct the fp16 weight (8M, N) row-major, bit-for-bit what the

@@ -51,15 +51,16 @@ def test_engine_greedy_state_cpu():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("quantizer_type", ["e8_d4", "e8_lattice"])
-def test_engine_graph_decode_gpu(quantizer_type):
+@pytest.mark.parametrize("quantizer_type,hidden,heads,inter", [("e8_d4", 256, 8, 704), ("e8_lattice", 256, 8, 704),
+                                                              ("e8_d4", 512, 4, 768)])
+def test_engine_graph_decode_gpu(quantizer_type, hidden, heads, inter):
     from eptq_b200.kernels.patch import load_quantized_model
     from eptq_b200.quantizers import E8D4Quantizer, E8LatticeQuantizer
     from eptq_b200.synthetic import write_quantized_dir
     from transformers import LlamaConfig
 
-    cfg = LlamaConfig(hidden_size=256, intermediate_size=704, num_hidden_layers=2, num_attention_heads=8,
-                      num_key_value_heads=8, vocab_size=512, max_position_embeddings=256, tie_word_embeddings=False)
+    cfg = LlamaConfig(hidden_size=hidden, intermediate_size=inter, num_hidden_layers=2, num_attention_heads=heads,
+                      num_key_value_heads=heads, vocab_size=512, max_position_embeddings=256, tie_word_embeddings=False)
     if quantizer_type == "e8_d4":
         q = E8D4Quantizer(radius=1.75)
     else:
@@ -85,6 +86,8 @@ def test_engine_graph_decode_gpu(quantizer_type):
         a = eng.forward(nxt, p1).float()
         b = plain.forward_reference(nxt, p1).float()
         assert float((a - b).abs().max()) <= 2e-2 * scale
+        # head size 128 with E8-D4 layers takes the fully fused step (norm, rotary, cache, residual in the GEMVs)
+        assert (eng._fused not in (None, False)) == (quantizer_type == "e8_d4" and hidden // heads == 128)
     eager, _ = eng.decode(ids, 12, use_graph=False)
     graphed, stats = eng.decode(ids, 12, use_graph=True)
     assert eng.graph is not None
