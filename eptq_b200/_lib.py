@@ -47,6 +47,7 @@ class EptqLayer(C.Structure):
         ("Q", _vp), ("table32", _vp), ("table16", _vp), ("g", _vp), ("h", _vp),
         ("O_vals", _vp), ("O_col", _vp), ("O_row_ptr", _vp), ("bias", _vp), ("S_group", _vp),
         ("table8", _vp), ("table8_scale", C.c_float), ("h_absmax", C.c_float),
+        ("table_packed", _vp), ("table_packed_scale", C.c_float), ("reserved", C.c_int32),
     ]
 
 
@@ -79,7 +80,7 @@ def load() -> C.CDLL:
     for name, (res, args) in EXPORTS.items():
         fn = getattr(lib, name)          # AttributeError if the symbol is not exported
         fn.restype, fn.argtypes = res, args
-    if lib.eptq_abi_version() != 1:
+    if lib.eptq_abi_version() != 2:
         raise RuntimeError("libeptq_b200.so has an unexpected ABI version")
     _lib = lib
     return lib

@@ -66,7 +66,9 @@ int forward_checked(const EptqLayer& L, const uint16_t* x, uint16_t* y, int B,
             return launch_gemm_tcgen05_ws(L, x, y, B, status, static_cast<cudaStream_t>(stream));
         return launch_gemm_tcgen05(L, x, y, B, status, static_cast<cudaStream_t>(stream));
     }
-    if (group_gemv_supported(&L, 1, B) && aligned16(y)) {
+    // The E8 variant copies 219 KB of table into every block: not worth it for a small layer.
+    const bool big_enough = L.quantizer != EPTQ_E8 || static_cast<long long>(L.M) * L.N >= (1LL << 20);
+    if (big_enough && group_gemv_supported(&L, 1, B) && aligned16(y)) {
         const uint16_t* xs[1] = {x};
         uint16_t* ys[1] = {y};
         const size_t need = group_workspace_bytes(&L, 1, B, 0);

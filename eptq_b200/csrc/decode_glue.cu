@@ -51,6 +51,10 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(__half* __restrict__ x
                                                           const __half* __restrict__ w, __half* __restrict__ out,
                                                           int H, float eps) {
     __shared__ float red[33];
+    // Programmatic dependent launch: let the next kernel of the stream start its own set-up now, and
+    // wait for the previous kernel's results before touching any input.
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const size_t row = static_cast<size_t>(blockIdx.x) * H;
     float ss = 0.f;
     for (int c = threadIdx.x * 8; c < H; c += blockDim.x * 8) {
@@ -93,6 +97,10 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(__half* __restrict__ x
 // ---- SiLU(gate) * up ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) silu_mul_kernel(const __half* __restrict__ gate, const __half* __restrict__ up,
                                                        __half* __restrict__ out, size_t n8) {
+    // Programmatic dependent launch: let the next kernel of the stream start its own set-up now, and
+    // wait for the previous kernel's results before touching any input.
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n8;
          i += static_cast<size_t>(gridDim.x) * blockDim.x) {
         const uint4 gv = reinterpret_cast<const uint4*>(gate)[i];
@@ -121,6 +129,10 @@ __global__ void rope_append_kernel(__half* __restrict__ q, const __half* __restr
                                    __half* __restrict__ k_cache, __half* __restrict__ v_cache,
                                    const long long* __restrict__ positions, const float* __restrict__ inv_freq,
                                    int T, int nh, int nkv, int hd, int max_len, float scaling) {
+    // Programmatic dependent launch: let the next kernel of the stream start its own set-up now, and
+    // wait for the previous kernel's results before touching any input.
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int r = blockIdx.x, b = r / T, t = r - b * T;
     const int head = blockIdx.y;
     const int i = threadIdx.x, half = hd >> 1;
@@ -179,6 +191,10 @@ __global__ void __launch_bounds__(kAttThreads) decode_attention_kernel(
     __shared__ float red[33];
     __shared__ float accs[KG][HD];
     __shared__ int is_last;
+    // Programmatic dependent launch: let the next kernel of the stream start its own set-up now, and
+    // wait for the previous kernel's results before touching any input.
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     const int tid = threadIdx.x;
     const int head = blockIdx.x, r = blockIdx.y, split = blockIdx.z, S = gridDim.z;
@@ -303,6 +319,22 @@ int attention_splits(int rows, int nh, int max_len) {
 constexpr size_t kAttCounterBytes = 65536;
 constexpr long long kAttMaxCounters = kAttCounterBytes / sizeof(unsigned);
 
+// Launch with the programmatic-stream-serialization attribute (the kernels above wait on their own).
+template <typename... KArgs, typename... Args>
+void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 int finish_launch() {
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return cudaGetLastError() == cudaSuccess ? EPTQ_OK : EPTQ_ERR_LAUNCH;
@@ -319,7 +351,7 @@ extern "C" int eptq_add_rmsnorm(uint16_t* x, const uint16_t* delta, const uint16
     if (rows < 0 || H < 8 || (H % 8) != 0) return EPTQ_ERR_SHAPE;
     if (!aligned16(x) || !aligned16(weight) || !aligned16(out) || (delta != nullptr && !aligned16(delta))) return EPTQ_ERR_ALIGN;
     if (rows == 0) return EPTQ_OK;
-    add_rmsnorm_kernel<<<rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+    launch_pdl(add_rmsnorm_kernel, dim3(rows), dim3(256), static_cast<cudaStream_t>(stream),
         reinterpret_cast<__half*>(x), reinterpret_cast<const __half*>(delta), reinterpret_cast<const __half*>(weight),
         reinterpret_cast<__half*>(out), H, eps);
     return finish_launch();
@@ -332,7 +364,7 @@ extern "C" int eptq_silu_mul(const uint16_t* gate, const uint16_t* up, uint16_t*
     if (n == 0) return EPTQ_OK;
     const size_t n8 = n / 8;
     const unsigned blocks = static_cast<unsigned>(n8 / 256 + 1 > 1184 ? 1184 : n8 / 256 + 1);
-    silu_mul_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+    launch_pdl(silu_mul_kernel, dim3(blocks), dim3(256), static_cast<cudaStream_t>(stream),
         reinterpret_cast<const __half*>(gate), reinterpret_cast<const __half*>(up), reinterpret_cast<__half*>(out), n8);
     return finish_launch();
 }
@@ -347,7 +379,7 @@ extern "C" int eptq_rope_append(uint16_t* q, const uint16_t* k, const uint16_t* 
     if (B == 0 || T == 0) return EPTQ_OK;
     const dim3 grid(static_cast<unsigned>(B) * T, n_heads + 2 * n_kv_heads);
     if (grid.y > 65535u) return EPTQ_ERR_SHAPE;
-    rope_append_kernel<<<grid, head_dim / 2, 0, static_cast<cudaStream_t>(stream)>>>(
+    launch_pdl(rope_append_kernel, grid, dim3(head_dim / 2), static_cast<cudaStream_t>(stream),
         reinterpret_cast<__half*>(q), reinterpret_cast<const __half*>(k), reinterpret_cast<const __half*>(v),
         reinterpret_cast<__half*>(k_cache), reinterpret_cast<__half*>(v_cache),
         reinterpret_cast<const long long*>(positions), inv_freq, T, n_heads, n_kv_heads, head_dim, max_len, scaling);
@@ -392,8 +424,8 @@ extern "C" int eptq_decode_attention(const uint16_t* q, const uint16_t* k_cache,
     const long long* ph = reinterpret_cast<const long long*>(positions);
     __half* oh = reinterpret_cast<__half*>(out);
     if (head_dim == 128)
-        decode_attention_kernel<128><<<grid, kAttThreads, 0, st>>>(qh, kh, vh, ph, oh, partial, counters, T, n_heads, n_kv_heads, max_len, scale);
+        launch_pdl(decode_attention_kernel<128>, grid, dim3(kAttThreads), st, qh, kh, vh, ph, oh, partial, counters, T, n_heads, n_kv_heads, max_len, scale);
     else
-        decode_attention_kernel<64><<<grid, kAttThreads, 0, st>>>(qh, kh, vh, ph, oh, partial, counters, T, n_heads, n_kv_heads, max_len, scale);
+        launch_pdl(decode_attention_kernel<64>, grid, dim3(kAttThreads), st, qh, kh, vh, ph, oh, partial, counters, T, n_heads, n_kv_heads, max_len, scale);
     return finish_launch();
 }

@@ -71,7 +71,8 @@ struct GroupLayer {
 
 struct GroupArgs {
     GroupLayer L[kMaxGroupLayers];
-    const uint2* table16;
+    const uint2* table16;     // E8-D4: fp16 (512, 4)
+    const unsigned* packed;   // E8: 65536 packed entries (see e8_decode)
     float* acc;             // zero on entry, zero again on exit
     unsigned* counters;
     long long W;            // total strips
@@ -91,7 +92,13 @@ constexpr int kCorrWarps = 2;
 constexpr int kGroupThreads = (kMainWarps + kCorrWarps) * 32;
 constexpr unsigned kTableAddr = 0x10000u;                       // shared-window address of the table
 constexpr int kGroupSmemBytes = 2 * 65536 - 1024;               // window [0x400, 0x20000)
-constexpr int kRing = 3;                                        // Q strips in flight per warp
+constexpr int kRing = 3;                                        // Q strips in flight per warp (E8-D4)
+// E8: the packed table (4 bytes per entry) does not fit whole; entries [0, kE8Resident) live in shared
+// memory behind the slabs, the rest is read from the copy in global memory (L2).
+constexpr int kRingE8 = 2;
+constexpr int kE8SmemBytes = 232448;                            // the most a block may ask for
+constexpr int kE8TableOffset = (kMainWarps + kCorrWarps) * 512 + 512;
+constexpr unsigned kE8Resident = (kE8SmemBytes - kE8TableOffset) / 4;
 
 __device__ __forceinline__ unsigned smem_addr(const void* p) {
     return static_cast<unsigned>(__cvta_generic_to_shared(p));
@@ -126,6 +133,43 @@ __device__ __forceinline__ unsigned split_pieces(float v) {
 __device__ __forceinline__ void code_addrs(unsigned q, unsigned lane_tab, unsigned& ai, unsigned& aj) {
     ai = (q & 0xFF80u) | lane_tab;
     aj = ((q << 7) & 0x3F80u) | ((q & 0xC000u) | lane_tab);
+}
+
+// Packed E8 entry -> four A-fragment registers (dims (0,1), (2,3), (4,5), (6,7) as fp16 pairs, in lattice
+// units).  Each coordinate is stored as n = 2*coordinate + 6 (0..12) in a 4-bit field placed so that a mask
+// drops it straight into the mantissa of the fp16 number 1024 + (n << s): fields of dims 0,1 at bits
+// [5:2],[21:18], dims 2,3 at [9:6],[25:22], dims 4,5 at [13:10],[29:26], dims 6,7 at [17:14],[33:30]
+// (the last one wraps around: its low two bits are bits 31:30, its high two bits 1:0), so the second
+// pair of registers comes from the word rotated by 8.  One fused multiply-add per register removes the
+// offset exactly: (1024 + 4n)/8 - 131 = (1024 + 64n)/128 - 11 = n/2 - 3.
+__device__ __forceinline__ void e8_decode(unsigned e, unsigned (&r)[4]) {
+    const unsigned rot = __funnelshift_r(e, e, 8);
+    const unsigned magic = 0x64006400u;
+    unsigned a0 = (e & 0x003C003Cu) | magic, a1 = (e & 0x03C003C0u) | magic;
+    unsigned a2 = (rot & 0x003C003Cu) | magic, a3 = (rot & 0x03C003C0u) | magic;
+    const __half2 kA = __floats2half2_rn(0.125f, 0.125f), cA = __floats2half2_rn(-131.f, -131.f);
+    const __half2 kB = __floats2half2_rn(0.0078125f, 0.0078125f), cB = __floats2half2_rn(-11.f, -11.f);
+    __half2 h0 = __hfma2(*reinterpret_cast<__half2*>(&a0), kA, cA), h1 = __hfma2(*reinterpret_cast<__half2*>(&a1), kB, cB);
+    __half2 h2 = __hfma2(*reinterpret_cast<__half2*>(&a2), kA, cA), h3 = __hfma2(*reinterpret_cast<__half2*>(&a3), kB, cB);
+    r[0] = *reinterpret_cast<unsigned*>(&h0); r[1] = *reinterpret_cast<unsigned*>(&h1);
+    r[2] = *reinterpret_cast<unsigned*>(&h2); r[3] = *reinterpret_cast<unsigned*>(&h3);
+}
+// Entry of true index u: from shared memory when resident, else from the global copy.
+__device__ __forceinline__ unsigned e8_lookup(unsigned u, unsigned tbase, const unsigned* packed) {
+    unsigned v;
+    asm volatile("{\n\t.reg .pred p;\n\t.reg .u64 ga;\n\t.reg .u32 sa;\n\t"
+                 "setp.ge.u32 p, %1, %2;\n\t"
+                 "mad.wide.u32 ga, %1, 4, %3;\n\t"
+                 "mad.lo.u32 sa, %1, 4, %4;\n\t"
+                 "@p ld.global.nc.u32 %0, [ga];\n\t"
+                 "@!p ld.shared.u32 %0, [sa];\n\t}"
+                 : "=r"(v) : "r"(u), "r"(kE8Resident), "l"(packed), "r"(tbase));
+    return v;
+}
+__device__ __forceinline__ void mma_f16r(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
 // Warp that owns global strip s when warp w owns [w*W/nw, (w+1)*W/nw).
@@ -335,7 +379,9 @@ struct StripIter {
     }
 };
 
+template <int KIND>
 __global__ void __launch_bounds__(kGroupThreads, 1) gemv_group_kernel(const __grid_constant__ GroupArgs p) {
+    constexpr int RING = KIND == EPTQ_E8 ? kRingE8 : kRing;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
@@ -391,16 +437,16 @@ __global__ void __launch_bounds__(kGroupThreads, 1) gemv_group_kernel(const __gr
     const int cur_l0 = pf.l, cur_rt0 = pf.rt, cur_left0 = pf.left;
     Cursor xfirst = pf;                                  // for the x loads that must follow the dependency wait
 
-    uint4 qa[kRing], qb[kRing];
-    __half hr[kRing], xr0[kRing], xr1[kRing];
+    uint4 qa[RING], qb[RING];
+    __half hr[RING], xr0[RING], xr1[RING];
 #pragma unroll
-    for (int i = 0; i < kRing; ++i) {
+    for (int i = 0; i < RING; ++i) {
         qa[i] = make_uint4(0, 0, 0, 0); qb[i] = make_uint4(0, 0, 0, 0);
         hr[i] = __ushort_as_half(0); xr0[i] = __ushort_as_half(0); xr1[i] = __ushort_as_half(0);
     }
     int pf_todo = n_total;
 #pragma unroll
-    for (int i = 0; i < kRing; ++i) {
+    for (int i = 0; i < RING; ++i) {
         if (pf_todo > 0) {
             qa[i] = ldg_stream(pf.pa);
             qb[i] = ldg_stream(pf.pb);
@@ -409,8 +455,15 @@ __global__ void __launch_bounds__(kGroupThreads, 1) gemv_group_kernel(const __gr
             --pf_todo;
         }
     }
-    // Replicated table; entry order follows the raw stored bits (true index ^ 0x100 on 9 bits).
-    {
+    if constexpr (KIND == EPTQ_E8) {
+        // Resident part of the packed table: asynchronous 16-byte copies, no registers in between.
+        const unsigned dst0 = base + kE8TableOffset;
+        const char* src0 = reinterpret_cast<const char*>(p.packed);
+        for (unsigned off = threadIdx.x * 16u; off < kE8Resident * 4u; off += kGroupThreads * 16u)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(dst0 + off), "l"(src0 + off) : "memory");
+        asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+    } else {
+        // Replicated table; entry order follows the raw stored bits (true index ^ 0x100 on 9 bits).
         const int chunk = threadIdx.x & 7;
         for (int e = threadIdx.x >> 3; e < 512; e += kGroupThreads / 8) {
             const uint2 v = __ldg(p.table16 + (e ^ 0x100));
@@ -454,9 +507,13 @@ __global__ void __launch_bounds__(kGroupThreads, 1) gemv_group_kernel(const __gr
 
     if (warp >= kMainWarps) {
         // ---- correction warps
-        const uint2 craw = __ldg(p.table16 + 511);      // what the main loop adds for a marker: entry (3,127), both halves
-        const float2 c01 = __half22float2(*reinterpret_cast<const __half2*>(&craw.x));
-        const float2 c23 = __half22float2(*reinterpret_cast<const __half2*>(&craw.y));
+        // What the main loop adds for a marker: E8-D4 entry (3,127) in both halves; E8 entry 65535 is zero.
+        float2 c01 = make_float2(0.f, 0.f), c23 = make_float2(0.f, 0.f);
+        if constexpr (KIND == EPTQ_E8D4) {
+            const uint2 craw = __ldg(p.table16 + 511);
+            c01 = __half22float2(*reinterpret_cast<const __half2*>(&craw.x));
+            c23 = __half22float2(*reinterpret_cast<const __half2*>(&craw.y));
+        }
         bool waited = false;
         const int cw = blockIdx.x * kCorrWarps + (warp - kMainWarps);
         int l = 0;
@@ -472,7 +529,7 @@ __global__ void __launch_bounds__(kGroupThreads, 1) gemv_group_kernel(const __gr
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (n_total <= 0) return;
 #pragma unroll
-    for (int i = 0; i < kRing; ++i) {
+    for (int i = 0; i < RING; ++i) {
         if (i < n_total) {
             xr0[i] = __ldg(xfirst.px);
             if (p.B > 1) xr1[i] = __ldg(xfirst.px + xfirst.N);
@@ -572,11 +629,75 @@ __global__ void __launch_bounds__(kGroupThreads, 1) gemv_group_kernel(const __gr
         }                                                                                                    \
     }
 
-    for (;;) {
-        EPTQ_GROUP_STEP(0)
-        EPTQ_GROUP_STEP(1)
-        EPTQ_GROUP_STEP(2)
+    // E8: all 16 lookups of a strip are issued before the first is used, so that the round trip of the
+    // non-resident ones (L2) is paid once per strip and overlaps the other warps' work.
+#define EPTQ_GROUP_STEP_E8(I)                                                                                \
+    {                                                                                                        \
+        if (todo == 0) break;                                                                                \
+        const uint4 ca = qa[I], cb = qb[I];                                                                  \
+        const float hx = __half2float(hr[I]) * cscale;                                                       \
+        unsigned* wslab = slab + par * 64;                                                                   \
+        wslab[lane] = split_pieces(__half2float(xr0[I]) * hx);                                               \
+        if (p.B > 1) wslab[32 + lane] = split_pieces(__half2float(xr1[I]) * hx);                             \
+        if (pf_todo > 0) {                                                                                   \
+            qa[I] = ldg_stream(pf.pa);                                                                       \
+            qb[I] = ldg_stream(pf.pb);                                                                       \
+            hr[I] = __ldg(pf.ph);                                                                            \
+            xr0[I] = __ldg(pf.px);                                                                           \
+            if (p.B > 1) xr1[I] = __ldg(pf.px + pf.N);                                                       \
+            step(pf);                                                                                        \
+            --pf_todo;                                                                                       \
+        }                                                                                                    \
+        const unsigned qw[8] = {ca.x ^ 0x80008000u, ca.y ^ 0x80008000u, ca.z ^ 0x80008000u, ca.w ^ 0x80008000u, \
+                                cb.x ^ 0x80008000u, cb.y ^ 0x80008000u, cb.z ^ 0x80008000u, cb.w ^ 0x80008000u}; \
+        unsigned ent[16];                                                                                    \
+        _Pragma("unroll")                                                                                    \
+        for (int k = 0; k < 8; ++k) {                                                                        \
+            ent[2 * k] = e8_lookup(qw[k] & 0xFFFFu, tbase_e8, p.packed);                                     \
+            ent[2 * k + 1] = e8_lookup(qw[k] >> 16, tbase_e8, p.packed);                                     \
+        }                                                                                                    \
+        __syncwarp();                                                                                        \
+        const uint4 w0 = *reinterpret_cast<const uint4*>(my_slab + par * 64);                                \
+        const uint4 w1 = *reinterpret_cast<const uint4*>(my_slab + par * 64 + 4);                            \
+        par ^= 1;                                                                                            \
+        const unsigned wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};                             \
+        _Pragma("unroll")                                                                                    \
+        for (int m = 0; m < 4; ++m) {                                                                        \
+            unsigned a0[4], a1[4], b0r[4], b1r[4];                                                           \
+            e8_decode(ent[2 * m], a0);                                                                       \
+            e8_decode(ent[2 * m + 1], a1);                                                                   \
+            e8_decode(ent[8 + 2 * m], b0r);                                                                  \
+            e8_decode(ent[8 + 2 * m + 1], b1r);                                                              \
+            const unsigned b0 = prmt(wv[2 * m], 0u, sel), b1 = prmt(wv[2 * m + 1], 0u, sel);                 \
+            mma_f16r(acc[0][0], a0[0], a0[1], a1[0], a1[1], b0, b1);                                         \
+            mma_f16r(acc[0][1], a0[2], a0[3], a1[2], a1[3], b0, b1);                                         \
+            mma_f16r(acc[1][0], b0r[0], b0r[1], b1r[0], b1r[1], b0, b1);                                     \
+            mma_f16r(acc[1][1], b0r[2], b0r[3], b1r[2], b1r[3], b0, b1);                                     \
+        }                                                                                                    \
+        --todo;                                                                                              \
+        if (--cleft == 0 || todo == 0) {                                                                     \
+            flush(cl, crt);                                                                                  \
+            if (cleft == 0) {                                                                                \
+                if (++crt == p.L[cl].row_tiles) { crt = 0; ++cl; }                                           \
+                if (cl < p.n_layers) { cleft = p.L[cl].ns; cscale = p.L[cl].x_scale; }                       \
+            }                                                                                                \
+        }                                                                                                    \
     }
+
+    if constexpr (KIND == EPTQ_E8) {
+        const unsigned tbase_e8 = base + kE8TableOffset;
+        for (;;) {
+            EPTQ_GROUP_STEP_E8(0)
+            EPTQ_GROUP_STEP_E8(1)
+        }
+    } else {
+        for (;;) {
+            EPTQ_GROUP_STEP(0)
+            EPTQ_GROUP_STEP(1)
+            EPTQ_GROUP_STEP(2)
+        }
+    }
+#undef EPTQ_GROUP_STEP_E8
 #undef EPTQ_GROUP_STEP
 }
 
@@ -629,11 +750,16 @@ bool plan_group(const EptqLayer* layers, int n, int B, int n_sms, GroupPlan& pla
 }
 
 bool group_layer_supported(const EptqLayer& L) {
-    return L.quantizer == EPTQ_E8D4 && L.table16 != nullptr && L.S_group == nullptr && L.M > 0 && L.N > 0 &&
-           (L.N % 32) == 0 && L.h_absmax > 0.f && L.Q != nullptr && L.g != nullptr && L.h != nullptr &&
-           L.O_row_ptr != nullptr && (L.n_masked == 0 || (L.O_vals != nullptr && L.O_col != nullptr)) &&
-           aligned16(L.Q) && aligned16(L.table16) && aligned16(L.g) && (L.bias == nullptr || aligned16(L.bias)) &&
-           (L.n_masked == 0 || aligned16(L.O_vals));
+    const bool common = L.S_group == nullptr && L.M > 0 && L.N > 0 && (L.N % 32) == 0 && L.h_absmax > 0.f &&
+                        L.Q != nullptr && L.g != nullptr && L.h != nullptr && L.O_row_ptr != nullptr &&
+                        (L.n_masked == 0 || (L.O_vals != nullptr && L.O_col != nullptr)) && aligned16(L.Q) &&
+                        aligned16(L.g) && (L.bias == nullptr || aligned16(L.bias)) &&
+                        (L.n_masked == 0 || aligned16(L.O_vals));
+    if (!common) return false;
+    if (L.quantizer == EPTQ_E8D4) return L.table16 != nullptr && aligned16(L.table16);
+    if (L.quantizer == EPTQ_E8)
+        return L.table_packed != nullptr && aligned16(L.table_packed) && L.table_packed_scale > 0.f;
+    return false;
 }
 
 }  // namespace
@@ -642,7 +768,9 @@ bool group_gemv_supported(const EptqLayer* layers, int n, int B) {
     if (layers == nullptr || n < 1 || n > kMaxGroupLayers || B < 1 || B > 2) return false;
     for (int i = 0; i < n; ++i) {
         if (!group_layer_supported(layers[i])) return false;
-        if (layers[i].table16 != layers[0].table16) return false;          // one codebook per launch
+        if (layers[i].quantizer != layers[0].quantizer || layers[i].table16 != layers[0].table16 ||
+            layers[i].table_packed != layers[0].table_packed ||
+            layers[i].table_packed_scale != layers[0].table_packed_scale) return false;   // one codebook per launch
     }
     return true;
 }
@@ -666,7 +794,9 @@ int launch_gemv_group(const EptqLayer* layers, int n, const EptqFusion* fusions,
     static std::mutex args_mutex;
     std::lock_guard<std::mutex> lock(args_mutex);
     GroupArgs& a = args;
+    const bool e8 = layers[0].quantizer == EPTQ_E8;
     a.table16 = reinterpret_cast<const uint2*>(layers[0].table16);
+    a.packed = e8 ? layers[0].table_packed : nullptr;
     a.counters = reinterpret_cast<unsigned*>(workspace);
     a.acc = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + kCounterBytes);
     a.W = plan.W;
@@ -718,7 +848,7 @@ int launch_gemv_group(const EptqLayer* layers, int n, const EptqFusion* fusions,
         int e = 0;
         std::frexp(L.h_absmax, &e);            // h_absmax = m * 2^e, m in [0.5, 1)  =>  2^-e <= 1/h_absmax
         G.x_scale = std::ldexp(1.0f, -e);
-        G.x_inv_scale = std::ldexp(1.0f, e);
+        G.x_inv_scale = std::ldexp(1.0f, e) * (e8 ? L.table_packed_scale : 1.0f);   // E8 entries are in lattice units
         G.residual = nullptr; G.position = nullptr; G.inv_freq = nullptr;
         G.y_op = EPTQ_Y_STORE; G.max_len = 0; G.rope_scaling = 1.f;
         if (fusions != nullptr) {
@@ -754,21 +884,25 @@ int launch_gemv_group(const EptqLayer* layers, int n, const EptqFusion* fusions,
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return EPTQ_ERR_LAUNCH;
     if (!attr_done[dev]) {
-        if (cudaFuncSetAttribute(gemv_group_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGroupSmemBytes) != cudaSuccess)
+        if (cudaFuncSetAttribute(gemv_group_kernel<EPTQ_E8D4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 kGroupSmemBytes) != cudaSuccess ||
+            cudaFuncSetAttribute(gemv_group_kernel<EPTQ_E8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 kE8SmemBytes) != cudaSuccess)
             return EPTQ_ERR_LAUNCH;
         attr_done[dev] = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(n_sms);
     cfg.blockDim = dim3(kGroupThreads);
-    cfg.dynamicSmemBytes = kGroupSmemBytes;
+    cfg.dynamicSmemBytes = e8 ? kE8SmemBytes : kGroupSmemBytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    const cudaError_t err = cudaLaunchKernelEx(&cfg, gemv_group_kernel, a);
+    const cudaError_t err = e8 ? cudaLaunchKernelEx(&cfg, gemv_group_kernel<EPTQ_E8>, a)
+                               : cudaLaunchKernelEx(&cfg, gemv_group_kernel<EPTQ_E8D4>, a);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return err == cudaSuccess ? EPTQ_OK : EPTQ_ERR_LAUNCH;
 }

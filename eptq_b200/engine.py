@@ -40,11 +40,15 @@ class DecoderLayerWeights:
 
 
 def apply_group(layers: Sequence[Callable], x: torch.Tensor) -> List[torch.Tensor]:
-    """layers[i](x) for all i; one kernel launch when the layers are E8-D4 EPTQLinear modules and the
-    batch is small enough for the persistent GEMV, otherwise one call per layer."""
+    """layers[i](x) for all i; one kernel launch when the layers are EPTQLinear modules of one codebook
+    and the batch is small enough for the persistent GEMV, otherwise one call per layer."""
     if (x.is_cuda and x.shape[0] <= 2 and all(isinstance(l, EPTQLinear) for l in layers)
-            and all(l.quantizer_type == "e8_d4" and l.S_group is None and l.in_features % 32 == 0 for l in layers)):
-        return forward_group(list(layers), [x] * len(layers))
+            and all(l.quantizer_type == layers[0].quantizer_type and l.S_group is None
+                    and l.in_features % 32 == 0 for l in layers)):
+        try:
+            return forward_group(list(layers), [x] * len(layers))
+        except RuntimeError:
+            pass                                   # not eligible as one launch (e.g. a warped E8 table)
     return [l(x) for l in layers]
 
 
@@ -150,9 +154,11 @@ class LlamaDecodeEngine:
     # ---- one token, everything fused into the GEMV launches -----------------------------------------
     def _fusable(self) -> bool:
         if self._fused is None:
-            ok = all(isinstance(m, EPTQLinear) and m.quantizer_type == "e8_d4" and m.S_group is None
-                     and m.in_features % 32 == 0 and m.out_features % 128 == 0
-                     for L in self.layers for m in (L.q, L.k, L.v, L.o, L.gate, L.up, L.down))
+            mods = [m for L in self.layers for m in (L.q, L.k, L.v, L.o, L.gate, L.up, L.down)]
+            ok = all(isinstance(m, EPTQLinear) and m.quantizer_type == mods[0].quantizer_type and m.S_group is None
+                     and m.in_features % 32 == 0 and m.out_features % 128 == 0 for m in mods)
+            if ok and mods[0].quantizer_type == "e8_lattice":
+                ok = bool(mods[0].descriptor().table_packed)        # E8 needs a table that packs
             self._fused = self._build_fused() if ok else False
         return self._fused is not False
 

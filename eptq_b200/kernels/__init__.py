@@ -150,6 +150,55 @@ def d4_table8(table: torch.Tensor) -> Optional[Tuple[torch.Tensor, float]]:
     return res
 
 
+_packed_cache: Dict[tuple, Optional[Tuple[torch.Tensor, float]]] = {}
+_E8_FIELD = (0, 4, 1, 5, 2, 6, 3, 7)      # 4-bit field index of dimension d; field f sits at bit 2 + 4 f
+
+
+def pack_e8_table(table: torch.Tensor) -> Optional[Tuple[torch.Tensor, float]]:
+    """(int32 (65536,) tensor on the table's device, scale) with the E8 table written as
+    scale * half-integer lattice coordinates, one packed word per entry (layout: `table_packed` in
+    include/eptq_b200.h); entries past the table's rows decode to the zero vector.  None if the table is
+    not such a multiple (a radially warped codebook) or has coordinates outside [-3, 3]."""
+    t = table.detach().float()
+    if t.dim() != 2 or t.shape[1] != 8 or t.shape[0] > 65535 or t.shape[0] == 0:
+        return None
+    nz = t.abs()[t != 0]
+    if nz.numel() == 0:
+        return None
+    scale = 2.0 * float(nz.min())
+    twice = torch.round(t * (2.0 / scale))
+    # 1e-3: a table already rounded to fp16 still packs (its entries are within 5e-4 of the lattice)
+    if float((twice * (scale / 2.0) - t).abs().max()) > 1e-3 * scale or float(twice.abs().max()) > 6:
+        return None
+    n = (twice + 6).to(torch.int64)                                         # 0..12
+    full = torch.full((65536, 8), 6, dtype=torch.int64, device=t.device)
+    full[: t.shape[0]] = n
+    word = torch.zeros(65536, dtype=torch.int64, device=t.device)
+    for d, f in enumerate(_E8_FIELD):
+        word |= full[:, d] << (2 + 4 * f)
+    word = (word & 0xFFFFFFFF) | (word >> 32)                               # the last field wraps around
+    word = torch.where(word >= 2 ** 31, word - 2 ** 32, word).to(torch.int32)
+    return word.contiguous(), scale
+
+
+def unpack_e8_table(word: torch.Tensor, scale: float) -> torch.Tensor:
+    """Inverse of pack_e8_table (fp32 (65536, 8)); what the kernel's decode computes."""
+    w = word.to(torch.int64) & 0xFFFFFFFF
+    w = w | ((w & 0x3) << 32)
+    cols = [((w >> (2 + 4 * f)) & 0xF).float() for f in _E8_FIELD]
+    return (torch.stack(cols, dim=1) - 6.0) * (scale / 2.0)
+
+
+def e8_packed(table: torch.Tensor) -> Optional[Tuple[torch.Tensor, float]]:
+    """pack_e8_table cached per table tensor (one host sync the first time)."""
+    key = (table.data_ptr(), table.device, table.dtype, tuple(table.shape), table._version)
+    if key not in _packed_cache:
+        if len(_packed_cache) > 64:
+            _packed_cache.clear()
+        _packed_cache[key] = pack_e8_table(table)
+    return _packed_cache[key]
+
+
 _absmax_cache: Dict[tuple, float] = {}
 
 
@@ -182,7 +231,13 @@ def _make_desc(quantizer_type: str, Q, table32, table16, g, h, O_vals, O_col, O_
     d.O_vals, d.O_col, d.O_row_ptr = _ptr(O_vals), _ptr(O_col), O_row_ptr.data_ptr()
     d.bias, d.S_group = _ptr(bias), _ptr(S_group)
     d.table8, d.table8_scale = None, 0.0
-    d.h_absmax = h_absmax(h) if (quantizer_type == "e8_d4" and Q.is_cuda) else 0.0
+    d.h_absmax = h_absmax(h) if Q.is_cuda else 0.0
+    d.table_packed, d.table_packed_scale = None, 0.0
+    if quantizer_type == "e8_lattice" and Q.is_cuda:
+        packed = e8_packed(table32 if table32 is not None else table16)
+        if packed is not None:
+            d._keep = packed[0]                  # keep the device table alive as long as the descriptor
+            d.table_packed, d.table_packed_scale = packed[0].data_ptr(), packed[1]
     if quantizer_type == "e8_d4" and Q.is_cuda:
         t8 = d4_table8(table32 if table32 is not None else table16)
         if t8 is not None:

@@ -21,7 +21,7 @@
 extern "C" {
 #endif
 
-#define EPTQ_ABI_VERSION 1
+#define EPTQ_ABI_VERSION 2
 
 typedef enum EptqStatus {
     EPTQ_OK = 0,
@@ -55,6 +55,15 @@ enum { EPTQ_E8 = 0, EPTQ_E8D4 = 1 };
  *              (table = raw * table8_scale) as FP8 E4M3 bytes, 4 per code, made
  *              by eptq_prepare_d4_table8.  Enables the tensor-core GEMV; NULL
  *              selects the general kernel.
+ *   table_packed  E8 only, optional: the table as table_packed_scale * (half-integer
+ *              lattice coordinates), one 32-bit word per entry, 65536 words (entry
+ *              65535 = the zero vector).  Coordinate c of dimension d is stored as
+ *              n = 2c + 6 (0..12) in a 4-bit field at bit 2 + 4*f(d) with
+ *              f = {0, 4, 1, 5, 2, 6, 3, 7} for d = 0..7; the last field wraps
+ *              around (its low two bits are bits 31:30, its high two bits 1:0).
+ *              Enables the persistent tensor-core GEMV for E8 layers; NULL selects
+ *              the general kernel.  A table that is not such a multiple (a radially
+ *              warped codebook) has no packed form.
  *   g, h       fp16 row scales (8*M) and column scales (N).
  *   O_vals     fp16 (n_masked, 8), ordered by row-major position of the markers.
  *   O_col      int32 (n_masked) column of each marker, same order.
@@ -83,6 +92,9 @@ typedef struct EptqLayer {
     const uint8_t* table8;
     float table8_scale;
     float h_absmax;           /* max |h|, or 0 if not known (then the persistent GEMV is not used) */
+    const uint32_t* table_packed; /* E8 only, optional: 65536 packed entries, see below */
+    float table_packed_scale;
+    int32_t reserved;
 } EptqLayer;
 
 /* ABI version of the loaded library (EPTQ_ABI_VERSION at build time). */

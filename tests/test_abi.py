@@ -29,7 +29,7 @@ def test_binding_covers_all_declared(built_library):
     from eptq_b200 import _lib
     assert sorted(_lib.EXPORTS) == declared_functions()
     lib = _lib.load()
-    assert lib.eptq_abi_version() == 1
+    assert lib.eptq_abi_version() == 2
     assert lib.eptq_strerror(0) == b"ok"
     assert b"workspace" in lib.eptq_strerror(5)
     assert lib.eptq_workspace_bytes(512, 4096, 1) > 0

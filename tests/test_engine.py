@@ -52,7 +52,7 @@ def test_engine_greedy_state_cpu():
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("quantizer_type,hidden,heads,inter", [("e8_d4", 256, 8, 704), ("e8_lattice", 256, 8, 704),
-                                                              ("e8_d4", 512, 4, 768)])
+                                                              ("e8_d4", 512, 4, 768), ("e8_lattice", 512, 4, 768)])
 def test_engine_graph_decode_gpu(quantizer_type, hidden, heads, inter):
     from eptq_b200.kernels.patch import load_quantized_model
     from eptq_b200.quantizers import E8D4Quantizer, E8LatticeQuantizer
@@ -86,8 +86,8 @@ def test_engine_graph_decode_gpu(quantizer_type, hidden, heads, inter):
         a = eng.forward(nxt, p1).float()
         b = plain.forward_reference(nxt, p1).float()
         assert float((a - b).abs().max()) <= 2e-2 * scale
-        # head size 128 with E8-D4 layers takes the fully fused step (norm, rotary, cache, residual in the GEMVs)
-        assert (eng._fused not in (None, False)) == (quantizer_type == "e8_d4" and hidden // heads == 128)
+        # head size 128 takes the fully fused step (norm, rotary, cache, residual in the GEMVs)
+        assert (eng._fused not in (None, False)) == (hidden // heads == 128)
     eager, _ = eng.decode(ids, 12, use_graph=False)
     graphed, stats = eng.decode(ids, 12, use_graph=True)
     assert eng.graph is not None

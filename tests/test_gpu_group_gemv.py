@@ -53,8 +53,33 @@ def test_group_equals_single_calls_and_repeats():
 
 def test_group_rejects_ineligible_sets():
     e8 = EPTQLinear.from_quantized_data(make_layer(64, 64, seed=1), torch.from_numpy(oracle.e8_table(1.6)), "e8_lattice").to(DEV)
-    with pytest.raises(RuntimeError):
-        forward_group([e8], [make_activations(1, 64).to(DEV)])
     d4 = EPTQLinear.from_quantized_data(make_layer(64, 64, seed=1), TABLE, "e8_d4").to(DEV)
+    with pytest.raises(RuntimeError):                                  # one codebook per launch
+        forward_group([e8, d4], [make_activations(1, 64).to(DEV)] * 2)
+    scaled = EPTQLinear.from_quantized_data(make_layer(256, 64, seed=2, qb_size=128), TABLE, "e8_d4").to(DEV)
+    with pytest.raises(RuntimeError):                                  # group scales run on the general kernel
+        forward_group([scaled], [make_activations(1, 64).to(DEV)])
     with pytest.raises(RuntimeError):
         forward_group([d4], [make_activations(3, 64).to(DEV)])        # batch 3 is not a group batch
+
+
+@pytest.mark.parametrize("B", [1, 2])
+def test_e8_group_matches_oracle(B):
+    """E8 layers: packed table partly in shared memory, partly read through L2."""
+    e8 = oracle.e8_table(1.6)
+    table = torch.from_numpy(e8)
+    shapes = [(4096, 4096), (1024, 2048), (2048, 11008), (64, 64)]
+    qds = [make_layer(o, i, seed=3 * o + i, bias=(k == 1)) for k, (o, i) in enumerate(shapes)]
+    lins = [EPTQLinear.from_quantized_data(qd, table, "e8_lattice").to(DEV) for qd in qds]
+    xs = [make_activations(B, i, seed=i + 7) for _, i in shapes]
+
+    def ref(qd, x):
+        W16 = oracle.dequantize_layer(util.qld_arrays(qd), e8)
+        return oracle.linear_reference(x.numpy(), W16, None if qd.bias is None else qd.bias.numpy())
+    for _ in range(2):
+        ys = forward_group(lins, [x.to(DEV) for x in xs])
+    for qd, x, y in zip(qds, xs, ys):
+        assert util.max_rel_err(y.float().cpu().numpy(), ref(qd, x)) <= util.REL_TOL
+    # the single-layer entry point takes the same kernel for a layer this large
+    y0 = lins[0](xs[0].to(DEV))
+    assert util.max_rel_err(y0.float().cpu().numpy(), ref(qds[0], xs[0])) <= util.REL_TOL

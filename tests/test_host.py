@@ -84,3 +84,17 @@ def test_cpu_tensor_raises_instead_of_falling_back(built_library):
     with pytest.raises(RuntimeError, match="CUDA"):
         e8d4_forward(lin.Q, lin._codebook, lin.g, lin.h, torch.zeros(1, 8, dtype=torch.float16),
                      lin.O_vals, lin.O_col, lin.O_row_ptr, torch.empty(0, dtype=torch.float16))
+
+
+def test_e8_table_packs_and_unpacks():
+    """The packed E8 table (4 bits per coordinate) reproduces the fp32 table; odd tables are refused."""
+    import oracle
+    from eptq_b200.kernels import pack_e8_table, unpack_e8_table
+    t = torch.from_numpy(oracle.e8_table(1.6))
+    word, scale = pack_e8_table(t)
+    assert word.shape == (65536,) and word.dtype == torch.int32 and abs(scale - 1 / 1.6) < 1e-6
+    back = unpack_e8_table(word, scale)
+    assert float((back[:65535] - t).abs().max()) < 1e-6
+    assert float(back[65535].abs().max()) == 0.0                 # marker slot decodes to zero
+    assert pack_e8_table(t * (1 + 0.05 * t.abs())) is None       # radially warped: not a lattice multiple
+    assert pack_e8_table(t[:, :4]) is None
