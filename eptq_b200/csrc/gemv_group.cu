@@ -87,6 +87,22 @@ struct GroupArgs {
 
 namespace {
 
+// Phase timestamps for latency studies: compiled in only with -DEPTQ_GROUP_TRACE (never in the shipped
+// library).  Slot k of block b is g_group_trace[b * 8 + k], in nanoseconds of the global timer.
+#ifdef EPTQ_GROUP_TRACE
+__device__ unsigned long long* g_group_trace = nullptr;
+__device__ __forceinline__ void trace_mark(int slot) {
+    if ((threadIdx.x & 31) == 0 && g_group_trace != nullptr) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        g_group_trace[blockIdx.x * 8 + slot] = t;
+    }
+}
+#define EPTQ_TRACE(slot, cond) do { if (cond) trace_mark(slot); } while (0)
+#else
+#define EPTQ_TRACE(slot, cond) do { } while (0)
+#endif
+
 constexpr int kMainWarps = 14;
 constexpr int kCorrWarps = 2;
 constexpr int kGroupThreads = (kMainWarps + kCorrWarps) * 32;
@@ -212,8 +228,7 @@ __device__ __forceinline__ Affine load_affine(const GroupLayer& L, int rt, int l
 // 4 correction quarters) reads the tile's accumulators, zeroes them for the next launch and writes y.
 __device__ __forceinline__ void arrive_and_finalize(const GroupArgs& p, const GroupLayer& L, int rt, int n_main,
                                                     int lane, const Affine& aff, const float* inv_rms) {
-    __threadfence();                                                 // this lane's adds are performed before the ticket
-    __syncwarp();
+    __syncwarp();      // orders every lane's adds before lane 0's release below (release is cumulative)
     unsigned ticket = 0;
     unsigned* ctr = p.counters + L.tile0 + rt;
     if (lane == 0)
@@ -221,6 +236,7 @@ __device__ __forceinline__ void arrive_and_finalize(const GroupArgs& p, const Gr
     ticket = __shfl_sync(0xffffffffu, ticket, 0);
     if (ticket != static_cast<unsigned>(n_main) + 3u) return;
     if (lane == 0) *ctr = 0u;
+    __syncwarp();      // lane 0's acquire, then the barrier: every lane sees the other warps' adds
     __threadfence();
     const int row = rt * 16 + (lane >> 1);
     const int o = row * 8 + (lane & 1) * 4;
@@ -373,9 +389,10 @@ struct StripIter {
         s = pos;
         l = 0;
         while (l + 1 < p.n_layers && p.L[l + 1].strip0 <= pos) ++l;
-        const long long local = pos - p.L[l].strip0;
-        rt = static_cast<int>(local / p.L[l].ns);
-        strip = static_cast<int>(local - static_cast<long long>(rt) * p.L[l].ns);
+        const unsigned local = static_cast<unsigned>(pos - p.L[l].strip0);     // < W < 2^32
+        const unsigned ns = static_cast<unsigned>(p.L[l].ns);
+        rt = static_cast<int>(local / ns);
+        strip = static_cast<int>(local - static_cast<unsigned>(rt) * ns);
     }
 };
 
@@ -389,14 +406,17 @@ __global__ void __launch_bounds__(kGroupThreads, 1) gemv_group_kernel(const __gr
     unsigned char* tab = smem_raw + (kTableAddr - base);       // generic pointer to shared address 0x10000
 
     asm volatile("griddepcontrol.launch_dependents;");
+    EPTQ_TRACE(0, warp == 0);
 
     // ---- main warps: find the first strips and start their loads before anything else, so that the DRAM
     // round trip runs under the table build.  (Correction warps carry the same variables unused.)
     const bool is_main = warp < kMainWarps;
     const int g = lane >> 2, t = lane & 3;
     const int gw = is_main ? blockIdx.x * kMainWarps + warp : p.nw;
-    const long long s_begin = gw < p.nw ? (static_cast<long long>(gw) * p.W) / p.nw : p.W;
-    const long long s_end = gw < p.nw ? (static_cast<long long>(gw + 1) * p.W) / p.nw : p.W;
+    // W * nw < 2^32 (checked on the host): unsigned 32-bit arithmetic is exact and much cheaper than 64-bit division.
+    const unsigned W32 = static_cast<unsigned>(p.W), nw32 = static_cast<unsigned>(p.nw);
+    const long long s_begin = gw < p.nw ? (static_cast<unsigned>(gw) * W32) / nw32 : W32;
+    const long long s_end = gw < p.nw ? ((static_cast<unsigned>(gw) + 1u) * W32) / nw32 : W32;
     const int n_total = static_cast<int>(s_end - s_begin);
 
     unsigned* slab = reinterpret_cast<unsigned*>(smem_raw) + warp * 128;     // [parity][batch][32] words
@@ -455,6 +475,7 @@ __global__ void __launch_bounds__(kGroupThreads, 1) gemv_group_kernel(const __gr
             --pf_todo;
         }
     }
+    EPTQ_TRACE(1, warp == 0);
     if constexpr (KIND == EPTQ_E8) {
         // Resident part of the packed table: asynchronous 16-byte copies, no registers in between.
         const unsigned dst0 = base + kE8TableOffset;
@@ -463,15 +484,18 @@ __global__ void __launch_bounds__(kGroupThreads, 1) gemv_group_kernel(const __gr
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(dst0 + off), "l"(src0 + off) : "memory");
         asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
     } else {
-        // Replicated table; entry order follows the raw stored bits (true index ^ 0x100 on 9 bits).
-        const int chunk = threadIdx.x & 7;
-        for (int e = threadIdx.x >> 3; e < 512; e += kGroupThreads / 8) {
-            const uint2 v = __ldg(p.table16 + (e ^ 0x100));
-            *reinterpret_cast<uint4*>(tab + e * 128 + chunk * 16) = make_uint4(v.x, v.y, v.x, v.y);
-        }
+        // Replicated table; entry order follows the raw stored bits (true index ^ 0x100 on 9 bits).  One load
+        // per thread (512 entries, 512 threads), then the 16 copies of that entry: one memory round trip.
+        static_assert(kGroupThreads == 512, "one table entry per thread");
+        const int e = threadIdx.x;
+        const uint2 v = __ldg(p.table16 + (e ^ 0x100));
+        const uint4 vv = make_uint4(v.x, v.y, v.x, v.y);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(tab + e * 128 + ((c + e) & 7) * 16) = vv;
     }
 
     __syncthreads();                                   // table complete (all 16 warps reach this once)
+    EPTQ_TRACE(2, warp == 0);
 
     // Fused RMSNorm of the input: every layer of the launch reads the same x; the column weight of the
     // norm is folded into h by the caller, the row factor rsqrt(mean(x^2) + eps) is applied by the
@@ -523,10 +547,12 @@ __global__ void __launch_bounds__(kGroupThreads, 1) gemv_group_kernel(const __gr
                 if (!waited) { asm volatile("griddepcontrol.wait;" ::: "memory"); waited = true; }
             });
         }
+        EPTQ_TRACE(7, warp == kMainWarps);
         return;
     }
 
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    EPTQ_TRACE(3, warp == 0);
     if (n_total <= 0) return;
 #pragma unroll
     for (int i = 0; i < RING; ++i) {
@@ -543,6 +569,7 @@ __global__ void __launch_bounds__(kGroupThreads, 1) gemv_group_kernel(const __gr
     const unsigned sel = (g & 1) ? ((((pbyte + 1) << 12) | (pbyte << 8)) | 0x0044u) : (0x4400u | ((pbyte + 1) << 4) | pbyte);
     const unsigned* my_slab = slab + (g >> 2) * 32 + 8 * t;
 
+    EPTQ_TRACE(4, warp == 0);
     int cl = cur_l0, crt = cur_rt0, cleft = cur_left0;   // compute position: layer, row tile, strips left in it
     float cscale = p.L[cl].x_scale;
     int todo = n_total;
@@ -556,6 +583,7 @@ __global__ void __launch_bounds__(kGroupThreads, 1) gemv_group_kernel(const __gr
             for (int c = 0; c < 4; ++c) acc[a][b][c] = 0.f;
 
     auto flush = [&](int l, int rt) {
+        EPTQ_TRACE(5, warp == 0);
         const GroupLayer& L = p.L[l];
         const Affine aff = load_affine(L, rt, lane);   // in flight while the ticket travels
         int first_warp;
@@ -578,6 +606,7 @@ __global__ void __launch_bounds__(kGroupThreads, 1) gemv_group_kernel(const __gr
                     red_add4(dst + (g + 8 * rg) * 8 + hf * 4, tot[0], tot[1], tot[2], tot[3]);
             }
         arrive_and_finalize(p, L, rt, n_main, lane, aff, inv_rms);
+        EPTQ_TRACE(6, warp == 0);
     };
 
 #define EPTQ_GROUP_STEP(I)                                                                                   \
@@ -908,3 +937,9 @@ int launch_gemv_group(const EptqLayer* layers, int n, const EptqFusion* fusions,
 }
 
 }  // namespace eptq
+
+#ifdef EPTQ_GROUP_TRACE
+extern "C" int eptq_debug_set_group_trace(unsigned long long* device_buffer) {
+    return cudaMemcpyToSymbol(eptq::g_group_trace, &device_buffer, sizeof(device_buffer)) == cudaSuccess ? 0 : 6;
+}
+#endif
