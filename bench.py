@@ -22,8 +22,9 @@ batch B (default 1), i.e. the quantized-linear work of one decode token.
             reference's dequantize_layer, torch CPU matmul) on a bounded sample
 
 With --gpus N > 1 (torchrun) the linears are sharded tensor-parallel
-(q/k/v/gate/up by output rows, o/down by input columns with an NCCL
-all-reduce) and the whole-model bytes are divided by the slowest rank's time.
+(q/k/v/gate/up by output rows, o/down by input columns followed by an
+all-reduce: the library's one-shot push kernel over peer memory, or NCCL with
+--nccl) and the whole-model bytes are divided by the slowest rank's time.
 
 `--impl reference` times the CPU path alone, on rank 0.
 """
@@ -196,8 +197,25 @@ def run_gpu_arm(args):
     lib = _lib.load()
     B = args.batch
     n_layers = args.layers
+    # Row-parallel partial outputs: this library's one-shot push all-reduce over peer memory, or NCCL.
+    comm = None
+    if world > 1 and not args.nccl:
+        from eptq_b200.comm import PushAllReduce
+        comm = PushAllReduce(dist.group.WORLD, B * 8192, dev)
 
-    table = E8D4Quantizer(radius=RADIUS).codes.to(dev)
+    def all_reduce(y):
+        if comm is not None and y.numel() <= comm.n_max:
+            comm.all_reduce_(y)
+        else:
+            dist.all_reduce(y)
+
+    if args.codebook == "e8":                       # not the headline: lets the E8 kernel be the profiled workload
+        from eptq_b200.quantizers import E8LatticeQuantizer
+        qz0 = E8LatticeQuantizer(radius=1.6)
+        qz0.remove_last()
+        table, kind = qz0.points.to(dev), "e8_lattice"
+    else:
+        table, kind = E8D4Quantizer(radius=RADIUS).codes.to(dev), KIND
     layers, total_bytes = [], 0
     for li in range(n_layers):
         for i, (name, (out_f, in_f)) in enumerate(LLAMA2_7B_LINEARS.items()):
@@ -205,7 +223,7 @@ def run_gpu_arm(args):
             total_bytes += algorithmic_bytes(out_f, in_f, qd.O.shape[0], B)
             if world > 1:
                 qd = shard_layer(qd, name, rank, world)
-            lin = EPTQLinear.from_quantized_data(qd, table, KIND)
+            lin = EPTQLinear.from_quantized_data(qd, table, kind)
             lin.tp_row_parallel = world > 1 and name.split(".")[-1] in ROW_PARALLEL
             layers.append((name, lin))
     torch.cuda.synchronize()
@@ -251,7 +269,7 @@ def run_gpu_arm(args):
                     if st != 0:
                         raise RuntimeError(lib.eptq_strerror(st).decode())
             for y in reduce_ys:
-                dist.all_reduce(y)
+                all_reduce(y)
 
     side = torch.cuda.Stream(device=dev)
     with torch.cuda.stream(side):
@@ -332,7 +350,7 @@ def run_gpu_arm(args):
                 outs = [l(x_dev[l.in_features]) for l in chunk]
             for l, o in zip(chunk, outs):
                 if l.tp_row_parallel:
-                    dist.all_reduce(o)
+                    all_reduce(o)
             y = outs[-1]
         y_host.copy_(y, non_blocking=True)
 
@@ -355,7 +373,7 @@ def run_gpu_arm(args):
     # The same layer set with the E8 codebook (radius 1.6) through the same grouped launch: the codebook of the
     # baseline's first, third and fifth configurations.  Reported as an extra figure.
     e8_stats = None
-    if not args.no_e8 and world == 1 and group > 1:
+    if not args.no_e8 and world == 1 and group > 1 and args.codebook == "e8d4":
         from eptq_b200.quantizers import E8LatticeQuantizer
         qz = E8LatticeQuantizer(radius=1.6)
         qz.remove_last()
@@ -408,14 +426,14 @@ def run_gpu_arm(args):
         ids = torch.randint(0, vocab, (1, 512), generator=torch.Generator().manual_seed(0)).to(dev)
         for qname in ("e8_d4", "e8_lattice"):
             if qname == "e8_d4":
-                tab = table
+                tab = E8D4Quantizer(radius=RADIUS).codes.to(dev)
             else:
                 qz = E8LatticeQuantizer(radius=1.6)
                 qz.remove_last()
                 tab = qz.points.to(dev)
             eng = synthetic_llama_engine(hidden, inter, n_dec, heads, kv, vocab, qname, tab, max_len=512 + 128,
                                          batch=1, device=str(dev), tp_rank=rank, tp_size=world,
-                                         tp_group=dist.group.WORLD if world > 1 else None)
+                                         tp_group=dist.group.WORLD if world > 1 else None, comm=comm)
             eng.decode(ids, 8)
             _, st = eng.decode(ids, 128)
             if world > 1:
@@ -431,6 +449,8 @@ def run_gpu_arm(args):
         decode_stats["config"] = ("llama2-7b architecture, random init, 32 layers, 512-token prompt + 128 greedy "
                                   f"tokens, batch 1, tp{world}, one CUDA graph per token")
 
+    if comm is not None:
+        comm.check()                                   # a device-side wait that ran out would show here
     if world > 1:
         dist.barrier()
         torch.cuda.synchronize()
@@ -452,14 +472,16 @@ def run_gpu_arm(args):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": step_ms, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
         "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": {"workload": "llama2-7b decode layer set, E8-D4 r=1.75, 0.2% critical blocks",
+        "config": {"workload": "llama2-7b decode layer set, " + ("E8-D4 r=1.75" if args.codebook == "e8d4" else "E8 r=1.6")
+                               + ", 0.2% critical blocks",
                    "batch": B, "layers": n_layers, "linears_per_step": len(layers),
                    "l2_policy": "inputs larger than L2 (1.66 GB of indices per step)" if n_layers >= 8 else "reduced layer count: may be L2-resident",
                    "launch_granularity": f"{group} independent linears per launch" if group > 1 else "one launch per linear",
-                   "parallelism": f"tp{world}" if world > 1 else "single"},
+                   "parallelism": f"tp{world}" if world > 1 else "single",
+                   "all_reduce": "none" if world == 1 else ("nccl" if comm is None else "one-shot push kernel over peer memory")},
         "decode_tokens_per_s_linears_only": 1e3 / step_ms * B,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": (52379392 if (group == 7 and B == 1 and world == 1) else None),
+                     "traffic": (52379392 if (group == 7 and B == 1 and world == 1 and args.codebook == "e8d4") else None),
                      "traffic_source": "dram read+write of one 7-linear launch, ncu capture in profiles/",
                      "peak_kind": f"{peak_kind} copy bandwidth",
                      "per_launch_bytes": per_launch_bytes, "per_launch_us": per_launch_us},
@@ -496,6 +518,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true", help="skip the whole-model decode tokens/s arm")
     ap.add_argument("--no-e8", action="store_true", help="skip the E8-codebook layer-set figure")
+    ap.add_argument("--nccl", action="store_true", help="tensor-parallel runs: NCCL all-reduce instead of the push kernel")
+    ap.add_argument("--codebook", default="e8d4", choices=["e8d4", "e8"],
+                    help="codebook of the timed layer set (the headline is e8d4)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

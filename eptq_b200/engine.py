@@ -63,8 +63,9 @@ class LlamaDecodeEngine:
     def __init__(self, layers: List[DecoderLayerWeights], embed: torch.Tensor, final_norm: torch.Tensor,
                  lm_head: torch.Tensor, inv_freq: torch.Tensor, rms_eps: float, head_dim: int,
                  n_heads: int, n_kv_heads: int, max_len: int, batch: int = 1,
-                 rope_scaling: float = 1.0, tp_group=None):
+                 rope_scaling: float = 1.0, tp_group=None, comm=None):
         self.layers = layers
+        self.comm = comm                 # eptq_b200.comm.PushAllReduce, or None for NCCL
         self.embed, self.final_norm, self.lm_head = embed, final_norm, lm_head
         self.inv_freq = inv_freq.float()
         self.eps, self.head_dim = float(rms_eps), int(head_dim)
@@ -111,8 +112,13 @@ class LlamaDecodeEngine:
         return F.rms_norm(x, (x.shape[-1],), w, self.eps)
 
     def _reduce(self, y: torch.Tensor) -> torch.Tensor:
+        """Sum the partial outputs of a row-parallel layer over the tensor-parallel group: the one-shot
+        push kernel for decode-sized vectors when `self.comm` is set, NCCL otherwise (prefill)."""
         if self.tp_group is not None:
-            torch.distributed.all_reduce(y, group=self.tp_group)
+            if self.comm is not None and y.numel() <= self.comm.n_max and y.numel() % 8 == 0:
+                self.comm.all_reduce_(y)
+            else:
+                torch.distributed.all_reduce(y, group=self.tp_group)
         return y
 
     def forward(self, ids: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
@@ -332,7 +338,7 @@ def synthetic_llama_engine(hidden: int, intermediate: int, n_layers: int, n_head
                            vocab: int, quantizer_type: str, codebook: torch.Tensor, max_len: int, batch: int = 1,
                            device: str = "cuda", seed: int = 42, outlier_frac: float = 0.002,
                            tp_rank: int = 0, tp_size: int = 1, tp_group=None, init_std: float = 0.02,
-                           rope_theta: float = 10000.0, rms_eps: float = 1e-5) -> LlamaDecodeEngine:
+                           rope_theta: float = 10000.0, rms_eps: float = 1e-5, comm=None) -> LlamaDecodeEngine:
     """Random-init model of a LLaMA architecture, every decoder linear a synthetic quantized layer
     (make_layer), sharded for this rank when tp_size > 1.  Real checkpoints need the model hub; the
     shapes and value distributions are what matters for throughput.  Row scales carry an extra factor
@@ -366,7 +372,7 @@ def synthetic_llama_engine(hidden: int, intermediate: int, n_layers: int, n_head
     inv_freq = 1.0 / (rope_theta ** (torch.arange(0, head_dim, 2, device=dev).float() / head_dim))
     return LlamaDecodeEngine(layers, embed, torch.ones(hidden, dtype=torch.float16, device=dev), head, inv_freq,
                              rms_eps, head_dim, n_heads // tp_size, n_kv_heads // tp_size, max_len, batch,
-                             tp_group=tp_group)
+                             tp_group=tp_group, comm=comm)
 
 
 ARCHITECTURES = {      # name -> hidden, intermediate, layers, heads, kv heads, vocabulary
@@ -394,6 +400,7 @@ def _main():
     ap.add_argument("--new-tokens", type=int, default=128)
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--nccl", action="store_true", help="all-reduce with NCCL instead of the push kernel")
     args = ap.parse_args()
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -413,12 +420,18 @@ def _main():
         q = E8LatticeQuantizer(radius=1.6)
         q.remove_last()
         table = q.points
+    comm = None
+    if world > 1 and not args.nccl:
+        from .comm import PushAllReduce
+        comm = PushAllReduce(group, args.batch * hidden, torch.device("cuda", local))
     eng = synthetic_llama_engine(hidden, inter, n_layers, heads, kv, vocab, args.quantizer, table,
                                  max_len=args.prefill + args.new_tokens, batch=args.batch, device=f"cuda:{local}",
-                                 tp_rank=rank, tp_size=world, tp_group=group)
+                                 tp_rank=rank, tp_size=world, tp_group=group, comm=comm)
     ids = torch.randint(0, vocab, (args.batch, args.prefill), generator=torch.Generator().manual_seed(0)).cuda()
     eng.decode(ids, min(8, args.new_tokens), use_graph=not args.no_graph)          # warm-up (and capture)
     toks, stats = eng.decode(ids, args.new_tokens, use_graph=not args.no_graph)
+    if comm is not None:
+        comm.check()
     if world > 1:
         stat_t = torch.tensor([stats["decode_s"]], device="cuda")
         torch.distributed.all_reduce(stat_t, op=torch.distributed.ReduceOp.MAX)
@@ -427,7 +440,8 @@ def _main():
         stats["ms_per_token"] = 1e3 * stats["decode_s"] / max(args.new_tokens - 1, 1)
     if rank == 0:
         print(json.dumps({"arch": args.arch, "layers": n_layers, "quantizer": args.quantizer, "batch": args.batch,
-                          "tp": world, "prefill_tokens": args.prefill, "new_tokens": args.new_tokens,
+                          "tp": world, "all_reduce": ("none" if world == 1 else "nccl" if comm is None else "push kernel"),
+                          "prefill_tokens": args.prefill, "new_tokens": args.new_tokens,
                           "cuda_graph": not args.no_graph, **stats}), flush=True)
     if world > 1:
         torch.cuda.synchronize()

@@ -296,6 +296,26 @@ int eptq_decode_attention(const uint16_t* q, const uint16_t* k_cache,
                           int head_dim, int max_len, float scale, void* workspace,
                           size_t workspace_bytes, void* stream);
 
+/*
+ * (No counterpart in the reference, which is single-GPU.)  One-shot all-reduce (sum)
+ * of a small fp16 vector over the GPUs of one node, for the partial outputs of
+ * row-parallel layers in tensor-parallel decode.  Each rank owns a data buffer of
+ * eptq_allreduce_data_bytes(n_ranks, n_max) bytes and a flag buffer of
+ * eptq_allreduce_flag_bytes(n_ranks) bytes, both zero-filled once and mapped into
+ * every peer (CUDA IPC or any other peer mapping; the caller's job).  `peer_data` /
+ * `peer_flags` are host arrays of n_ranks device pointers, entry r = rank r's buffer
+ * as seen from this GPU (entry `rank` = the local one).  Every rank calls with the
+ * same n (multiple of 8, <= n_max) in the same order; `out` may be `x`.  The kernel
+ * stores its vector into every peer's buffer (plain stores over NVLink), then waits
+ * -- bounded -- for the peers' flags and sums locally.  A wait that runs out sets the
+ * int that follows the call counters at the end of the local flag buffer to
+ * EPTQ_ERR_TIMEOUT and leaves `out` unwritten.  At most 8 ranks.
+ */
+size_t eptq_allreduce_data_bytes(int n_ranks, int n_max);
+size_t eptq_allreduce_flag_bytes(int n_ranks);
+int eptq_allreduce_push(const uint16_t* x, uint16_t* out, int n, void* const* peer_data,
+                        void* const* peer_flags, int rank, int n_ranks, int n_max, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
