@@ -54,17 +54,21 @@ class PushAllReduce:
         self._flag_ptrs = (C.c_void_p * self.world)(*flag_ptrs)
         dist.barrier(group=group)              # everyone has mapped everyone before the first store
 
-    def all_reduce_(self, t: torch.Tensor) -> torch.Tensor:
-        if not (t.is_cuda and t.dtype == torch.float16 and t.is_contiguous()):
-            raise RuntimeError("eptq_b200: push all-reduce takes contiguous fp16 CUDA tensors")
+    def all_reduce_(self, t: torch.Tensor, residual: torch.Tensor = None) -> torch.Tensor:
+        """t <- sum over ranks of t; with `residual`: residual <- residual + sum (returned), t untouched."""
+        for x in (t, residual):
+            if x is not None and not (x.is_cuda and x.dtype == torch.float16 and x.is_contiguous()):
+                raise RuntimeError("eptq_b200: push all-reduce takes contiguous fp16 CUDA tensors")
         n = t.numel()
-        if n > self.n_max or n % 8:
+        if n > self.n_max or n % 8 or (residual is not None and residual.numel() != n):
             raise RuntimeError(f"eptq_b200: push all-reduce of {n} elements (limit {self.n_max}, multiple of 8)")
-        st = _lib.load().eptq_allreduce_push(t.data_ptr(), t.data_ptr(), n, self._data_ptrs, self._flag_ptrs,
-                                             self.rank, self.world, self.n_max,
+        out = t if residual is None else residual
+        st = _lib.load().eptq_allreduce_push(t.data_ptr(), out.data_ptr(),
+                                             None if residual is None else residual.data_ptr(), n,
+                                             self._data_ptrs, self._flag_ptrs, self.rank, self.world, self.n_max,
                                              torch.cuda.current_stream(self.device).cuda_stream)
         _lib.check(st, "eptq allreduce_push")
-        return t
+        return out
 
     def check(self) -> None:
         """Raise if any reduction so far ran into its wait limit (one device read)."""

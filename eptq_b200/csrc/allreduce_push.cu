@@ -28,7 +28,8 @@ struct PushArgs {
     __half* data[kArMaxRanks];        // every rank's data buffer (this rank's own included)
     unsigned* flags[kArMaxRanks];     // every rank's flag buffer
     const __half* x;                  // this rank's partial, n elements
-    __half* out;                      // the sum, n elements (may be x)
+    __half* out;                      // the sum, n elements (may be x or residual)
+    const __half* residual;           // optional: out = residual + sum (each rounded to fp16)
     unsigned* seq;                    // kArBlocks call counters of this rank
     int* status;                      // set to EPTQ_ERR_TIMEOUT if a wait ran out
     int rank, T, n, n_max;
@@ -38,6 +39,10 @@ __global__ void __launch_bounds__(kArThreads) allreduce_push_kernel(const PushAr
     __shared__ unsigned s_seq;
     __shared__ int s_ok;
     const int tid = threadIdx.x, b = blockIdx.x;
+    // Programmatic dependent launch: the next kernel may begin its set-up while this one exchanges data;
+    // this one waits for its producer before it reads x.
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     if (tid == 0) { s_seq = a.seq[b] + 1u; s_ok = 1; }
     __syncthreads();
     const unsigned seq = s_seq;
@@ -83,6 +88,12 @@ __global__ void __launch_bounds__(kArThreads) allreduce_push_kernel(const PushAr
             __half2 o[4];
 #pragma unroll
             for (int k = 0; k < 4; ++k) o[k] = __floats2half2_rn(acc[2 * k], acc[2 * k + 1]);
+            if (a.residual != nullptr) {
+                const uint4 rv = *reinterpret_cast<const uint4*>(a.residual + i);
+                const __half2* rh = reinterpret_cast<const __half2*>(&rv);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) o[k] = __hadd2(rh[k], o[k]);
+            }
             *reinterpret_cast<uint4*>(a.out + i) = *reinterpret_cast<const uint4*>(o);
         }
     }
@@ -104,12 +115,13 @@ extern "C" size_t eptq_allreduce_flag_bytes(int n_ranks) {
     return static_cast<size_t>(2) * n_ranks * kArBlocks * sizeof(unsigned) + kArBlocks * sizeof(unsigned) + 16;
 }
 
-extern "C" int eptq_allreduce_push(const uint16_t* x, uint16_t* out, int n, void* const* peer_data,
-                                   void* const* peer_flags, int rank, int n_ranks, int n_max, void* stream) {
+extern "C" int eptq_allreduce_push(const uint16_t* x, uint16_t* out, const uint16_t* residual, int n,
+                                   void* const* peer_data, void* const* peer_flags, int rank, int n_ranks,
+                                   int n_max, void* stream) {
     if (x == nullptr || out == nullptr || peer_data == nullptr || peer_flags == nullptr) return EPTQ_ERR_NULL;
     if (n_ranks < 1 || n_ranks > kArMaxRanks || rank < 0 || rank >= n_ranks || n < 8 || (n % 8) != 0 ||
         n > n_max || (n_max % 8) != 0) return EPTQ_ERR_SHAPE;
-    if (!aligned16(x) || !aligned16(out)) return EPTQ_ERR_ALIGN;
+    if (!aligned16(x) || !aligned16(out) || (residual != nullptr && !aligned16(residual))) return EPTQ_ERR_ALIGN;
     PushArgs a = {};
     for (int r = 0; r < n_ranks; ++r) {
         if (peer_data[r] == nullptr || peer_flags[r] == nullptr) return EPTQ_ERR_NULL;
@@ -123,8 +135,18 @@ extern "C" int eptq_allreduce_push(const uint16_t* x, uint16_t* out, int n, void
     a.status = reinterpret_cast<int*>(a.seq + kArBlocks);
     a.x = reinterpret_cast<const __half*>(x);
     a.out = reinterpret_cast<__half*>(out);
+    a.residual = reinterpret_cast<const __half*>(residual);
     a.rank = rank; a.T = n_ranks; a.n = n; a.n_max = n_max;
-    allreduce_push_kernel<<<kArBlocks, kArThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(kArBlocks);
+    cfg.blockDim = dim3(kArThreads);
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, allreduce_push_kernel, a);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return cudaGetLastError() == cudaSuccess ? EPTQ_OK : EPTQ_ERR_LAUNCH;
 }

@@ -131,7 +131,7 @@ class LlamaDecodeEngine:
         from .kernels import glue
         B, T = ids.shape
         hd, nh, nkv = self.head_dim, self.n_heads, self.n_kv_heads
-        if T == 1 and B <= 2 and hd == 128 and self.tp_group is None and self._fusable():
+        if T == 1 and B <= 2 and hd == 128 and (self.tp_group is None or self.comm is not None) and self._fusable():
             return self._forward_fused_decode(ids, positions)
         x = F.embedding(ids, self.embed).reshape(B * T, -1)                        # fresh tensor, updated in place
         fused_attention = T <= 8 and hd in (64, 128)
@@ -192,9 +192,10 @@ class LlamaDecodeEngine:
         return plan
 
     def _forward_fused_decode(self, ids: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
-        """Five launches per decoder layer: q/k/v (RMSNorm folded in; rotary embedding and the cache
+        """Six launches per decoder layer: q/k/v (RMSNorm folded in; rotary embedding and the cache
         append done by the finalizing warps), attention, o (+ residual), gate/up (RMSNorm folded in),
-        SiLU*up, down (+ residual)."""
+        SiLU*up, down (+ residual).  Tensor-parallel: o and down store partial sums and the push
+        all-reduce adds them to the residual stream (eight launches)."""
         from . import _lib
         from .kernels import glue, linear_forward_group
         B = ids.shape[0]
@@ -216,9 +217,16 @@ class LlamaDecodeEngine:
             kc, vc = self.k_cache[li], self.v_cache[li]
             q = linear_forward_group(P["qkv"], [x, x, x], [nh * hd, 0, 0], fusions=qkv_f, ys=[None, kc, vc])[0]
             att = glue.decode_attention(q, kc, vc, positions, B)
-            linear_forward_group(P["o"], [att], [0], fusions=res_f, ys=[x])
+            if self.tp_group is None:
+                linear_forward_group(P["o"], [att], [0], fusions=res_f, ys=[x])
+            else:                                   # partial sums: the reduction adds them to the residual stream
+                self.comm.all_reduce_(linear_forward_group(P["o"], [att], [L.o.out_features])[0], residual=x)
             gate, up = linear_forward_group(P["gate_up"], [x, x], [L.gate.out_features, L.up.out_features], fusions=gu_f)
-            linear_forward_group(P["down"], [glue.silu_mul(gate, up)], [0], fusions=res_f, ys=[x])
+            act = glue.silu_mul(gate, up)
+            if self.tp_group is None:
+                linear_forward_group(P["down"], [act], [0], fusions=res_f, ys=[x])
+            else:
+                self.comm.all_reduce_(linear_forward_group(P["down"], [act], [L.down.out_features])[0], residual=x)
         hn = glue.add_rmsnorm(x, self.final_norm, self.eps)
         return F.linear(hn, self.lm_head).reshape(B, 1, -1)
 

@@ -305,7 +305,9 @@ int eptq_decode_attention(const uint16_t* q, const uint16_t* k_cache,
  * every peer (CUDA IPC or any other peer mapping; the caller's job).  `peer_data` /
  * `peer_flags` are host arrays of n_ranks device pointers, entry r = rank r's buffer
  * as seen from this GPU (entry `rank` = the local one).  Every rank calls with the
- * same n (multiple of 8, <= n_max) in the same order; `out` may be `x`.  The kernel
+ * same n (multiple of 8, <= n_max) in the same order; `out` may be `x`.  With
+ * `residual` (or NULL) the result is residual + sum, and `out` may be `residual`: the
+ * residual stream of a decoder layer is updated by the reduction itself.  The kernel
  * stores its vector into every peer's buffer (plain stores over NVLink), then waits
  * -- bounded -- for the peers' flags and sums locally.  A wait that runs out sets the
  * int that follows the call counters at the end of the local flag buffer to
@@ -313,8 +315,9 @@ int eptq_decode_attention(const uint16_t* q, const uint16_t* k_cache,
  */
 size_t eptq_allreduce_data_bytes(int n_ranks, int n_max);
 size_t eptq_allreduce_flag_bytes(int n_ranks);
-int eptq_allreduce_push(const uint16_t* x, uint16_t* out, int n, void* const* peer_data,
-                        void* const* peer_flags, int rank, int n_ranks, int n_max, void* stream);
+int eptq_allreduce_push(const uint16_t* x, uint16_t* out, const uint16_t* residual, int n,
+                        void* const* peer_data, void* const* peer_flags, int rank, int n_ranks,
+                        int n_max, void* stream);
 
 #ifdef __cplusplus
 }

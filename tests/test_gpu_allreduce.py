@@ -23,6 +23,11 @@ def _worker(rank, world, port, results):
         dist.all_reduce(want)
         got = comm.all_reduce_(x.clone())
         ok &= bool(float((got.float() - want.float()).abs().max()) <= 2e-3 * float(want.float().abs().max()))
+    res = torch.randn(4096, generator=torch.Generator(device=dev).manual_seed(5), device=dev).half()
+    part = torch.full((4096,), 0.5 * (rank + 1), device=dev).half()
+    want = res + sum(0.5 * (r + 1) for r in range(world))
+    got = comm.all_reduce_(part, residual=res.clone())
+    ok &= bool(float((got.float() - want.float()).abs().max()) <= 2e-3 * float(want.float().abs().max()))
     # replayed from a CUDA graph: the call counters advance on the device
     x = torch.full((4096,), float(rank + 1), device=dev).half()
     buf = x.clone()
