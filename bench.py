@@ -344,7 +344,7 @@ def run_gpu_arm(args):
         y = None
         for i in range(0, len(layers), group):
             chunk = [l for _, l in layers[i:i + group]]
-            if group > 1:
+            if group > 1 and B <= 16:                     # above 16 rows the linears are GEMMs, one call per layer
                 outs = forward_group(chunk, [x_dev[l.in_features] for l in chunk])
             else:
                 outs = [l(x_dev[l.in_features]) for l in chunk]

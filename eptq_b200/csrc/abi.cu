@@ -137,7 +137,7 @@ size_t eptq_workspace_bytes(int M, int N, int B) {
         const size_t mma = mma_workspace_bytes(M, N, B);
         if (mma > bytes) bytes = mma;
     }
-    if (B <= 2 && (N % 32) == 0) {
+    if (B <= kGemmMinBatch && (N % 32) == 0) {
         EptqLayer shape = {};
         shape.M = M; shape.N = N;
         const size_t grp = group_workspace_bytes(&shape, 1, B, 0);

@@ -213,26 +213,50 @@ __global__ void __launch_bounds__(kAttThreads) decode_attention_kernel(
         qs[i] = __half2float(q[static_cast<size_t>(r) * nh * HD + head * HD + i]) * scale;
     __syncthreads();
 
+    // Loads are issued in batches before any is used, so that a block pays about one memory round trip
+    // per 64 keys instead of one per key row: 4 key rows per 8-lane group, and -- when the whole split
+    // fits -- this thread's 8 value rows too, which then arrive under the softmax.
+    constexpr int KPI = kAttThreads / 8;          // keys scored per pass of the block
+    constexpr int SUB = 4;                        // passes batched
+    constexpr int VSUB = 8;                       // value rows per thread batched
+    const int kg = tid / LPR, jv = tid - kg * LPR;
+    const bool small = n <= KG * VSUB;
+    uint4 vreg[VSUB];
     {
         const int grp = tid >> 3, j = tid & 7;
         // The trip count is the same for every lane of a warp (the shuffles below name all 32 lanes);
         // a group past the end recomputes the last key and drops the result.
-        for (int base = 0; base < n; base += kAttThreads / 8) {
-            const bool valid = base + grp < n;
-            const int kk = valid ? base + grp : n - 1;
-            const __half* kr = Kb + static_cast<size_t>(kk) * HD;
-            float d = 0.f;
+        for (int base = 0; base < n; base += KPI * SUB) {
+            uint4 kreg[SUB][HD / 64];
 #pragma unroll
-            for (int c = 0; c < HD / 64; ++c) {
-                float f[8];
-                unpack8(ldg128(kr + c * 64 + j * 8), f);
+            for (int it = 0; it < SUB; ++it) {
+                const int kk = min(base + it * KPI + grp, n - 1);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) d = fmaf(f[i], qs[c * 64 + j * 8 + i], d);
+                for (int c = 0; c < HD / 64; ++c) kreg[it][c] = ldg128(Kb + static_cast<size_t>(kk) * HD + c * 64 + j * 8);
             }
-            d += __shfl_xor_sync(0xffffffffu, d, 1);
-            d += __shfl_xor_sync(0xffffffffu, d, 2);
-            d += __shfl_xor_sync(0xffffffffu, d, 4);
-            if (j == 0 && valid) sc[kk] = d;
+            if (small && base == 0) {
+#pragma unroll
+                for (int it = 0; it < VSUB; ++it) {
+                    const int kk = kg + it * KG;
+                    vreg[it] = kk < n ? ldg128(Vb + static_cast<size_t>(kk) * HD + jv * 8) : make_uint4(0, 0, 0, 0);
+                }
+            }
+#pragma unroll
+            for (int it = 0; it < SUB; ++it) {
+                float d = 0.f;
+#pragma unroll
+                for (int c = 0; c < HD / 64; ++c) {
+                    float f[8];
+                    unpack8(kreg[it][c], f);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) d = fmaf(f[i], qs[c * 64 + j * 8 + i], d);
+                }
+                d += __shfl_xor_sync(0xffffffffu, d, 1);
+                d += __shfl_xor_sync(0xffffffffu, d, 2);
+                d += __shfl_xor_sync(0xffffffffu, d, 4);
+                const int kk = base + it * KPI + grp;
+                if (j == 0 && kk < n) sc[kk] = d;
+            }
         }
     }
     __syncthreads();
@@ -250,18 +274,40 @@ __global__ void __launch_bounds__(kAttThreads) decode_attention_kernel(
     float acc[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-    {
-        const int kg = tid / LPR, j = tid - kg * LPR;
-        for (int kk = kg; kk < n; kk += KG) {
-            float f[8];
-            unpack8(ldg128(Vb + static_cast<size_t>(kk) * HD + j * 8), f);
-            const float p = sc[kk];
+    if (small) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) acc[i] = fmaf(p, f[i], acc[i]);
+        for (int it = 0; it < VSUB; ++it) {
+            const int kk = kg + it * KG;
+            if (kk < n) {
+                float f[8];
+                unpack8(vreg[it], f);
+                const float p = sc[kk];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[i] = fmaf(p, f[i], acc[i]);
+            }
         }
+    } else {
+        for (int base = 0; base < n; base += KG * VSUB) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) accs[kg][j * 8 + i] = acc[i];
+            for (int it = 0; it < VSUB; ++it) {
+                const int kk = base + kg + it * KG;
+                vreg[it] = kk < n ? ldg128(Vb + static_cast<size_t>(kk) * HD + jv * 8) : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int it = 0; it < VSUB; ++it) {
+                const int kk = base + kg + it * KG;
+                if (kk < n) {
+                    float f[8];
+                    unpack8(vreg[it], f);
+                    const float p = sc[kk];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) acc[i] = fmaf(p, f[i], acc[i]);
+                }
+            }
+        }
     }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) accs[kg][jv * 8 + i] = acc[i];
     __syncthreads();
     float mine = 0.f;
     if (tid < HD) {

@@ -794,7 +794,7 @@ bool group_layer_supported(const EptqLayer& L) {
 }  // namespace
 
 bool group_gemv_supported(const EptqLayer* layers, int n, int B) {
-    if (layers == nullptr || n < 1 || n > kMaxGroupLayers || B < 1 || B > 2) return false;
+    if (layers == nullptr || n < 1 || n > kMaxGroupLayers || B < 1 || B > kGemmMinBatch) return false;   // > 2: passes of two rows
     for (int i = 0; i < n; ++i) {
         if (!group_layer_supported(layers[i])) return false;
         if (layers[i].quantizer != layers[0].quantizer || layers[i].table16 != layers[0].table16 ||
@@ -807,12 +807,13 @@ bool group_gemv_supported(const EptqLayer* layers, int n, int B) {
 size_t group_workspace_bytes(const EptqLayer* layers, int n, int B, int n_sms) {
     GroupPlan plan;
     if (n_sms <= 0) n_sms = 148;
-    if (!plan_group(layers, n, B, n_sms, plan)) return 0;
+    if (!plan_group(layers, n, B > 2 ? 2 : B, n_sms, plan)) return 0;
     return kPartialOffset;
 }
 
-int launch_gemv_group(const EptqLayer* layers, int n, const EptqFusion* fusions, const uint16_t* const* xs,
-                      uint16_t* const* ys, int B, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+namespace {
+int launch_gemv_group_pass(const EptqLayer* layers, int n, const EptqFusion* fusions, const uint16_t* const* xs,
+                           uint16_t* const* ys, int B, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
     const int n_sms = cached_sm_count();
     GroupPlan plan;
     if (!plan_group(layers, n, B, n_sms, plan)) return EPTQ_ERR_UNSUPPORTED;
@@ -934,6 +935,30 @@ int launch_gemv_group(const EptqLayer* layers, int n, const EptqFusion* fusions,
                                : cudaLaunchKernelEx(&cfg, gemv_group_kernel<EPTQ_E8D4>, a);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return err == cudaSuccess ? EPTQ_OK : EPTQ_ERR_LAUNCH;
+}
+
+}  // namespace
+
+// Batches above 2 run as passes of two batch rows over the same weights (the kernel's MMA columns hold two
+// rows); the scratch is reused, the passes are ordered on the stream.  Fused epilogues that index a cache
+// by batch entry are limited to one pass.
+int launch_gemv_group(const EptqLayer* layers, int n, const EptqFusion* fusions, const uint16_t* const* xs,
+                      uint16_t* const* ys, int B, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+    if (B <= 2) return launch_gemv_group_pass(layers, n, fusions, xs, ys, B, workspace, workspace_bytes, stream);
+    if (fusions != nullptr || n > kMaxGroupLayers) return EPTQ_ERR_UNSUPPORTED;
+    const uint16_t* xp[kMaxGroupLayers];
+    uint16_t* yp[kMaxGroupLayers];
+    for (int b0 = 0; b0 < B; b0 += 2) {
+        for (int i = 0; i < n; ++i) {
+            if (xs[i] == nullptr || ys[i] == nullptr) return EPTQ_ERR_NULL;
+            xp[i] = xs[i] + static_cast<size_t>(b0) * layers[i].N;
+            yp[i] = ys[i] + static_cast<size_t>(b0) * 8 * layers[i].M;
+        }
+        const int st = launch_gemv_group_pass(layers, n, nullptr, xp, yp, B - b0 >= 2 ? 2 : 1, workspace,
+                                              workspace_bytes, stream);
+        if (st != EPTQ_OK) return st;
+    }
+    return EPTQ_OK;
 }
 
 }  // namespace eptq

@@ -42,7 +42,7 @@ class DecoderLayerWeights:
 def apply_group(layers: Sequence[Callable], x: torch.Tensor) -> List[torch.Tensor]:
     """layers[i](x) for all i; one kernel launch when the layers are EPTQLinear modules of one codebook
     and the batch is small enough for the persistent GEMV, otherwise one call per layer."""
-    if (x.is_cuda and x.shape[0] <= 2 and all(isinstance(l, EPTQLinear) for l in layers)
+    if (x.is_cuda and x.shape[0] <= 16 and all(isinstance(l, EPTQLinear) for l in layers)
             and all(l.quantizer_type == layers[0].quantizer_type and l.S_group is None
                     and l.in_features % 32 == 0 for l in layers)):
         try:

@@ -172,10 +172,11 @@ int eptq_linear_forward(const EptqLayer* layer, const uint16_t* x, uint16_t* y,
  * = layer i applied to x[i] (B, N_i).  For layers whose inputs are all ready --
  * q/k/v or gate/up of a decoder layer (the reference calls them one by one,
  * kernels/linear.py:154-212), the experts of a mixture, or a single layer.
- * Requirements: E8-D4 layers sharing one table16, no group scales, N % 32 == 0,
- * h_absmax set, B = 1 or 2; otherwise EPTQ_ERR_UNSUPPORTED (call
- * eptq_linear_forward per layer instead).  `xs` / `ys` are host arrays of
- * device pointers.  Scratch as for eptq_linear_forward, size from
+ * Requirements: layers of one codebook (E8-D4 sharing one table16, or E8 sharing
+ * one table_packed), no group scales, N % 32 == 0, h_absmax set, B <= 16;
+ * otherwise EPTQ_ERR_UNSUPPORTED (call eptq_linear_forward per layer instead).
+ * One launch covers two batch rows; larger B is run as ceil(B/2) launches over
+ * the same weights.  `xs` / `ys` are host arrays of device pointers.  Scratch as for eptq_linear_forward, size from
  * eptq_group_workspace_bytes.
  */
 size_t eptq_group_workspace_bytes(const EptqLayer* layers, int n_layers, int B);
@@ -203,7 +204,7 @@ int eptq_linear_forward_group(const EptqLayer* layers, int n_layers,
  *         EPTQ_Y_ROPE_TO_CACHE the same, stored into a key cache: y points to fp16
  *                              (B, 8M/128, max_len, 128), row *position.
  *         EPTQ_Y_TO_CACHE      no rotation, stored into a value cache likewise.
- *   The three head-wise ops need 8M a multiple of 128 (M % 16 == 0).
+ *   The three head-wise ops need 8M a multiple of 128 (M % 16 == 0).  Fusions need B <= 2.
  */
 enum { EPTQ_X_PLAIN = 0, EPTQ_X_RMSNORM = 2 };
 enum { EPTQ_Y_STORE = 0, EPTQ_Y_ADD_RESIDUAL = 1, EPTQ_Y_ROPE = 2, EPTQ_Y_ROPE_TO_CACHE = 3, EPTQ_Y_TO_CACHE = 4 };

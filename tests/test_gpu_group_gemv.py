@@ -60,7 +60,23 @@ def test_group_rejects_ineligible_sets():
     with pytest.raises(RuntimeError):                                  # group scales run on the general kernel
         forward_group([scaled], [make_activations(1, 64).to(DEV)])
     with pytest.raises(RuntimeError):
-        forward_group([d4], [make_activations(3, 64).to(DEV)])        # batch 3 is not a group batch
+        forward_group([d4], [make_activations(17, 64).to(DEV)])       # above 16 rows the layers are GEMMs
+
+
+@pytest.mark.parametrize("batch", [3, 4, 7, 16])
+def test_group_batches_above_two(batch):
+    """Batches 3..16 run as passes of two rows over the same weights."""
+    shapes = [(4096, 4096), (264, 2752), (1024, 4096)]
+    qds = [make_layer(o, i, seed=5 * k + o, outlier_frac=0.004, bias=(k == 0)) for k, (o, i) in enumerate(shapes)]
+    lins = [EPTQLinear.from_quantized_data(qd, TABLE, "e8_d4").to(DEV) for qd in qds]
+    xs = [make_activations(batch, i, seed=51 + k) for k, (_, i) in enumerate(shapes)]
+    ys = forward_group(lins, [x.to(DEV) for x in xs])
+    for qd, x, y in zip(qds, xs, ys):
+        ref = reference(qd, x)
+        for b in range(batch):
+            assert util.max_rel_err(y[b].float().cpu().numpy(), ref[b]) <= util.REL_TOL
+    y1 = lins[0](xs[0].to(DEV))                       # the single-layer entry takes the same route
+    assert util.max_rel_err(y1.float().cpu().numpy(), reference(qds[0], xs[0])) <= util.REL_TOL
 
 
 @pytest.mark.parametrize("B", [1, 2])

@@ -76,7 +76,7 @@ def test_small_batches(batch, out_f, in_f):
 
 
 def test_agrees_with_general_kernel_and_is_repeatable():
-    """Batch 5 (five identical rows) runs on the general kernel; batch 1 on the tensor-core one."""
+    """Five identical rows (three passes of two rows) agree with the single row."""
     qd = make_layer(4096, 4096, seed=6)
     lin = build(qd)
     x = make_activations(1, 4096, seed=15).to(DEV)
@@ -86,10 +86,10 @@ def test_agrees_with_general_kernel_and_is_repeatable():
     assert float((y1[0].float() - ref).abs().max() / ref.abs().max()) <= util.REL_TOL
     for _ in range(3):                               # batch 1: fp32 atomic adds, repeats agree to an fp16 ulp
         assert util.max_rel_err(lin(x).float().cpu().numpy(), y1.float().cpu().numpy()) <= 1e-3
-    x4 = torch.cat([x, x, x, x])                     # batch 4: ordered reduction, bit-repeatable
+    x4 = torch.cat([x, x, x, x])                     # batch 4: two passes of the same kernel
     y4 = lin(x4)
     for _ in range(3):
-        assert torch.equal(lin(x4), y4)
+        assert util.max_rel_err(lin(x4).float().cpu().numpy(), y4.float().cpu().numpy()) <= 1e-3
 
 
 def test_interleaved_shapes_share_scratch():
