@@ -1,8 +1,8 @@
 """Regenerates the golden fixtures in this directory from the reference itself.
 
-Needs the reference checkout (default /root/reference, override with
-EPTQ_REFERENCE); it is imported as package ``eptq`` through a temporary
-symlink and run on the CPU.  What is stored:
+Needs a checkout of the reference (kmudmlab/eptq): pass its path in the
+environment variable EPTQ_REFERENCE.  It is imported as package ``eptq``
+through a temporary symlink and run on the CPU.  What is stored:
 
   tables.json          sha256 of the reference's fp32 codebooks (raw and divided)
   case_*.npz           small layers: inputs, the reference's ``dequantize_layer``
@@ -10,7 +10,7 @@ symlink and run on the CPU.  What is stored:
   config1.json         sha256 of W16 for the full OPT-125m fc1 configuration
                        (3072x768, E8 r=1.6, seed 42) built by eptq_b200.synthetic
 
-Usage:  python tests/golden/make_golden.py
+Usage:  EPTQ_REFERENCE=<path to the reference checkout> python tests/golden/make_golden.py
 """
 import hashlib
 import json
@@ -26,7 +26,9 @@ HERE = Path(__file__).resolve().parent
 REPO = HERE.parent.parent
 sys.path.insert(0, str(REPO))
 
-ref_root = Path(os.environ.get("EPTQ_REFERENCE", "/root/reference"))
+if "EPTQ_REFERENCE" not in os.environ:
+    raise SystemExit("set EPTQ_REFERENCE to the path of the reference checkout")
+ref_root = Path(os.environ["EPTQ_REFERENCE"])
 tmp = tempfile.mkdtemp()
 os.symlink(ref_root, Path(tmp) / "eptq")
 sys.path.insert(0, tmp)
