@@ -475,26 +475,59 @@ __global__ void __launch_bounds__(kGroupThreads, 1) gemv_group_kernel(const __gr
             --pf_todo;
         }
     }
+    // ---- correction warps.  They need neither the table nor, unless the input norm is fused, anything the
+    // other warps compute, so in that case they start at once and the table barrier is for the main warps only.
+    auto run_corrections = [&](const float* inv_rms_ptr) {
+        // What the main loop adds for a marker: E8-D4 entry (3,127) in both halves; E8 entry 65535 is zero.
+        float2 c01 = make_float2(0.f, 0.f), c23 = make_float2(0.f, 0.f);
+        if constexpr (KIND == EPTQ_E8D4) {
+            const uint2 craw = __ldg(p.table16 + 511);
+            c01 = __half22float2(*reinterpret_cast<const __half2*>(&craw.x));
+            c23 = __half22float2(*reinterpret_cast<const __half2*>(&craw.y));
+        }
+        bool waited = false;
+        const int cw = blockIdx.x * kCorrWarps + (warp - kMainWarps);
+        int l = 0;
+        for (int u = cw; u < p.corr_units; u += p.n_corr_warps) {
+            while (l + 1 < p.n_layers && p.L[l + 1].corr0 <= u) ++l;
+            correction_unit(p, p.L[l], u - p.L[l].corr0, lane, c01.x, c01.y, c23.x, c23.y, inv_rms_ptr, [&]() {
+                if (!waited) { asm volatile("griddepcontrol.wait;" ::: "memory"); waited = true; }
+            });
+        }
+        EPTQ_TRACE(7, warp == kMainWarps);
+    };
+    const bool corr_early = p.x_norm == 0;                 // the same for every thread of the launch
+    if (corr_early && warp >= kMainWarps) {
+        run_corrections(nullptr);
+        return;
+    }
+    const int builders = corr_early ? kMainWarps * 32 : kGroupThreads;
     EPTQ_TRACE(1, warp == 0);
     if constexpr (KIND == EPTQ_E8) {
         // Resident part of the packed table: asynchronous 16-byte copies, no registers in between.
         const unsigned dst0 = base + kE8TableOffset;
         const char* src0 = reinterpret_cast<const char*>(p.packed);
-        for (unsigned off = threadIdx.x * 16u; off < kE8Resident * 4u; off += kGroupThreads * 16u)
+        for (unsigned off = threadIdx.x * 16u; off < kE8Resident * 4u; off += builders * 16u)
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(dst0 + off), "l"(src0 + off) : "memory");
         asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
     } else {
-        // Replicated table; entry order follows the raw stored bits (true index ^ 0x100 on 9 bits).  One load
-        // per thread (512 entries, 512 threads), then the 16 copies of that entry: one memory round trip.
-        static_assert(kGroupThreads == 512, "one table entry per thread");
-        const int e = threadIdx.x;
-        const uint2 v = __ldg(p.table16 + (e ^ 0x100));
-        const uint4 vv = make_uint4(v.x, v.y, v.x, v.y);
+        // Replicated table; entry order follows the raw stored bits (true index ^ 0x100 on 9 bits).  Both loads
+        // of a thread (512 entries over 448 or 512 threads) go out before the stores: one memory round trip.
+        static_assert(kMainWarps * 64 >= 512, "at most two table entries per thread");
+        const int e0 = threadIdx.x, e1 = threadIdx.x + builders;
+        const uint2 v0 = __ldg(p.table16 + (e0 ^ 0x100));
+        const uint2 v1 = e1 < 512 ? __ldg(p.table16 + (e1 ^ 0x100)) : make_uint2(0, 0);
+        const uint4 vv0 = make_uint4(v0.x, v0.y, v0.x, v0.y), vv1 = make_uint4(v1.x, v1.y, v1.x, v1.y);
 #pragma unroll
-        for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(tab + e * 128 + ((c + e) & 7) * 16) = vv;
+        for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(tab + e0 * 128 + ((c + e0) & 7) * 16) = vv0;
+        if (e1 < 512) {
+#pragma unroll
+            for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(tab + e1 * 128 + ((c + e1) & 7) * 16) = vv1;
+        }
     }
 
-    __syncthreads();                                   // table complete (all 16 warps reach this once)
+    if (corr_early) asm volatile("bar.sync 1, %0;" :: "n"(kMainWarps * 32) : "memory");   // table complete: main warps only
+    else __syncthreads();                                                                    // all 16 warps
     EPTQ_TRACE(2, warp == 0);
 
     // Fused RMSNorm of the input: every layer of the launch reads the same x; the column weight of the
@@ -530,24 +563,7 @@ __global__ void __launch_bounds__(kGroupThreads, 1) gemv_group_kernel(const __gr
     }
 
     if (warp >= kMainWarps) {
-        // ---- correction warps
-        // What the main loop adds for a marker: E8-D4 entry (3,127) in both halves; E8 entry 65535 is zero.
-        float2 c01 = make_float2(0.f, 0.f), c23 = make_float2(0.f, 0.f);
-        if constexpr (KIND == EPTQ_E8D4) {
-            const uint2 craw = __ldg(p.table16 + 511);
-            c01 = __half22float2(*reinterpret_cast<const __half2*>(&craw.x));
-            c23 = __half22float2(*reinterpret_cast<const __half2*>(&craw.y));
-        }
-        bool waited = false;
-        const int cw = blockIdx.x * kCorrWarps + (warp - kMainWarps);
-        int l = 0;
-        for (int u = cw; u < p.corr_units; u += p.n_corr_warps) {
-            while (l + 1 < p.n_layers && p.L[l + 1].corr0 <= u) ++l;
-            correction_unit(p, p.L[l], u - p.L[l].corr0, lane, c01.x, c01.y, c23.x, c23.y, inv_rms, [&]() {
-                if (!waited) { asm volatile("griddepcontrol.wait;" ::: "memory"); waited = true; }
-            });
-        }
-        EPTQ_TRACE(7, warp == kMainWarps);
+        run_corrections(inv_rms);
         return;
     }
 

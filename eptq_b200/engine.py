@@ -163,6 +163,7 @@ class LlamaDecodeEngine:
             mods = [m for L in self.layers for m in (L.q, L.k, L.v, L.o, L.gate, L.up, L.down)]
             ok = all(isinstance(m, EPTQLinear) and m.quantizer_type == mods[0].quantizer_type and m.S_group is None
                      and m.in_features % 32 == 0 and m.out_features % 128 == 0 for m in mods)
+            ok = ok and all(m._codebook is mods[0]._codebook for m in mods)      # one table per launch
             if ok and mods[0].quantizer_type == "e8_lattice":
                 ok = bool(mods[0].descriptor().table_packed)        # E8 needs a table that packs
             self._fused = self._build_fused() if ok else False
