@@ -396,7 +396,9 @@ struct StripIter {
     }
 };
 
-template <int KIND>
+// NB = batch rows of the launch (1 or 2): a compile-time constant, so that the batch-1 kernel carries no
+// second-row loads, stores or branches in its main loop.
+template <int KIND, int NB>
 __global__ void __launch_bounds__(kGroupThreads, 1) gemv_group_kernel(const __grid_constant__ GroupArgs p) {
     constexpr int RING = KIND == EPTQ_E8 ? kRingE8 : kRing;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -574,7 +576,7 @@ __global__ void __launch_bounds__(kGroupThreads, 1) gemv_group_kernel(const __gr
     for (int i = 0; i < RING; ++i) {
         if (i < n_total) {
             xr0[i] = __ldg(xfirst.px);
-            if (p.B > 1) xr1[i] = __ldg(xfirst.px + xfirst.N);
+            if constexpr (NB > 1) xr1[i] = __ldg(xfirst.px + xfirst.N);
             step(xfirst);
         }
     }
@@ -632,13 +634,13 @@ __global__ void __launch_bounds__(kGroupThreads, 1) gemv_group_kernel(const __gr
         const float hx = __half2float(hr[I]) * cscale;                                                       \
         unsigned* wslab = slab + par * 64;                                                                   \
         wslab[lane] = split_pieces(__half2float(xr0[I]) * hx);                                               \
-        if (p.B > 1) wslab[32 + lane] = split_pieces(__half2float(xr1[I]) * hx);                             \
+        if constexpr (NB > 1) wslab[32 + lane] = split_pieces(__half2float(xr1[I]) * hx);                             \
         if (pf_todo > 0) {                                                                                   \
             qa[I] = ldg_stream(pf.pa);                                                                       \
             qb[I] = ldg_stream(pf.pb);                                                                       \
             hr[I] = __ldg(pf.ph);                                                                            \
             xr0[I] = __ldg(pf.px);                                                                           \
-            if (p.B > 1) xr1[I] = __ldg(pf.px + pf.N);                                                       \
+            if constexpr (NB > 1) xr1[I] = __ldg(pf.px + pf.N);                                                       \
             step(pf);                                                                                        \
             --pf_todo;                                                                                       \
         }                                                                                                    \
@@ -683,13 +685,13 @@ __global__ void __launch_bounds__(kGroupThreads, 1) gemv_group_kernel(const __gr
         const float hx = __half2float(hr[I]) * cscale;                                                       \
         unsigned* wslab = slab + par * 64;                                                                   \
         wslab[lane] = split_pieces(__half2float(xr0[I]) * hx);                                               \
-        if (p.B > 1) wslab[32 + lane] = split_pieces(__half2float(xr1[I]) * hx);                             \
+        if constexpr (NB > 1) wslab[32 + lane] = split_pieces(__half2float(xr1[I]) * hx);                             \
         if (pf_todo > 0) {                                                                                   \
             qa[I] = ldg_stream(pf.pa);                                                                       \
             qb[I] = ldg_stream(pf.pb);                                                                       \
             hr[I] = __ldg(pf.ph);                                                                            \
             xr0[I] = __ldg(pf.px);                                                                           \
-            if (p.B > 1) xr1[I] = __ldg(pf.px + pf.N);                                                       \
+            if constexpr (NB > 1) xr1[I] = __ldg(pf.px + pf.N);                                                       \
             step(pf);                                                                                        \
             --pf_todo;                                                                                       \
         }                                                                                                    \
@@ -930,10 +932,10 @@ int launch_gemv_group_pass(const EptqLayer* layers, int n, const EptqFusion* fus
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return EPTQ_ERR_LAUNCH;
     if (!attr_done[dev]) {
-        if (cudaFuncSetAttribute(gemv_group_kernel<EPTQ_E8D4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 kGroupSmemBytes) != cudaSuccess ||
-            cudaFuncSetAttribute(gemv_group_kernel<EPTQ_E8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 kE8SmemBytes) != cudaSuccess)
+        if (cudaFuncSetAttribute(gemv_group_kernel<EPTQ_E8D4, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGroupSmemBytes) != cudaSuccess ||
+            cudaFuncSetAttribute(gemv_group_kernel<EPTQ_E8D4, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGroupSmemBytes) != cudaSuccess ||
+            cudaFuncSetAttribute(gemv_group_kernel<EPTQ_E8, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kE8SmemBytes) != cudaSuccess ||
+            cudaFuncSetAttribute(gemv_group_kernel<EPTQ_E8, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kE8SmemBytes) != cudaSuccess)
             return EPTQ_ERR_LAUNCH;
         attr_done[dev] = true;
     }
@@ -947,8 +949,9 @@ int launch_gemv_group_pass(const EptqLayer* layers, int n, const EptqFusion* fus
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    const cudaError_t err = e8 ? cudaLaunchKernelEx(&cfg, gemv_group_kernel<EPTQ_E8>, a)
-                               : cudaLaunchKernelEx(&cfg, gemv_group_kernel<EPTQ_E8D4>, a);
+    const cudaError_t err =
+        e8 ? (B == 1 ? cudaLaunchKernelEx(&cfg, gemv_group_kernel<EPTQ_E8, 1>, a) : cudaLaunchKernelEx(&cfg, gemv_group_kernel<EPTQ_E8, 2>, a))
+           : (B == 1 ? cudaLaunchKernelEx(&cfg, gemv_group_kernel<EPTQ_E8D4, 1>, a) : cudaLaunchKernelEx(&cfg, gemv_group_kernel<EPTQ_E8D4, 2>, a));
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return err == cudaSuccess ? EPTQ_OK : EPTQ_ERR_LAUNCH;
 }
