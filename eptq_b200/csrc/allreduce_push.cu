@@ -2,13 +2,15 @@
 // the row-parallel layers (o / down projections) of a tensor-parallel decode step.  The reference is
 // single-GPU (kernels/patch.py:24-27); NCCL's all-reduce of 8 KB costs more than the GEMV it follows,
 // so each rank instead stores its partial straight into a slot of every peer's buffer over NVLink
-// (ordinary global stores through peer pointers), raises a flag, waits for the other ranks' flags and
-// sums the slots locally.  No TMA, no multicast loads, no reads of remote memory: only stores go out.
+// (ordinary global stores through peer pointers, each word carrying its own arrival tag), polls its own
+// slots until the peers' words are there and sums them locally.  No TMA, no multicast loads, no reads of remote memory: only stores go out.
 //
-// Buffers per rank (allocated and exchanged by the caller): data [2 parities][T sources][n_max] fp16 and
-// flags [2][T][kArBlocks] u32.  Call k uses parity k & 1; a rank can enter call k+1 only after it saw
-// every rank's flags of call k, i.e. after every rank has finished reading call k-1, so two parities
-// suffice.  Every wait is bounded; on a timeout the kernel records EPTQ_ERR_TIMEOUT and returns.
+// Buffers per rank (allocated and exchanged by the caller): data [2 parities][T sources][n_max/2] words of
+// 8 bytes (two fp16 values + the call number), and a small block of call counters and a status word.
+// Call k uses parity k & 1 and tags its words with k; a rank can enter call k+1 only after it received every
+// rank's words of call k, i.e. after every rank has finished reading call k-1, so two parities suffice and a
+// stale word can never carry the current tag.  Every wait is bounded; on a timeout the kernel records
+// EPTQ_ERR_TIMEOUT and returns.
 
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -37,66 +39,54 @@ struct PushArgs {
 
 __global__ void __launch_bounds__(kArThreads) allreduce_push_kernel(const PushArgs a) {
     __shared__ unsigned s_seq;
-    __shared__ int s_ok;
     const int tid = threadIdx.x, b = blockIdx.x;
     // Programmatic dependent launch: the next kernel may begin its set-up while this one exchanges data;
     // this one waits for its producer before it reads x.
     asm volatile("griddepcontrol.launch_dependents;");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (tid == 0) { s_seq = a.seq[b] + 1u; s_ok = 1; }
+    if (tid == 0) s_seq = a.seq[b] + 1u;
     __syncthreads();
     const unsigned seq = s_seq;
     const unsigned parity = seq & 1u;
-    const int per_block = ((a.n + kArBlocks * 8 - 1) / (kArBlocks * 8)) * 8;      // multiple of 8 elements
-    const int lo = b * per_block;
-    const int hi = min(a.n, lo + per_block);
-
-    // push my chunk into my slot of every rank's buffer
-    const size_t my_slot = (static_cast<size_t>(parity) * a.T + a.rank) * a.n_max;
-    for (int i = lo + tid * 8; i < hi; i += kArThreads * 8) {
-        const uint4 v = *reinterpret_cast<const uint4*>(a.x + i);
-        for (int r = 0; r < a.T; ++r) *reinterpret_cast<uint4*>(a.data[r] + my_slot + i) = v;
-    }
-    __threadfence_system();
-    __syncthreads();
-    if (tid < a.T) {
-        unsigned* f = a.flags[tid] + (parity * a.T + a.rank) * kArBlocks + b;
-        asm volatile("st.release.sys.global.u32 [%0], %1;" :: "l"(f), "r"(seq) : "memory");
-        // wait for rank `tid`'s flag of this call in my own buffer
-        const unsigned* w = a.flags[a.rank] + (parity * a.T + tid) * kArBlocks + b;
-        unsigned got = 0, spins = 0;
-        for (;;) {
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(got) : "l"(w) : "memory");
-            if (got == seq) break;
-            if (++spins > kArSpinLimit) { s_ok = 0; atomicExch(a.status, static_cast<int>(EPTQ_ERR_TIMEOUT)); break; }
+    // A word is two fp16 values plus the call number, written with ONE 8-byte store: the receiver polls the
+    // word itself, so no fence and no separate flag are needed (the payload and its flag cannot be seen apart).
+    const int words = a.n >> 1, words_max = a.n_max >> 1;
+    const size_t my_slot = (static_cast<size_t>(parity) * a.T + a.rank) * words_max;
+    const unsigned* x32 = reinterpret_cast<const unsigned*>(a.x);
+    for (int w = b * kArThreads + tid; w < words; w += kArBlocks * kArThreads) {
+        const unsigned v = x32[w];
+        for (int r = 0; r < a.T; ++r) {
+            uint2* dst = reinterpret_cast<uint2*>(a.data[r]) + my_slot + w;
+            asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1,%2};" :: "l"(dst), "r"(v), "r"(seq) : "memory");
         }
     }
-    __syncthreads();
-    if (s_ok) {
-        const __half* mine = a.data[a.rank] + static_cast<size_t>(parity) * a.T * a.n_max;
-        for (int i = lo + tid * 8; i < hi; i += kArThreads * 8) {
-            float acc[8];
-#pragma unroll
-            for (int k = 0; k < 8; ++k) acc[k] = 0.f;
-            for (int r = 0; r < a.T; ++r) {
-                const uint4 v = __ldcg(reinterpret_cast<const uint4*>(mine + static_cast<size_t>(r) * a.n_max + i));
-                float f[8];
-                unpack8(v, f);
-#pragma unroll
-                for (int k = 0; k < 8; ++k) acc[k] += f[k];
+    const uint2* mine = reinterpret_cast<const uint2*>(a.data[a.rank]) + static_cast<size_t>(parity) * a.T * words_max;
+    const unsigned* res32 = reinterpret_cast<const unsigned*>(a.residual);
+    unsigned* out32 = reinterpret_cast<unsigned*>(a.out);
+    bool ok = true;
+    for (int w = b * kArThreads + tid; w < words && ok; w += kArBlocks * kArThreads) {
+        float2 acc = make_float2(0.f, 0.f);
+        for (int r = 0; r < a.T; ++r) {
+            const uint2* src = mine + static_cast<size_t>(r) * words_max + w;
+            unsigned lo = 0, flag = 0, spins = 0;
+            for (;;) {
+                asm volatile("ld.relaxed.sys.global.v2.u32 {%0,%1}, [%2];" : "=r"(lo), "=r"(flag) : "l"(src) : "memory");
+                if (flag == seq) break;
+                if (++spins > kArSpinLimit) { ok = false; break; }
             }
-            __half2 o[4];
-#pragma unroll
-            for (int k = 0; k < 4; ++k) o[k] = __floats2half2_rn(acc[2 * k], acc[2 * k + 1]);
-            if (a.residual != nullptr) {
-                const uint4 rv = *reinterpret_cast<const uint4*>(a.residual + i);
-                const __half2* rh = reinterpret_cast<const __half2*>(&rv);
-#pragma unroll
-                for (int k = 0; k < 4; ++k) o[k] = __hadd2(rh[k], o[k]);
-            }
-            *reinterpret_cast<uint4*>(a.out + i) = *reinterpret_cast<const uint4*>(o);
+            if (!ok) break;
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&lo));
+            acc.x += f.x; acc.y += f.y;
         }
+        if (!ok) { atomicExch(a.status, static_cast<int>(EPTQ_ERR_TIMEOUT)); break; }
+        __half2 o = __floats2half2_rn(acc.x, acc.y);
+        if (res32 != nullptr) {
+            const unsigned rv = res32[w];
+            o = __hadd2(*reinterpret_cast<const __half2*>(&rv), o);
+        }
+        out32[w] = *reinterpret_cast<const unsigned*>(&o);
     }
+    __syncthreads();
     if (tid == 0) a.seq[b] = seq;
 }
 
@@ -107,7 +97,7 @@ using namespace eptq;
 
 extern "C" size_t eptq_allreduce_data_bytes(int n_ranks, int n_max) {
     if (n_ranks < 1 || n_ranks > kArMaxRanks || n_max < 8 || (n_max % 8) != 0) return 0;
-    return static_cast<size_t>(2) * n_ranks * n_max * sizeof(uint16_t);
+    return static_cast<size_t>(2) * n_ranks * (n_max / 2) * 8;
 }
 
 extern "C" size_t eptq_allreduce_flag_bytes(int n_ranks) {
@@ -121,7 +111,7 @@ extern "C" int eptq_allreduce_push(const uint16_t* x, uint16_t* out, const uint1
     if (x == nullptr || out == nullptr || peer_data == nullptr || peer_flags == nullptr) return EPTQ_ERR_NULL;
     if (n_ranks < 1 || n_ranks > kArMaxRanks || rank < 0 || rank >= n_ranks || n < 8 || (n % 8) != 0 ||
         n > n_max || (n_max % 8) != 0) return EPTQ_ERR_SHAPE;
-    if (!aligned16(x) || !aligned16(out) || (residual != nullptr && !aligned16(residual))) return EPTQ_ERR_ALIGN;
+    if ((n % 2) != 0 || !aligned16(x) || !aligned16(out) || (residual != nullptr && !aligned16(residual))) return EPTQ_ERR_ALIGN;
     PushArgs a = {};
     for (int r = 0; r < n_ranks; ++r) {
         if (peer_data[r] == nullptr || peer_flags[r] == nullptr) return EPTQ_ERR_NULL;

@@ -309,8 +309,9 @@ int eptq_decode_attention(const uint16_t* q, const uint16_t* k_cache,
  * same n (multiple of 8, <= n_max) in the same order; `out` may be `x`.  With
  * `residual` (or NULL) the result is residual + sum, and `out` may be `residual`: the
  * residual stream of a decoder layer is updated by the reduction itself.  The kernel
- * stores its vector into every peer's buffer (plain stores over NVLink), then waits
- * -- bounded -- for the peers' flags and sums locally.  A wait that runs out sets the
+ * stores its vector into every peer's buffer (plain 8-byte stores over NVLink, each
+ * carrying two values and the call number), then polls -- bounded -- its own buffer
+ * until every peer's words are there and sums locally.  A wait that runs out sets the
  * int that follows the call counters at the end of the local flag buffer to
  * EPTQ_ERR_TIMEOUT and leaves `out` unwritten.  At most 8 ranks.
  */
