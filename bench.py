@@ -252,6 +252,9 @@ def run_gpu_arm(args):
             calls.append((arr, n, xp, yp, reduce_ys, grouped, i))
         return calls, need
 
+    if world > 1:
+        dist.barrier()                       # ranks finish building at different times: line them up before the
+        torch.cuda.synchronize()             # first reduction, whose device-side wait is bounded
     calls, ws_bytes = make_calls(group)
     calls1, ws_bytes1 = make_calls(1)
     ws = torch.zeros(max(ws_bytes, ws_bytes1), dtype=torch.uint8, device=dev)

@@ -9,7 +9,7 @@
 // 8 bytes (two fp16 values + the call number), and a small block of call counters and a status word.
 // Call k uses parity k & 1 and tags its words with k; a rank can enter call k+1 only after it received every
 // rank's words of call k, i.e. after every rank has finished reading call k-1, so two parities suffice and a
-// stale word can never carry the current tag.  Every wait is bounded; on a timeout the kernel records
+// stale word can never carry the current tag.  Every wait is bounded (two seconds of wall time); on a timeout the kernel records
 // EPTQ_ERR_TIMEOUT and returns.
 
 #include <cuda_fp16.h>
@@ -24,7 +24,7 @@ namespace {
 constexpr int kArBlocks = 8;
 constexpr int kArThreads = 128;
 constexpr int kArMaxRanks = 8;
-constexpr unsigned kArSpinLimit = 400000;          // about a quarter of a second of polling
+constexpr unsigned long long kArWaitNs = 2000000000ull;   // a wait gives up after two seconds
 
 struct PushArgs {
     __half* data[kArMaxRanks];        // every rank's data buffer (this rank's own included)
@@ -65,20 +65,38 @@ __global__ void __launch_bounds__(kArThreads) allreduce_push_kernel(const PushAr
     unsigned* out32 = reinterpret_cast<unsigned*>(a.out);
     bool ok = true;
     for (int w = b * kArThreads + tid; w < words && ok; w += kArBlocks * kArThreads) {
-        float2 acc = make_float2(0.f, 0.f);
-        for (int r = 0; r < a.T; ++r) {
-            const uint2* src = mine + static_cast<size_t>(r) * words_max + w;
-            unsigned lo = 0, flag = 0, spins = 0;
-            for (;;) {
-                asm volatile("ld.relaxed.sys.global.v2.u32 {%0,%1}, [%2];" : "=r"(lo), "=r"(flag) : "l"(src) : "memory");
-                if (flag == seq) break;
-                if (++spins > kArSpinLimit) { ok = false; break; }
+        // One pass issues the loads of all sources that are still missing before it looks at any of them, so
+        // that the round trips overlap; the wait is bounded by wall time (the global timer), checked every
+        // 256 passes.
+        unsigned val[kArMaxRanks];
+        unsigned missing = (1u << a.T) - 1u;
+        unsigned long long t_start = 0;
+        for (unsigned pass = 0; missing != 0u; ++pass) {
+            unsigned lo[kArMaxRanks], flag[kArMaxRanks];
+#pragma unroll
+            for (int r = 0; r < kArMaxRanks; ++r)
+                if ((missing >> r) & 1u) {
+                    const uint2* src = mine + static_cast<size_t>(r) * words_max + w;
+                    asm volatile("ld.relaxed.sys.global.v2.u32 {%0,%1}, [%2];" : "=r"(lo[r]), "=r"(flag[r]) : "l"(src) : "memory");
+                }
+#pragma unroll
+            for (int r = 0; r < kArMaxRanks; ++r)
+                if (((missing >> r) & 1u) && flag[r] == seq) { val[r] = lo[r]; missing &= ~(1u << r); }
+            if (missing != 0u && (pass & 255u) == 255u) {
+                unsigned long long now;
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+                if (t_start == 0) t_start = now;
+                else if (now - t_start > kArWaitNs) { ok = false; break; }
             }
-            if (!ok) break;
-            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&lo));
-            acc.x += f.x; acc.y += f.y;
         }
         if (!ok) { atomicExch(a.status, static_cast<int>(EPTQ_ERR_TIMEOUT)); break; }
+        float2 acc = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int r = 0; r < kArMaxRanks; ++r)
+            if (r < a.T) {                                   // fixed order: every rank computes the same sum
+                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&val[r]));
+                acc.x += f.x; acc.y += f.y;
+            }
         __half2 o = __floats2half2_rn(acc.x, acc.y);
         if (res32 != nullptr) {
             const unsigned rv = res32[w];
