@@ -95,3 +95,65 @@ def test_engine_graph_decode_gpu(quantizer_type, hidden, heads, inter):
     again, _ = eng.decode(ids, 12, use_graph=True)
     assert torch.equal(again, graphed)
     assert stats["tokens_per_s"] > 0
+
+
+def _tp_engine_worker(rank, world, port, out):
+    """Rank `rank` of a tensor-parallel engine on the CPU: dense fp32 shards of one tiny model (output rows of
+    q/k/v/gate/up, input columns of o/down), gloo all-reduce, the plain PyTorch statement of the step."""
+    import os
+
+    import torch.distributed as dist
+    import torch.nn as nn
+    from transformers import LlamaForCausalLM
+
+    from eptq_b200.engine import DecoderLayerWeights
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.manual_seed(0)
+    model = LlamaForCausalLM(_tiny_config(4)).float().eval()
+
+    def rows(lin):
+        n = lin.out_features // world
+        m = nn.Linear(lin.in_features, n, bias=False)
+        m.weight.data = lin.weight.data[rank * n:(rank + 1) * n].clone()
+        return m
+
+    def cols(lin):
+        n = lin.in_features // world
+        m = nn.Linear(n, lin.out_features, bias=False)
+        m.weight.data = lin.weight.data[:, rank * n:(rank + 1) * n].clone()
+        return m
+    core, cfg = model.model, model.config
+    layers = [DecoderLayerWeights(rows(l.self_attn.q_proj), rows(l.self_attn.k_proj), rows(l.self_attn.v_proj),
+                                  cols(l.self_attn.o_proj), rows(l.mlp.gate_proj), rows(l.mlp.up_proj),
+                                  cols(l.mlp.down_proj), l.input_layernorm.weight.data,
+                                  l.post_attention_layernorm.weight.data) for l in core.layers]
+    hd = cfg.hidden_size // cfg.num_attention_heads
+    eng = LlamaDecodeEngine(layers, core.embed_tokens.weight.data, core.norm.weight.data, model.lm_head.weight.data,
+                            core.rotary_emb.inv_freq, cfg.rms_norm_eps, hd, cfg.num_attention_heads // world,
+                            cfg.num_key_value_heads // world, max_len=32, batch=1, tp_group=dist.group.WORLD)
+    ids = torch.randint(0, 128, (1, 7), generator=torch.Generator().manual_seed(5))
+    with torch.no_grad():
+        first = eng.prefill(ids)
+        seq = [int(first)]
+        for _ in range(3):
+            eng._step()
+            seq.append(int(eng.next_token))
+        if rank == 0:
+            full = torch.cat([ids, torch.tensor([seq[:-1]])], dim=1)
+            ref = model(input_ids=full).logits[0, 6:].argmax(-1).tolist()
+            torch.save({"seq": seq, "ref": ref}, out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_engine_tensor_parallel_two_rank_gloo(tmp_path):
+    """Heads split over two ranks, partial sums of o / down all-reduced: same greedy tokens as the whole model."""
+    import os
+
+    import torch.multiprocessing as mp
+    out = str(tmp_path / "tp.pt")
+    mp.spawn(_tp_engine_worker, args=(2, 29800 + os.getpid() % 1500, out), nprocs=2, join=True)
+    got = torch.load(out)
+    assert got["seq"] == got["ref"]
