@@ -1,4 +1,5 @@
-// Persistent E8-D4 decode GEMV over a group of independent layers (batch 1..2).
+// Persistent decode GEMV over a group of independent layers of one codebook (E8-D4 or E8), two batch rows
+// per launch (larger batches run as several launches over the same weights).
 //
 // One launch, one block of 16 warps per SM, covers up to kMaxGroupLayers layers
 // whose inputs are all ready (q/k/v, gate/up, the experts of a mixture, or a
@@ -29,8 +30,15 @@
 // Critical blocks: two warps per block walk the CSR in units of 4 Q rows and add
 // sum (O[i] - code[65535]) * h*x to the same accumulators.
 //
-// Reference counterpart: e8d4_fused_kernel_t (csrc/eptq_kernels.cu:161-292),
-// one launch per layer and batch row there.
+// E8 variant (KIND == EPTQ_E8): same structure; the A fragments come from a packed 4-byte entry per index
+// (e8_decode), looked up in shared memory for the resident part of the table and in global memory for the
+// rest (e8_lookup).
+//
+// Optional fused work around each layer (EptqFusion): RMSNorm of the shared input, residual add, rotary
+// embedding and stores into a key/value cache, all done by the warp that finalizes a row tile.
+//
+// Reference counterparts: e8d4_fused_kernel_t (csrc/eptq_kernels.cu:161-292) and e8_fused_kernel
+// (csrc/eptq_kernels.cu:39-150), one launch per layer and batch row there.
 
 #include <cmath>
 #include <mutex>

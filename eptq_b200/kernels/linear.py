@@ -205,7 +205,8 @@ class EPTQLinear(nn.Module):
 
 def forward_group(layers, xs):
     """Apply several independent EPTQLinear layers in one kernel launch: layers[i](xs[i]) for all i.
-    Inputs need one common leading shape; returns the list of outputs.  Meant for q/k/v and gate/up."""
+    Inputs need one common leading shape with at most 16 rows; the layers must share one codebook and have no
+    group scales.  Returns the list of outputs.  Meant for q/k/v and gate/up."""
     lead = xs[0].shape[:-1]
     x2 = []
     for lin, x in zip(layers, xs):
