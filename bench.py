@@ -201,9 +201,13 @@ def run_gpu_arm(args):
     n_layers = args.layers
     # Row-parallel partial outputs: this library's one-shot push all-reduce over peer memory, or NCCL.
     comm = None
+    comm_note = None
     if world > 1 and not args.nccl:
         from eptq_b200.comm import PushAllReduce
-        comm = PushAllReduce(dist.group.WORLD, B * 8192, dev)
+        try:
+            comm = PushAllReduce(dist.group.WORLD, B * 8192, dev)
+        except RuntimeError as exc:              # raised on every rank alike: fall back to NCCL together
+            comm, comm_note = None, str(exc)
 
     def all_reduce(y):
         if comm is not None and y.numel() <= comm.n_max:
@@ -483,7 +487,8 @@ def run_gpu_arm(args):
                    "l2_policy": "inputs larger than L2 (1.66 GB of indices per step)" if n_layers >= 8 else "reduced layer count: may be L2-resident",
                    "launch_granularity": f"{group} independent linears per launch" if group > 1 else "one launch per linear",
                    "parallelism": f"tp{world}" if world > 1 else "single",
-                   "all_reduce": "none" if world == 1 else ("nccl" if comm is None else "one-shot push kernel over peer memory")},
+                   "all_reduce": "none" if world == 1 else ("nccl" if comm is None else "one-shot push kernel over peer memory"),
+                   "all_reduce_note": comm_note},
         "decode_tokens_per_s_linears_only": 1e3 / step_ms * B,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": (52379392 if (group == 7 and B == 1 and world == 1 and args.codebook == "e8d4") else None),

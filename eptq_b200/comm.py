@@ -36,20 +36,30 @@ class PushAllReduce:
         dist.all_gather_object(handles, mine, group=group)
         self._peers = []                       # keeps the mapped storages alive
         data_ptrs, flag_ptrs = [], []
-        for r, (hd, hf) in enumerate(handles):
-            if r == self.rank:
-                data_ptrs.append(self.data.data_ptr())
-                flag_ptrs.append(self.flags.data_ptr())
-                continue
-            # Open the handle in THIS GPU's context (not the owner's, which the handle tuple names): the
-            # mapping is then addressable by this GPU's kernels, with peer access enabled by the open.
-            here = device.index if device.index is not None else torch.cuda.current_device()
-            with torch.cuda.device(here):
-                sd = torch.UntypedStorage._new_shared_cuda(here, *hd[1:])
-                sf = torch.UntypedStorage._new_shared_cuda(here, *hf[1:])
-            self._peers.append((sd, sf))
-            data_ptrs.append(sd.data_ptr())
-            flag_ptrs.append(sf.data_ptr())
+        failure = None
+        try:
+            for r, (hd, hf) in enumerate(handles):
+                if r == self.rank:
+                    data_ptrs.append(self.data.data_ptr())
+                    flag_ptrs.append(self.flags.data_ptr())
+                    continue
+                # Open the handle in THIS GPU's context (not the owner's, which the handle tuple names): the
+                # mapping is then addressable by this GPU's kernels, with peer access enabled by the open.
+                here = device.index if device.index is not None else torch.cuda.current_device()
+                with torch.cuda.device(here):
+                    sd = torch.UntypedStorage._new_shared_cuda(here, *hd[1:])
+                    sf = torch.UntypedStorage._new_shared_cuda(here, *hf[1:])
+                self._peers.append((sd, sf))
+                data_ptrs.append(sd.data_ptr())
+                flag_ptrs.append(sf.data_ptr())
+        except Exception as exc:               # no peer access, IPC not permitted, ...
+            failure = exc
+        # Every rank learns whether every rank succeeded, so that all of them take the same path afterwards.
+        ok = torch.tensor([0 if failure is not None else 1], device=device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+        if int(ok.item()) == 0:
+            raise RuntimeError(f"eptq_b200: peer memory for the push all-reduce could not be mapped on every rank "
+                               f"(this rank: {failure!r})")
         self._data_ptrs = (C.c_void_p * self.world)(*data_ptrs)
         self._flag_ptrs = (C.c_void_p * self.world)(*flag_ptrs)
         dist.barrier(group=group)              # everyone has mapped everyone before the first store

@@ -432,7 +432,11 @@ def _main():
     comm = None
     if world > 1 and not args.nccl:
         from .comm import PushAllReduce
-        comm = PushAllReduce(group, args.batch * hidden, torch.device("cuda", local))
+        try:
+            comm = PushAllReduce(group, args.batch * hidden, torch.device("cuda", local))
+        except RuntimeError as exc:              # raised on every rank alike: NCCL instead
+            if rank == 0:
+                print(f"push all-reduce unavailable, using NCCL: {exc}", file=__import__("sys").stderr)
     eng = synthetic_llama_engine(hidden, inter, n_layers, heads, kv, vocab, args.quantizer, table,
                                  max_len=args.prefill + args.new_tokens, batch=args.batch, device=f"cuda:{local}",
                                  tp_rank=rank, tp_size=world, tp_group=group, comm=comm)
