@@ -83,7 +83,7 @@ def load() -> C.CDLL:
     for name, (res, args) in EXPORTS.items():
         fn = getattr(lib, name)          # AttributeError if the symbol is not exported
         fn.restype, fn.argtypes = res, args
-    if lib.eptq_abi_version() != 2:
+    if lib.eptq_abi_version() != 3:
         raise RuntimeError("libeptq_b200.so has an unexpected ABI version")
     _lib = lib
     return lib

@@ -27,6 +27,9 @@ bool group_gemv_supported(const EptqLayer* layers, int n, int B);
 size_t group_workspace_bytes(const EptqLayer* layers, int n, int B, int n_sms);
 int launch_gemv_group(const EptqLayer* layers, int n, const EptqFusion* fusions, const uint16_t* const* xs,
                       uint16_t* const* ys, int B, void* workspace, size_t workspace_bytes, cudaStream_t stream);
+bool stream_gemv_supported(const EptqLayer* layers, int n, int B);
+int launch_gemv_stream(const EptqLayer* layers, int n, const EptqFusion* fusions, const uint16_t* const* xs,
+                       uint16_t* const* ys, int B, void* workspace, size_t workspace_bytes, cudaStream_t stream);
 
 namespace {
 
@@ -66,6 +69,11 @@ int forward_checked(const EptqLayer& L, const uint16_t* x, uint16_t* y, int B,
             return launch_gemm_tcgen05_ws(L, x, y, B, status, static_cast<cudaStream_t>(stream));
         return launch_gemm_tcgen05(L, x, y, B, status, static_cast<cudaStream_t>(stream));
     }
+    if (stream_gemv_supported(&L, 1, B) && aligned16(y) && workspace != nullptr && workspace_bytes >= kPartialOffset) {
+        const uint16_t* xs[1] = {x};
+        uint16_t* ys[1] = {y};
+        return launch_gemv_stream(&L, 1, nullptr, xs, ys, B, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+    }
     // The E8 variant copies 219 KB of table into every block: not worth it for a small layer.
     const bool big_enough = L.quantizer != EPTQ_E8 || static_cast<long long>(L.M) * L.N >= (1LL << 20);
     if (big_enough && group_gemv_supported(&L, 1, B) && aligned16(y)) {
@@ -78,27 +86,6 @@ int forward_checked(const EptqLayer& L, const uint16_t* x, uint16_t* y, int B,
     if (mma_gemv_supported(L, B) && aligned16(L.g) && (L.bias == nullptr || aligned16(L.bias)) && aligned16(y))
         return launch_gemv_mma(L, x, y, B, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
     return launch_gemv_simt(L, x, y, B, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
-}
-
-// Round-to-nearest-even float -> FP8 E4M3 (1-4-3, bias 7, max 448), host side.
-uint8_t host_e4m3(float v) {
-    const uint8_t sign = v < 0.f ? 0x80 : 0x00;
-    float a = v < 0.f ? -v : v;
-    if (!(a == a)) return 0x7f;
-    if (a > 448.f) a = 448.f;
-    if (a < 0.0009765625f) return sign;                       // below half the smallest subnormal
-    int e = 0;
-    float m = std::frexp(a, &e);                              // a = m * 2^e, m in [0.5, 1)
-    int exp = e - 1;                                          // a = (2m) * 2^exp, 2m in [1, 2)
-    if (exp < -6) {                                           // subnormal: multiples of 2^-9
-        const int q = static_cast<int>(std::nearbyint(a * 512.f));
-        return sign | static_cast<uint8_t>(q);                // q == 8 is the smallest normal
-    }
-    int mant = static_cast<int>(std::nearbyint((2.f * m - 1.f) * 8.f));
-    if (mant == 8) { mant = 0; ++exp; }
-    if (exp > 8) { exp = 8; mant = 6; }
-    if (exp == 8 && mant > 6) mant = 6;
-    return sign | static_cast<uint8_t>(((exp + 7) << 3) | mant);
 }
 
 }  // namespace
@@ -147,6 +134,7 @@ size_t eptq_workspace_bytes(int M, int N, int B) {
 }
 
 size_t eptq_group_workspace_bytes(const EptqLayer* layers, int n_layers, int B) {
+    if (stream_gemv_supported(layers, n_layers, B)) return kPartialOffset;
     if (!group_gemv_supported(layers, n_layers, B)) return 0;
     return (group_workspace_bytes(layers, n_layers, B, 0) + 255) & ~static_cast<size_t>(255);
 }
@@ -162,8 +150,11 @@ int eptq_linear_forward_group_fused(const EptqLayer* layers, int n_layers, const
         if (xs[i] == nullptr || ys[i] == nullptr) return EPTQ_ERR_NULL;
         if (!aligned16(xs[i])) return EPTQ_ERR_ALIGN;
     }
-    if (!group_gemv_supported(layers, n_layers, B)) return EPTQ_ERR_UNSUPPORTED;
     if (workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return EPTQ_ERR_ALIGN;
+    if (stream_gemv_supported(layers, n_layers, B))
+        return launch_gemv_stream(layers, n_layers, fusions, xs, ys, B, workspace, workspace_bytes,
+                                  static_cast<cudaStream_t>(stream));
+    if (!group_gemv_supported(layers, n_layers, B)) return EPTQ_ERR_UNSUPPORTED;
     return launch_gemv_group(layers, n_layers, fusions, xs, ys, B, workspace, workspace_bytes,
                              static_cast<cudaStream_t>(stream));
 }
@@ -195,10 +186,10 @@ int eptq_prepare_d4_table8(const float* table, uint8_t* out, float* scale) {
     for (int i = 0; i < 2048; ++i) {
         const double r2 = table[i] / sc * 2.0;
         const double r = std::nearbyint(r2);
-        if (std::fabs(r2 - r) > 2e-3 || std::fabs(r) > 15.0) return EPTQ_ERR_UNSUPPORTED;
-        out[i] = host_e4m3(static_cast<float>(r * 0.5));
+        if (std::fabs(r2 - r) > 2e-3 || std::fabs(r) > 127.0) return EPTQ_ERR_UNSUPPORTED;
+        out[i] = static_cast<uint8_t>(static_cast<int8_t>(r));
     }
-    *scale = static_cast<float>(sc);
+    *scale = static_cast<float>(sc * 0.5);
     return EPTQ_OK;
 }
 

@@ -1,0 +1,778 @@
+// Streaming decode GEMV for E8-D4 layers, batch 1: the weight indices arrive through a ring of bulk-tensor
+// (TMA) loads, the codebook is an int8 table in shared memory, the products run on the integer tensor cores.
+//
+// One persistent block per SM; the launch covers 1..32 independent layers (as gemv_group.cu).  The work of
+// all layers is one sequence of units of 64 Q rows x 128 columns (16 KB of indices), row tile after row tile;
+// block b takes the contiguous range [b*U/G, (b+1)*U/G).
+//
+//   producer (one thread)   cp.async.bulk.tensor.3d loads, one per unit, into a ring of 6 stages; a stage is
+//                           reloaded as soon as its 16 consumer warps have copied their indices to registers.
+//                           The loads start at kernel entry, before the dependency on the previous kernel.
+//   16 consumer warps       warp w owns columns 8w..8w+7 of the stage and all 64 rows.  ldmatrix hands lane
+//                           (g,t) the index pair (row 8r+g, columns 2t, 2t+1) of row group r; each half
+//                           codeword is one 32-bit read of four int8 coordinates from a table with one copy
+//                           per lane (entry e of lane l at 128*e + 4*l: no bank conflicts); four such reads
+//                           are the A fragment of one mma.sync.m16n8k32.s8 (rows g / g+8 = the two halves of
+//                           the codeword, k = 4*t + dimension for two columns).  B holds the activation of
+//                           those columns as two int8 digits in the byte of the matching dimension, so the
+//                           eight result columns are (digit, dimension) and the int32 accumulators are exact.
+//   activations             x*h of the layer is scaled by 32000/max|x*h| to 16 bits and split into a low and
+//                           a high signed byte (planes in shared memory, built once per layer and block).
+//                           Error per term <= max|x*h| / 64000, independent of the length of the sum.
+//   end of a row tile       the warps add their int32 partials into a 4 KB shared-memory tile, 512 threads
+//                           turn it into floats, add them to the tile's fp32 accumulators in scratch and take
+//                           tickets; the last arrival (of all blocks and of the critical-block corrections)
+//                           applies g, bias and the fused epilogue -- the protocol of gemv_group.cu.
+//   2 correction warps      critical blocks: sum (O - code[marker]) * h*x, as in gemv_group.cu.
+//
+// Every wait on an mbarrier is bounded by the global timer; a wait that runs out stops further waiting in
+// that warp (the control flow still reaches every barrier) and EPTQ_ERR_TIMEOUT is written to the status
+// word of the scratch (the last counter).
+//
+// Reference counterpart: e8d4_fused_kernel_t (csrc/eptq_kernels.cu:161-292), one launch per layer there.
+
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "gemv_group_common.cuh"
+
+namespace eptq {
+
+using namespace groupdev;
+
+namespace {
+
+constexpr int kConsumerWarps = 16;
+constexpr int kProducerWarp = kConsumerWarps;                       // warp index
+constexpr int kFinalizerWarp = kConsumerWarps + 1;
+constexpr int kStreamCorrWarps = 2;                                 // warps 18, 19
+constexpr int kAuxWarps = 1 + kStreamCorrWarps;                     // finalizer and correction warps
+constexpr int kStreamThreads = (kConsumerWarps + 1 + kAuxWarps) * 32;   // five warpgroups
+constexpr int kStages = 6;
+constexpr int kStageBytes = 64 * 128 * 2;
+constexpr int kStreamMaxN = 27648;                                  // columns the digit planes hold
+// Shared memory by absolute shared-window address (dynamic shared memory starts at 0x400 on sm_100; the
+// kernel checks it).  The table sits on a 64 KB boundary so that a lookup address is (bits of q) | constant.
+constexpr unsigned kBase = 0x400u;
+constexpr unsigned kFullBar = 0x400u;                               // kStages x 8 bytes
+constexpr unsigned kEmptyBar = 0x440u;
+constexpr unsigned kRedFull = 0x480u;                               // 2 x 8: a flush buffer holds a finished tile
+constexpr unsigned kRedFree = 0x490u;                               // 2 x 8: the finalizer has emptied it
+constexpr unsigned kMail = 0x4A0u;                                  // 2 x {layer, row tile, units, scale}
+constexpr unsigned kMisc = 0x500u;                                  // 64 floats of reductions and results
+constexpr unsigned kRed = 0x800u;                                   // 2 x [digit][64 rows][8] int32
+constexpr unsigned kPlane = 0x2800u;                                // low digits, then high digits
+constexpr unsigned kTable = 0x10000u;
+constexpr unsigned kRing = 0x20000u;
+constexpr unsigned kSmemEnd = kRing + kStages * kStageBytes;        // 0x38000
+constexpr int kStreamSmemBytes = static_cast<int>(kSmemEnd - kBase);
+static_assert(kPlane + 2 * kStreamMaxN <= kTable, "digit planes overlap the table");
+
+struct StreamArgs {
+    GroupArgs g;                                  // layers and scratch; W = units, nw = blocks
+    alignas(64) CUtensorMap maps[kMaxGroupLayers];
+    float unit;                                   // table value = integer coordinate * unit
+    float inv_unit;
+    int* status;
+    unsigned long long wait_ns;                   // limit of one mbarrier wait
+};
+
+// Phase time stamps for latency studies: compiled in only with -DEPTQ_STREAM_TRACE (never in the shipped
+// library).  Slot k of block b is g_stream_trace[b * 8 + k], nanoseconds of the global timer.
+#ifdef EPTQ_STREAM_TRACE
+__device__ unsigned long long* g_stream_trace = nullptr;
+__device__ __forceinline__ void stream_trace(int slot) {
+    if ((threadIdx.x & 31) == 0 && g_stream_trace != nullptr) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        g_stream_trace[blockIdx.x * 8 + slot] = t;
+    }
+}
+#define EPTQ_STRACE(slot, cond) do { if (cond) stream_trace(slot); } while (0)
+#else
+#define EPTQ_STRACE(slot, cond) do { } while (0)
+#endif
+
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(unsigned bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(unsigned bar, unsigned parity) {
+    unsigned done;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    return done != 0;
+}
+// Bounded wait: false when `limit_ns` of the global timer pass without the phase completing.
+__device__ __noinline__ bool mbar_wait_slow(unsigned bar, unsigned parity, unsigned long long limit_ns) {
+    unsigned long long t0;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    for (;;) {
+        for (int i = 0; i < 64; ++i)
+            if (mbar_try(bar, parity)) return true;
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        if (t - t0 > limit_ns) return false;
+    }
+}
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, unsigned long long limit_ns) {
+    return mbar_try(bar, parity) || mbar_wait_slow(bar, parity, limit_ns);
+}
+__device__ __forceinline__ unsigned lds32(unsigned addr) {
+    unsigned v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint4 lds128(unsigned addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ unsigned lds16(unsigned addr) {
+    unsigned short v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts32(unsigned addr, unsigned v) {
+    asm volatile("st.shared.u32 [%0], %1;" :: "r"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void sts64(unsigned addr, unsigned a, unsigned b) {
+    asm volatile("st.shared.v2.u32 [%0], {%1,%2};" :: "r"(addr), "r"(a), "r"(b) : "memory");
+}
+__device__ __forceinline__ void sts128(unsigned addr, unsigned a, unsigned b, unsigned c, unsigned d) {
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" :: "r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ unsigned prmt(unsigned a, unsigned b, unsigned sel) {
+    unsigned d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+// (a & m) | (b & ~m)
+__device__ __forceinline__ unsigned bitsel(unsigned a, unsigned b, unsigned m) {
+    unsigned d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xE4;" : "=r"(d) : "r"(a), "r"(b), "r"(m));
+    return d;
+}
+__device__ __forceinline__ void ldsm4(unsigned addr, unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void imma(int (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void consumer_barrier() {
+    asm volatile("bar.sync 1, %0;" :: "n"(kConsumerWarps * 32) : "memory");
+}
+// Four fp16 table values -> four int8 lattice coordinates in one word.
+__device__ __forceinline__ unsigned pack_coords(uint2 v, float inv_unit) {
+    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&v.x));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
+    return (static_cast<unsigned>(__float2int_rn(a.x * inv_unit)) & 0xFFu) |
+           ((static_cast<unsigned>(__float2int_rn(a.y * inv_unit)) & 0xFFu) << 8) |
+           ((static_cast<unsigned>(__float2int_rn(b.x * inv_unit)) & 0xFFu) << 16) |
+           ((static_cast<unsigned>(__float2int_rn(b.y * inv_unit)) & 0xFFu) << 24);
+}
+
+// Arrival at row tile rt16 with `weight`: a tile is complete when cc128 units (one per 64x128 unit of its
+// 64-row tile, whoever processed it) and four correction quarters have arrived.  Returns true for the
+// arrival that completes it.  Call with the whole warp; the adds of all lanes are released by lane 0.
+__device__ __forceinline__ bool tile_arrive(const GroupArgs& p, const GroupLayer& L, int rt16, unsigned weight, int lane) {
+    __syncwarp();
+    unsigned old = 0;
+    if (lane == 0)
+        asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], %2;" : "=r"(old) : "l"(p.counters + L.tile0 + rt16), "r"(weight) : "memory");
+    old = __shfl_sync(0xffffffffu, old, 0);
+    return old + weight == static_cast<unsigned>(L.cc128) + 4u;
+}
+
+// Critical blocks of 4 consecutive Q rows, batch 1: 8 lanes per row, two entries per lane and pass (the
+// correction warps run with 64 registers).  Adds sum (O - marker code) * h*x to the tile's accumulators and
+// arrives as one of the tile's four correction quarters.
+template <typename WaitFn>
+__device__ __forceinline__ void stream_correction_unit(const GroupArgs& p, const GroupLayer& L, int qt, int lane,
+                                                       float c0, float c1, float c2, float c3, const float* inv_rms,
+                                                       WaitFn wait_dep) {
+    const int row = qt * 4 + (lane >> 3);
+    const int sub = lane & 7;
+    const int rt = qt >> 2;
+    float acc[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+    int lo = 0, hi = 0;
+    if (row < L.M) {
+        lo = __ldg(L.O_row_ptr + row);
+        hi = __ldg(L.O_row_ptr + row + 1);
+    }
+    bool first = true;
+    for (int i = lo + sub; __any_sync(0xffffffffu, i < hi) || first; i += 16) {
+        int col[2];
+        float hv[2];
+        uint4 ov[2];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) col[j] = (i + 8 * j < hi) ? __ldg(L.O_col + i + 8 * j) : -1;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            if (col[j] >= 0) {
+                hv[j] = __half2float(__ldg(L.h + col[j]));
+                ov[j] = ldg128(L.O_vals + static_cast<size_t>(i + 8 * j) * 8);
+            } else {
+                hv[j] = 0.f;
+                ov[j] = make_uint4(0, 0, 0, 0);
+            }
+        }
+        if (first) { wait_dep(); first = false; }
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            float o8[8];
+            unpack8(ov[j], o8);
+            const float xv = (col[j] >= 0) ? hv[j] * __half2float(__ldg(L.x + col[j])) : 0.f;
+            acc[0] = fmaf(o8[0] - c0, xv, acc[0]); acc[1] = fmaf(o8[1] - c1, xv, acc[1]);
+            acc[2] = fmaf(o8[2] - c2, xv, acc[2]); acc[3] = fmaf(o8[3] - c3, xv, acc[3]);
+            acc[4] = fmaf(o8[4] - c0, xv, acc[4]); acc[5] = fmaf(o8[5] - c1, xv, acc[5]);
+            acc[6] = fmaf(o8[6] - c2, xv, acc[6]); acc[7] = fmaf(o8[7] - c3, xv, acc[7]);
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        acc[k] += __shfl_xor_sync(0xffffffffu, acc[k], 1);
+        acc[k] += __shfl_xor_sync(0xffffffffu, acc[k], 2);
+        acc[k] += __shfl_xor_sync(0xffffffffu, acc[k], 4);
+    }
+    if (sub == 0 && lo < hi) {
+        float* dst = p.acc + L.acc_off + static_cast<size_t>(rt) * p.B * 128 + ((qt & 3) * 4 + (lane >> 3)) * 8;
+        red_add4(dst, acc[0], acc[1], acc[2], acc[3]);
+        red_add4(dst + 4, acc[4], acc[5], acc[6], acc[7]);
+    }
+    if (tile_arrive(p, L, rt, 1u, lane)) finalize_tile(p, L, rt, lane, load_affine(L, rt, lane), inv_rms);
+}
+
+__global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __grid_constant__ StreamArgs P) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    const GroupArgs& p = P.g;
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const unsigned base = smem_addr(smem_raw);
+    if (base != kBase) {                                   // layout assumption broken: refuse, do not touch memory
+        if (threadIdx.x == 0) atomicExch(P.status, EPTQ_ERR_LAUNCH);
+        return;
+    }
+    asm volatile("griddepcontrol.launch_dependents;");
+    EPTQ_STRACE(0, warp == 0);
+
+    const unsigned W32 = static_cast<unsigned>(p.W), nw32 = static_cast<unsigned>(p.nw);
+    const unsigned u_begin = (blockIdx.x * W32) / nw32, u_end = ((blockIdx.x + 1u) * W32) / nw32;   // W * nw < 2^32
+    const int n_units = static_cast<int>(u_end - u_begin);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(kFullBar + 8 * s, 1);
+            mbar_init(kEmptyBar + 8 * s, kConsumerWarps * 32);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(kRedFull + 8 * b, kConsumerWarps * 32);
+            mbar_init(kRedFree + 8 * b, 32);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+
+    // Position of the block's first unit.
+    int l0 = 0;
+    while (l0 + 1 < p.n_layers && static_cast<unsigned>(p.L[l0 + 1].unit0) <= u_begin) ++l0;
+    const int local0 = static_cast<int>(u_begin) - p.L[l0].unit0;
+    const int rt0 = local0 / p.L[l0].cc128, cc0 = local0 - rt0 * p.L[l0].cc128;
+    float* misc = reinterpret_cast<float*>(smem_raw + (kMisc - kBase));
+
+    // Registers: the block starts with 96 per thread (640 threads); the warpgroup of the producer, the
+    // finalizer and the correction warps gives up 32 per thread, the four consumer warpgroups take 8 each (the
+    // sums match: 128 * 32 = 512 * 8, and an increase waits for registers released inside the block).  The
+    // change sits inside each role's own branch (a path that saw both would be held to the lower limit) and is
+    // one instruction for the whole fifth warpgroup.
+    if (warp >= kProducerWarp) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+
+        // ------------------------------------------------------------ producer
+        if (warp == kProducerWarp) {
+            if (lane == 0) {
+                int l = l0, rt = rt0, cc = cc0, ncc = p.L[l0].cc128, nrt = p.L[l0].rt64;
+                int s = 0;
+                unsigned ph = 0;
+                for (int i = 0; i < n_units; ++i) {
+                    if (i >= kStages && !mbar_wait(kEmptyBar + 8 * s, ph ^ 1u, P.wait_ns)) {
+                        atomicExch(P.status, EPTQ_ERR_TIMEOUT);
+                        break;
+                    }
+                    mbar_expect_tx(kFullBar + 8 * s, kStageBytes);
+                    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                                 :: "r"(kRing + s * kStageBytes), "l"(&P.maps[l]), "r"(0), "r"(rt * 64), "r"(cc * 2), "r"(kFullBar + 8 * s)
+                                 : "memory");
+                    if (++cc == ncc) {
+                        cc = 0;
+                        if (++rt == nrt) {
+                            rt = 0;
+                            if (++l < p.n_layers) { ncc = p.L[l].cc128; nrt = p.L[l].rt64; }
+                        }
+                    }
+                    if (++s == kStages) { s = 0; ph ^= 1u; }
+                }
+            }
+            EPTQ_STRACE(7, true);
+            return;
+        }
+
+        if (p.x_norm) asm volatile("bar.sync 2, %0;" :: "n"((kConsumerWarps + kAuxWarps) * 32) : "memory");
+        const float* inv_rms = p.x_norm ? misc + 40 : nullptr;
+
+        // ------------------------------------------------------------ finalizer
+        // One flush per (layer, 64-row tile) the block's range touches, in order: the consumers leave the int32
+        // sums of the tile in a flush buffer; this warp turns them into floats, adds them to the accumulators
+        // in scratch, arrives at the four 16-row tiles and finalizes those it completes.
+        if (warp == kFinalizerWarp) {
+            int l = l0, rt = rt0, cc = cc0;
+            int left = n_units;
+            unsigned k = 0;
+            bool waited = false;
+            while (left > 0) {
+                const GroupLayer& L = p.L[l];
+                const int seg = min(left, L.cc128 - cc);           // units of this tile in the range
+                const unsigned b = k & 1u;
+                if (!mbar_wait(kRedFull + 8 * b, (k >> 1) & 1u, P.wait_ns)) {
+                    if (lane == 0) atomicExch(P.status, EPTQ_ERR_TIMEOUT);
+                    break;
+                }
+                const float scale = __uint_as_float(lds32(kMail + 16 * b + 12));
+                const unsigned buf = kRed + b * 4096;
+                // This lane: row lane>>1 of each 16-row tile, dimensions 4*(lane&1)..+3.  The buffer stores
+                // dimension d at d ^ 4*((row>>2)&1) ^ digit: the halves of a row swap when bit 2 of the row is
+                // set, and the high-digit words are pairwise exchanged.
+                uint4 lo[4], hi[4];
+                const unsigned my = static_cast<unsigned>((lane * 4) ^ (((lane >> 3) & 1) << 2));
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    lo[j] = lds128(buf + (j * 128 + my) * 4);
+                    const uint4 hsw = lds128(buf + 2048 + (j * 128 + my) * 4);
+                    hi[j] = make_uint4(hsw.y, hsw.x, hsw.w, hsw.z);
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    sts128(buf + (j * 128 + lane * 4) * 4, 0u, 0u, 0u, 0u);
+                    sts128(buf + 2048 + (j * 128 + lane * 4) * 4, 0u, 0u, 0u, 0u);
+                }
+                mbar_arrive(kRedFree + 8 * b);
+                if (!waited) { asm volatile("griddepcontrol.wait;" ::: "memory"); waited = true; }
+                Affine aff[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int rt16 = rt * 4 + j;
+                    if (rt16 < L.row_tiles) {
+                        aff[j] = load_affine(L, rt16, lane);
+                        float* dst = p.acc + L.acc_off + static_cast<size_t>(rt16) * p.B * 128 + lane * 4;
+                        red_add4(dst, fmaf(256.f, static_cast<float>(static_cast<int>(hi[j].x)), static_cast<float>(static_cast<int>(lo[j].x))) * scale,
+                                 fmaf(256.f, static_cast<float>(static_cast<int>(hi[j].y)), static_cast<float>(static_cast<int>(lo[j].y))) * scale,
+                                 fmaf(256.f, static_cast<float>(static_cast<int>(hi[j].z)), static_cast<float>(static_cast<int>(lo[j].z))) * scale,
+                                 fmaf(256.f, static_cast<float>(static_cast<int>(hi[j].w)), static_cast<float>(static_cast<int>(lo[j].w))) * scale);
+                    }
+                }
+                // one round trip for the four arrivals
+                __syncwarp();
+                unsigned old = 0;
+                const unsigned weight = static_cast<unsigned>(seg);
+                if (lane < 4 && rt * 4 + lane < L.row_tiles)
+                    asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], %2;"
+                                 : "=r"(old) : "l"(p.counters + L.tile0 + rt * 4 + lane), "r"(weight) : "memory");
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const unsigned oj = __shfl_sync(0xffffffffu, old, j);
+                    if (rt * 4 + j < L.row_tiles && oj + weight == static_cast<unsigned>(L.cc128) + 4u)
+                        finalize_tile(p, L, rt * 4 + j, lane, aff[j], inv_rms);
+                }
+                left -= seg;
+                cc = 0;
+                if (++rt == L.rt64) { rt = 0; ++l; }
+                ++k;
+            }
+            EPTQ_STRACE(5, true);
+            return;
+        }
+
+        // ------------------------------------------------------------ correction warps
+        {
+            // What the main loop adds for a marker: entry (class 3, code 127) in both halves.
+            const unsigned e511 = pack_coords(__ldg(p.table16 + 511), P.inv_unit);
+            const float c0 = static_cast<float>(static_cast<signed char>(e511 & 0xFF)) * P.unit;
+            const float c1 = static_cast<float>(static_cast<signed char>((e511 >> 8) & 0xFF)) * P.unit;
+            const float c2 = static_cast<float>(static_cast<signed char>((e511 >> 16) & 0xFF)) * P.unit;
+            const float c3 = static_cast<float>(static_cast<signed char>(e511 >> 24)) * P.unit;
+            bool waited = false;
+            const int cw = blockIdx.x * kStreamCorrWarps + (warp - kFinalizerWarp - 1);
+            int l = 0;
+            for (int u = cw; u < p.corr_units; u += p.n_corr_warps) {
+                while (l + 1 < p.n_layers && p.L[l + 1].corr0 <= u) ++l;
+                stream_correction_unit(p, p.L[l], u - p.L[l].corr0, lane, c0, c1, c2, c3, inv_rms,
+                                       [&]() { if (!waited) { asm volatile("griddepcontrol.wait;" ::: "memory"); waited = true; } });
+            }
+            EPTQ_STRACE(6, warp == kFinalizerWarp + 1);
+            return;
+        }
+    }
+
+    // ---------------------------------------------------------------- consumers
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
+    const int tid = threadIdx.x;                            // 0..511
+    // Table, one copy per lane: entry e (raw index bits: true (class, code) ^ 0x100) of lane l at kTable + 128 e + 4 l.
+    {
+        const unsigned v = pack_coords(__ldg(p.table16 + (tid ^ 0x100)), P.inv_unit);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) sts128(kTable + tid * 128 + ((c + tid) & 7) * 16, v, v, v, v);
+    }
+    for (int i = tid; i < 2048; i += kConsumerWarps * 32) sts32(kRed + 4 * i, 0u);
+
+    const int g = lane >> 2, t = lane & 3;
+    const int chunk64 = warp >> 3, w8 = warp & 7;
+    const unsigned lane_tab = static_cast<unsigned>(lane * 4) | kTable;
+    const unsigned dsel = g & 3, psel = g >> 2;
+    // B fragment: the digit of plane psel goes to byte dsel (dimension), zeros elsewhere (PRMT index 4 = 0 byte).
+    const unsigned sel0 = 0x4444u ^ (0x4u << (4 * dsel));
+    const unsigned sel1 = 0x4444u ^ (0x5u << (4 * dsel));
+    const unsigned plane = kPlane + psel * kStreamMaxN + 8 * warp + 2 * t;
+    // ldmatrix row address of this lane inside a stage: matrix lane>>3 = row group, row lane&7, 128-byte swizzle.
+    const unsigned qm = kRing + static_cast<unsigned>(chunk64 * 8192 + ((lane >> 3) * 8 + (lane & 7)) * 128 + ((w8 ^ (lane & 7)) << 4));
+
+    bool ok = true;
+    bool dep_waited = false;
+    float out_scale = 0.f;
+
+    // Digit planes (and the fused RMSNorm factor) of layer l.  Four chunks of 8 columns per thread stay in
+    // registers between the maximum and the split into digits; longer rows reload the rest.
+    auto prepare_layer = [&](int l) {
+        const GroupLayer& L = p.L[l];
+        if (!dep_waited) { asm volatile("griddepcontrol.wait;" ::: "memory"); dep_waited = true; }
+        constexpr int kStride = kConsumerWarps * 32 * 8;
+        float xh[4][8];
+        float mx = 0.f, ss = 0.f;
+        {
+            uint4 xr[4], hr[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int c = tid * 8 + k * kStride;
+                xr[k] = make_uint4(0, 0, 0, 0); hr[k] = make_uint4(0, 0, 0, 0);
+                if (c < L.N) { xr[k] = ldg128(L.x + c); hr[k] = ldg128(L.h + c); }
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                float xv[8], hv[8];
+                unpack8(xr[k], xv);
+                unpack8(hr[k], hv);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    xh[k][e] = xv[e] * hv[e];
+                    mx = fmaxf(mx, fabsf(xh[k][e]));
+                    ss = fmaf(xv[e], xv[e], ss);
+                }
+            }
+        }
+        for (int c = tid * 8 + 4 * kStride; c < L.N; c += kStride) {
+            float xv[8], hv[8];
+            unpack8(ldg128(L.x + c), xv);
+            unpack8(ldg128(L.h + c), hv);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                mx = fmaxf(mx, fabsf(xv[e] * hv[e]));
+                ss = fmaf(xv[e], xv[e], ss);
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        }
+        consumer_barrier();                                 // the previous layer's readers of misc and planes are done
+        if (lane == 0) { misc[warp] = mx; misc[16 + warp] = ss; }
+        consumer_barrier();
+        float tot = 0.f;
+        mx = 0.f;
+#pragma unroll
+        for (int w = 0; w < kConsumerWarps; ++w) { mx = fmaxf(mx, misc[w]); tot += misc[16 + w]; }
+        const float S = mx > 0.f ? 32000.f / mx : 1.f;
+        out_scale = P.unit / S;
+        if (p.x_norm && tid == 0) misc[40] = rsqrtf(tot / static_cast<float>(L.N) + p.norm_eps);
+        const int n_pad = L.cc128 * 128;
+        auto digits = [&](int c, const float (&v)[8]) {
+            unsigned lo[2] = {0u, 0u}, hi[2] = {0u, 0u};
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const int q16 = __float2int_rn(v[e] * S);
+                const int h8 = (q16 + 128) >> 8, l8 = q16 - (h8 << 8);
+                lo[e >> 2] |= (static_cast<unsigned>(l8) & 0xFFu) << (8 * (e & 3));
+                hi[e >> 2] |= (static_cast<unsigned>(h8) & 0xFFu) << (8 * (e & 3));
+            }
+            sts64(kPlane + c, lo[0], lo[1]);
+            sts64(kPlane + kStreamMaxN + c, hi[0], hi[1]);
+        };
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int c = tid * 8 + k * kStride;
+            if (c < L.N) digits(c, xh[k]);
+            else if (c < n_pad) { sts64(kPlane + c, 0u, 0u); sts64(kPlane + kStreamMaxN + c, 0u, 0u); }
+        }
+        for (int c = tid * 8 + 4 * kStride; c < n_pad; c += kStride) {
+            if (c < L.N) {
+                float xv[8], hv[8], v[8];
+                unpack8(ldg128(L.x + c), xv);
+                unpack8(ldg128(L.h + c), hv);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] = xv[e] * hv[e];
+                digits(c, v);
+            } else {
+                sts64(kPlane + c, 0u, 0u);
+                sts64(kPlane + kStreamMaxN + c, 0u, 0u);
+            }
+        }
+        consumer_barrier();
+    };
+
+    int acc[8][4];
+#pragma unroll
+    for (int r = 0; r < 8; ++r)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[r][c] = 0;
+    unsigned flush_no = 0;
+
+    // End of this block's part of a 64-row tile: leave the sums in a flush buffer for the finalizer warp.
+    auto flush = [&]() {
+        const unsigned b = flush_no & 1u;
+        if (flush_no >= 2u && ok) ok = mbar_wait(kRedFree + 8 * b, ((flush_no >> 1) - 1u) & 1u, P.wait_ns);
+        // Word of (digit p, row, dimension d): p*512 + row*8 + (d ^ 4*((row>>2)&1) ^ p); the swizzle spreads the
+        // 32 lanes of one instruction (8 rows g, digit t>>1, dimension pair t&1) over the 32 banks.
+        const unsigned mine = kRed + b * 4096 + static_cast<unsigned>(((t >> 1) * 512 + g * 8) * 4);
+        const unsigned sw = static_cast<unsigned>(((g >> 2) << 2) ^ (t >> 1));
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const unsigned d = static_cast<unsigned>((c >> 1) * 4 + 2 * (t & 1) + (c & 1)) ^ sw;
+                asm volatile("red.shared.add.s32 [%0], %1;" :: "r"(mine + (r * 64 + d) * 4), "r"(acc[r][c]) : "memory");
+                acc[r][c] = 0;
+            }
+        if (tid == 0) sts32(kMail + 16 * b + 12, __float_as_uint(out_scale));
+        mbar_arrive(kRedFull + 8 * b);
+        ++flush_no;
+    };
+
+    int l = l0, rt = rt0, cc = cc0;
+    int ncc = p.L[l0].cc128, nrt = p.L[l0].rt64;
+    unsigned q[8];
+    EPTQ_STRACE(1, warp == 0);
+    prepare_layer(l);                                        // its barriers also publish the table and the zeroed buffers
+    EPTQ_STRACE(2, warp == 0);
+    if (p.x_norm) asm volatile("bar.arrive 2, %0;" :: "n"((kConsumerWarps + kAuxWarps) * 32) : "memory");
+    ok = mbar_wait(kFullBar, 0u, P.wait_ns);
+    EPTQ_STRACE(3, warp == 0);
+    ldsm4(qm, q[0], q[1], q[2], q[3]);
+    ldsm4(qm + 4096, q[4], q[5], q[6], q[7]);
+    unsigned plane_c = plane + cc * 128;
+    unsigned ph = 0;
+    int s = 0;
+    // One body for all stages (an unrolled ring would repeat the flush and the layer switch six times and no
+    // longer fit the instruction cache).
+    for (int i = 0; i < n_units;) {
+        unsigned a[8][4];
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            const unsigned qq = q[r];
+            const unsigned qs = qq >> 16;
+            const unsigned ia = (qq & 0xFF80u) | lane_tab;
+            const unsigned ib = (qs & 0xFF80u) | lane_tab;
+            a[r][0] = lds32(ia);
+            a[r][1] = lds32(bitsel(qq << 7, ia, 0x3F80u));
+            a[r][2] = lds32(ib);
+            a[r][3] = lds32(bitsel(qs << 7, ib, 0x3F80u));
+        }
+        mbar_arrive(kEmptyBar + 8 * s);                     // every lane: its indices are in registers
+        const unsigned pv = lds16(plane_c);
+        const unsigned b0 = prmt(pv, 0u, sel0), b1 = prmt(pv, 0u, sel1);
+        bool tile_end = false, layer_end = false;
+        plane_c += 128;
+        if (++cc == ncc) {
+            cc = 0;
+            plane_c = plane;
+            tile_end = true;
+            if (++rt == nrt) {
+                rt = 0;
+                layer_end = true;
+                if (++l < p.n_layers) { ncc = p.L[l].cc128; nrt = p.L[l].rt64; }
+            }
+        }
+        ++i;
+        if (++s == kStages) { s = 0; ph ^= 1u; }
+        if (i < n_units) {
+            if (ok) ok = mbar_wait(kFullBar + 8 * s, ph, P.wait_ns);
+            const unsigned stage = qm + s * kStageBytes;
+            ldsm4(stage, q[0], q[1], q[2], q[3]);
+            ldsm4(stage + 4096, q[4], q[5], q[6], q[7]);
+        }
+#pragma unroll
+        for (int r = 0; r < 8; ++r) imma(acc[r], a[r][0], a[r][1], a[r][2], a[r][3], b0, b1);
+        if (i == n_units) EPTQ_STRACE(4, warp == 0);
+        if (tile_end || i == n_units) flush();
+        if (layer_end && i < n_units) prepare_layer(l);
+    }
+    if (!ok && lane == 0) atomicExch(P.status, EPTQ_ERR_TIMEOUT);
+}
+
+// ------------------------------------------------------------------------------------------------ host
+
+PFN_cuTensorMapEncodeTiled_v12000 stream_map_encoder() {
+    static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, []() {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
+    });
+    return fn;
+}
+
+// Tensor map over Q seen as (64 columns, M rows, N/64 column chunks): one load brings 64 rows x two chunks.
+bool encode_q_map(const int16_t* Q, int M, int N, CUtensorMap* out) {
+    const cuuint64_t dims[3] = {64, static_cast<cuuint64_t>(M), static_cast<cuuint64_t>(N / 64)};
+    const cuuint64_t strides[2] = {static_cast<cuuint64_t>(N) * 2, 128};
+    const cuuint32_t box[3] = {64, 64, 2};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    return stream_map_encoder()(out, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<int16_t*>(Q), dims, strides, box, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+struct MapKey {
+    const void* q; int m, n;
+    bool operator==(const MapKey& o) const { return q == o.q && m == o.m && n == o.n; }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        return std::hash<const void*>()(k.q) ^ (static_cast<size_t>(k.m) * 0x9E3779B97F4A7C15ull) ^ (static_cast<size_t>(k.n) << 32);
+    }
+};
+
+int stream_sm_count() {
+    static int sms[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+    if (sms[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+        sms[dev] = n;
+    }
+    return sms[dev];
+}
+
+bool stream_layer_supported(const EptqLayer& L) {
+    return L.quantizer == EPTQ_E8D4 && L.S_group == nullptr && L.M > 0 && L.N > 0 && (L.N % 64) == 0 &&
+           L.N <= kStreamMaxN && L.table8 != nullptr && L.table8_scale > 0.f && L.table16 != nullptr &&
+           aligned16(L.table16) && L.Q != nullptr && L.g != nullptr &&
+           L.h != nullptr && L.O_row_ptr != nullptr && (L.n_masked == 0 || (L.O_vals != nullptr && L.O_col != nullptr)) &&
+           aligned16(L.Q) && aligned16(L.g) && aligned16(L.h) && (L.bias == nullptr || aligned16(L.bias)) &&
+           (L.n_masked == 0 || aligned16(L.O_vals));
+}
+
+}  // namespace
+
+bool stream_gemv_supported(const EptqLayer* layers, int n, int B) {
+    if (layers == nullptr || n < 1 || n > kMaxGroupLayers || B != 1 || stream_map_encoder() == nullptr) return false;
+    int tiles = 0;
+    long long units = 0;
+    for (int i = 0; i < n; ++i) {
+        if (!stream_layer_supported(layers[i])) return false;
+        if (layers[i].table16 != layers[0].table16 || layers[i].table8_scale != layers[0].table8_scale) return false;
+        tiles += (layers[i].M + 15) / 16;
+        units += static_cast<long long>((layers[i].M + 63) / 64) * ((layers[i].N + 127) / 128);
+    }
+    if (tiles > kMaxCounters - 1) return false;
+    if (static_cast<size_t>(tiles) * B * 128 * sizeof(float) > kPartialOffset - kCounterBytes) return false;
+    return units * 1024 < (1LL << 32);                     // owner arithmetic in 32 bits (blocks <= 1024)
+}
+
+int launch_gemv_stream(const EptqLayer* layers, int n, const EptqFusion* fusions, const uint16_t* const* xs,
+                       uint16_t* const* ys, int B, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+    if (!stream_gemv_supported(layers, n, B)) return EPTQ_ERR_UNSUPPORTED;
+    if (workspace == nullptr || workspace_bytes < kPartialOffset) return EPTQ_ERR_WORKSPACE;
+    const int n_sms = stream_sm_count();
+    if (n_sms < 1) return EPTQ_ERR_LAUNCH;
+
+    static StreamArgs args;                    // large: keep it off the stack; filled under a lock
+    static std::mutex args_mutex;
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> maps;
+    std::lock_guard<std::mutex> lock(args_mutex);
+    StreamArgs& a = args;
+    {
+        const int st = fill_group_args(a.g, layers, n, fusions, xs, ys, B, workspace);
+        if (st != EPTQ_OK) return st;
+    }
+    for (int i = 0; i < n; ++i) if (!aligned16(xs[i])) return EPTQ_ERR_ALIGN;
+    long long units = 0;
+    int corr_units = 0;
+    for (int i = 0; i < n; ++i) {
+        units += static_cast<long long>(a.g.L[i].rt64) * a.g.L[i].cc128;
+        corr_units += a.g.L[i].row_tiles * 4;
+        const MapKey key{layers[i].Q, layers[i].M, layers[i].N};
+        auto it = maps.find(key);
+        if (it == maps.end()) {
+            CUtensorMap m;
+            if (!encode_q_map(layers[i].Q, layers[i].M, layers[i].N, &m)) return EPTQ_ERR_LAUNCH;
+            if (maps.size() > 8192) maps.clear();
+            it = maps.emplace(key, m).first;
+        }
+        a.maps[i] = it->second;
+    }
+    const int blocks = units < n_sms ? static_cast<int>(units) : n_sms;
+    a.g.W = units;
+    a.g.nw = blocks;
+    a.g.corr_units = corr_units;
+    a.g.n_corr_warps = blocks * kStreamCorrWarps;
+    a.unit = layers[0].table8_scale;
+    a.inv_unit = 1.0f / layers[0].table8_scale;
+    a.status = reinterpret_cast<int*>(workspace) + (kMaxCounters - 1);
+    a.wait_ns = 2000000000ull;
+
+    static bool attr_done[64] = {};            // guarded by args_mutex
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return EPTQ_ERR_LAUNCH;
+    if (!attr_done[dev]) {
+        if (cudaFuncSetAttribute(gemv_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamSmemBytes) != cudaSuccess)
+            return EPTQ_ERR_LAUNCH;
+        attr_done[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(blocks);
+    cfg.blockDim = dim3(kStreamThreads);
+    cfg.dynamicSmemBytes = kStreamSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t err = cudaLaunchKernelEx(&cfg, gemv_stream_kernel, a);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return err == cudaSuccess ? EPTQ_OK : EPTQ_ERR_LAUNCH;
+}
+
+}  // namespace eptq
+
+#ifdef EPTQ_STREAM_TRACE
+extern "C" int eptq_debug_set_stream_trace(unsigned long long* device_buffer) {
+    return cudaMemcpyToSymbol(eptq::g_stream_trace, &device_buffer, sizeof(device_buffer)) == cudaSuccess ? 0 : 6;
+}
+#endif

@@ -128,10 +128,11 @@ def _(Q, codes, g, h, x, O_vals, O_col, O_row_ptr, bias):
 _table8_cache: Dict[tuple, Optional[Tuple[torch.Tensor, float]]] = {}
 
 
-def d4_table8(table: torch.Tensor) -> Optional[Tuple[torch.Tensor, float]]:
-    """(device uint8 (2048,) tensor, scale) with the E8-D4 table expressed as
-    scale * half-integer lattice coordinates in FP8 E4M3, or None if the table is
-    not such a multiple.  Prepared on the host once per table tensor."""
+def d4_table8(table: torch.Tensor):
+    """(host int8 (2048,) numpy array, scale) with the E8-D4 table expressed as
+    scale * integer lattice coordinates, or None if the table is not such a multiple
+    (a radially warped codebook).  Prepared on the host once per table tensor; the
+    library copies it into the kernel parameters at each launch."""
     key = (table.data_ptr(), table.device, table.dtype, table._version)
     if key in _table8_cache:
         return _table8_cache[key]
@@ -143,7 +144,7 @@ def d4_table8(table: torch.Tensor) -> Optional[Tuple[torch.Tensor, float]]:
         scale = C.c_float(0.0)
         st = _lib.load().eptq_prepare_d4_table8(host.ctypes.data, out.ctypes.data, C.addressof(scale))
         if st == 0:
-            res = (torch.from_numpy(out).to(table.device), float(scale.value))
+            res = (out.view(np.int8), float(scale.value))
     if len(_table8_cache) > 64:
         _table8_cache.clear()
     _table8_cache[key] = res
@@ -238,11 +239,11 @@ def _make_desc(quantizer_type: str, Q, table32, table16, g, h, O_vals, O_col, O_
         if packed is not None:
             d._keep = packed[0]                  # keep the device table alive as long as the descriptor
             d.table_packed, d.table_packed_scale = packed[0].data_ptr(), packed[1]
-    if quantizer_type == "e8_d4" and Q.is_cuda:
+    if quantizer_type == "e8_d4":
         t8 = d4_table8(table32 if table32 is not None else table16)
         if t8 is not None:
-            d._keep = t8[0]                      # keep the device table alive as long as the descriptor
-            d.table8, d.table8_scale = t8[0].data_ptr(), t8[1]
+            d._keep = t8[0]                      # keep the host table alive as long as the descriptor
+            d.table8, d.table8_scale = t8[0].ctypes.data, t8[1]
     return d
 
 

@@ -21,7 +21,7 @@
 extern "C" {
 #endif
 
-#define EPTQ_ABI_VERSION 2
+#define EPTQ_ABI_VERSION 3
 
 typedef enum EptqStatus {
     EPTQ_OK = 0,
@@ -51,10 +51,13 @@ enum { EPTQ_E8 = 0, EPTQ_E8D4 = 1 };
  *              Needed for bit-exact reconstruction (eptq_dequantize, eptq_gemm).
  *   table16    the same table rounded to fp16 (what the reference's kernels
  *              read, kernels/linear.py:93-95).  Needed by the GEMV.
- *   table8     E8-D4 only, optional: the raw lattice coordinates of the 512 codes
- *              (table = raw * table8_scale) as FP8 E4M3 bytes, 4 per code, made
- *              by eptq_prepare_d4_table8.  Enables the tensor-core GEMV; NULL
- *              selects the general kernel.
+ *   table8     E8-D4 only, optional, HOST memory: the 512 codes as int8 lattice
+ *              coordinates, 4 per code (table = coordinate * table8_scale), made by
+ *              eptq_prepare_d4_table8.  The library copies the 2 KB into the kernel's
+ *              parameters at each launch, so the buffer only has to live until the
+ *              call returns.  Enables the streaming integer-tensor-core GEMV
+ *              (batch 1, N a multiple of 64 and at most 27648, no group scales);
+ *              NULL selects the fp16-table kernels.
  *   table_packed  E8 only, optional: the table as table_packed_scale * (half-integer
  *              lattice coordinates), one 32-bit word per entry, 65536 words (entry
  *              65535 = the zero vector).  Coordinate c of dimension d is stored as
@@ -110,10 +113,10 @@ uint64_t eptq_launch_count(void);
 /*
  * Host-side, no GPU involved: express an E8-D4 table (512 x 4 fp32, already
  * divided by the radius, as the reference builds it in quantizers/e8_d4.py:83-86)
- * as scale * (half-integer lattice coordinates) and write the coordinates as
- * 2048 FP8 E4M3 bytes to `out`, the scale to `*scale`.  Returns
+ * as scale * (integer lattice coordinates, twice the half-integer D4 coordinates)
+ * and write the 2048 coordinates as int8 to `out`, the scale to `*scale`.  Returns
  * EPTQ_ERR_UNSUPPORTED when the table is not such a multiple (for example a
- * radially warped codebook); such layers run on the general kernel.
+ * radially warped codebook); such layers run on the fp16-table kernels.
  */
 int eptq_prepare_d4_table8(const float* table, uint8_t* out, float* scale);
 

@@ -29,7 +29,7 @@ def test_binding_covers_all_declared(built_library):
     from eptq_b200 import _lib
     assert sorted(_lib.EXPORTS) == declared_functions()
     lib = _lib.load()
-    assert lib.eptq_abi_version() == 2
+    assert lib.eptq_abi_version() == 3
     assert lib.eptq_strerror(0) == b"ok"
     assert b"workspace" in lib.eptq_strerror(5)
     assert lib.eptq_workspace_bytes(512, 4096, 1) > 0
@@ -58,14 +58,9 @@ def test_prepare_d4_table8_on_host(built_library):
     out = np.zeros(2048, np.uint8)
     scale = ctypes.c_float(0)
     assert lib.eptq_prepare_d4_table8(tab.ctypes.data, out.ctypes.data, ctypes.addressof(scale)) == 0
-    assert abs(scale.value - 1 / 1.75) < 1e-6
-    # decode E4M3 on the host and compare with the raw lattice coordinates
-    def e4m3(b):
-        s = -1.0 if b & 0x80 else 1.0
-        e, m = (b >> 3) & 0xF, b & 7
-        return s * (m / 8 * 2.0 ** -6 if e == 0 else (1 + m / 8) * 2.0 ** (e - 7))
-    dec = np.array([e4m3(int(b)) for b in out], dtype=np.float32)
-    assert np.array_equal(dec, oracle.d4_raw_codes().reshape(-1))
+    assert abs(scale.value - 0.5 / 1.75) < 1e-6
+    # int8 coordinates are twice the raw (half-integer) lattice coordinates
+    assert np.array_equal(out.view(np.int8).astype(np.float32) * 0.5, oracle.d4_raw_codes().reshape(-1))
     warped = tab * (1 + 0.05 * np.abs(tab))
     assert lib.eptq_prepare_d4_table8(np.ascontiguousarray(warped).ctypes.data, out.ctypes.data,
                                       ctypes.addressof(scale)) == 7
