@@ -29,6 +29,8 @@ EXPORTS = {
     "eptq_group_workspace_bytes": (_sz, [_vp, _i, _i]),
     "eptq_linear_forward_group": (_i, [_vp, _i, _vp, _vp, _i, _vp, _sz, _vp]),
     "eptq_linear_forward_group_fused": (_i, [_vp, _i, _vp, _vp, _vp, _i, _vp, _sz, _vp]),
+    "eptq_linear_forward_chain": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _sz, _vp]),
+    "eptq_workspace_status": (_i, [_vp, _vp, _vp]),
     "eptq_static_scratch_bytes": (_sz, []),
     "eptq_linear_forward_static_scratch": (_i, [_vp, _vp, _vp, _i, _vp]),
     "eptq_allreduce_data_bytes": (_sz, [_i, _i]),
@@ -54,7 +56,7 @@ class EptqLayer(C.Structure):
     ]
 
 
-X_PLAIN, X_RMSNORM = 0, 2
+X_PLAIN, X_RMSNORM, X_SILU_MUL = 0, 2, 3
 Y_STORE, Y_ADD_RESIDUAL, Y_ROPE, Y_ROPE_TO_CACHE, Y_TO_CACHE = 0, 1, 2, 3, 4
 
 
@@ -63,7 +65,7 @@ class EptqFusion(C.Structure):
     _fields_ = [
         ("x_op", C.c_int32), ("y_op", C.c_int32), ("norm_eps", C.c_float), ("rope_scaling", C.c_float),
         ("max_len", C.c_int32), ("reserved", C.c_int32),
-        ("residual", _vp), ("position", _vp), ("inv_freq", _vp),
+        ("residual", _vp), ("position", _vp), ("inv_freq", _vp), ("x_aux", _vp),
     ]
 
 

@@ -28,8 +28,9 @@ size_t group_workspace_bytes(const EptqLayer* layers, int n, int B, int n_sms);
 int launch_gemv_group(const EptqLayer* layers, int n, const EptqFusion* fusions, const uint16_t* const* xs,
                       uint16_t* const* ys, int B, void* workspace, size_t workspace_bytes, cudaStream_t stream);
 bool stream_gemv_supported(const EptqLayer* layers, int n, int B);
-int launch_gemv_stream(const EptqLayer* layers, int n, const EptqFusion* fusions, const uint16_t* const* xs,
-                       uint16_t* const* ys, int B, void* workspace, size_t workspace_bytes, cudaStream_t stream);
+int launch_gemv_stream(const EptqLayer* layers, int n, const EptqFusion* fusions, const int* phases,
+                       const uint16_t* const* xs, uint16_t* const* ys, int B, void* workspace, size_t workspace_bytes,
+                       cudaStream_t stream);
 
 namespace {
 
@@ -72,7 +73,7 @@ int forward_checked(const EptqLayer& L, const uint16_t* x, uint16_t* y, int B,
     if (stream_gemv_supported(&L, 1, B) && aligned16(y) && workspace != nullptr && workspace_bytes >= kPartialOffset) {
         const uint16_t* xs[1] = {x};
         uint16_t* ys[1] = {y};
-        return launch_gemv_stream(&L, 1, nullptr, xs, ys, B, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+        return launch_gemv_stream(&L, 1, nullptr, nullptr, xs, ys, B, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
     }
     // The E8 variant copies 219 KB of table into every block: not worth it for a small layer.
     const bool big_enough = L.quantizer != EPTQ_E8 || static_cast<long long>(L.M) * L.N >= (1LL << 20);
@@ -152,11 +153,39 @@ int eptq_linear_forward_group_fused(const EptqLayer* layers, int n_layers, const
     }
     if (workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return EPTQ_ERR_ALIGN;
     if (stream_gemv_supported(layers, n_layers, B))
-        return launch_gemv_stream(layers, n_layers, fusions, xs, ys, B, workspace, workspace_bytes,
+        return launch_gemv_stream(layers, n_layers, fusions, nullptr, xs, ys, B, workspace, workspace_bytes,
                                   static_cast<cudaStream_t>(stream));
     if (!group_gemv_supported(layers, n_layers, B)) return EPTQ_ERR_UNSUPPORTED;
     return launch_gemv_group(layers, n_layers, fusions, xs, ys, B, workspace, workspace_bytes,
                              static_cast<cudaStream_t>(stream));
+}
+
+int eptq_linear_forward_chain(const EptqLayer* layers, int n_layers, const EptqFusion* fusions, const int* phases,
+                              const uint16_t* const* xs, uint16_t* const* ys, int B,
+                              void* workspace, size_t workspace_bytes, void* stream) {
+    if (layers == nullptr || xs == nullptr || ys == nullptr || phases == nullptr) return EPTQ_ERR_NULL;
+    if (n_layers < 1 || B < 1) return EPTQ_ERR_SHAPE;
+    for (int i = 0; i < n_layers; ++i) {
+        const int st = check_layer_common(&layers[i]);
+        if (st != EPTQ_OK) return st;
+        if (xs[i] == nullptr || ys[i] == nullptr) return EPTQ_ERR_NULL;
+        if (!aligned16(xs[i])) return EPTQ_ERR_ALIGN;
+    }
+    if (workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return EPTQ_ERR_ALIGN;
+    if (!stream_gemv_supported(layers, n_layers, B)) return EPTQ_ERR_UNSUPPORTED;
+    return launch_gemv_stream(layers, n_layers, fusions, phases, xs, ys, B, workspace, workspace_bytes,
+                              static_cast<cudaStream_t>(stream));
+}
+
+// Status word of a scratch buffer (the last counter): EPTQ_OK, or EPTQ_ERR_TIMEOUT / EPTQ_ERR_LAUNCH left by a
+// kernel whose bounded wait ran out.  Copies it to the host on `stream`, waits for the copy, clears the word.
+int eptq_workspace_status(void* workspace, int* host_out, void* stream) {
+    if (workspace == nullptr || host_out == nullptr) return EPTQ_ERR_NULL;
+    int* word = reinterpret_cast<int*>(workspace) + (kMaxCounters - 1);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (cudaMemcpyAsync(host_out, word, sizeof(int), cudaMemcpyDeviceToHost, s) != cudaSuccess) return EPTQ_ERR_LAUNCH;
+    if (cudaMemsetAsync(word, 0, sizeof(int), s) != cudaSuccess) return EPTQ_ERR_LAUNCH;
+    return cudaStreamSynchronize(s) == cudaSuccess ? EPTQ_OK : EPTQ_ERR_LAUNCH;
 }
 
 int eptq_linear_forward_group(const EptqLayer* layers, int n_layers,

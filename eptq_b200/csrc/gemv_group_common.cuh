@@ -34,6 +34,12 @@ struct GroupLayer {
     int unit0;              // index of this layer's first unit in the global sequence
     int rt64;               // ceil(M / 64)
     int cc128;              // ceil(N / 128)
+    // chained launches (gemv_stream.cu): layers of a later phase read what earlier phases wrote
+    int phase;
+    int wait_tiles;         // row tiles of the previous phase: x may be read once that many of them are finalized
+    int x_op;               // EPTQ_X_PLAIN, EPTQ_X_RMSNORM or EPTQ_X_SILU_MUL
+    float norm_eps;
+    const __half* x_aux;    // EPTQ_X_SILU_MUL: x = silu(x) * x_aux
     // fused epilogue (EptqFusion): what the finalizing warp does with a finished row tile
     const __half* residual;     // EPTQ_Y_ADD_RESIDUAL
     const long long* position;  // rotary angle / cache row (device scalar)
@@ -55,8 +61,15 @@ struct GroupArgs {
     int nw;                 // total main warps
     int corr_units;         // total correction units
     int n_corr_warps;
-    int x_norm;             // EPTQ_X_RMSNORM: all layers read one x; outputs are scaled by rsqrt(mean(x^2) + eps)
+    int x_norm;             // EPTQ_X_RMSNORM on every layer, all reading one x: outputs are scaled by rsqrt(mean(x^2) + eps)
     float norm_eps;
+    // phases of a chained launch: units and row tiles per phase, completion counter
+    int n_phases;
+    int total_tiles;
+    unsigned* done;         // [phase][32] row tiles finalized in this launch, then one word of finished blocks; the
+                            // last block to finish puts the zeros back.  Null when the launch has one phase.
+    int phase_unit0[kMaxGroupLayers];
+    int phase_units[kMaxGroupLayers];
 };
 
 namespace groupdev {
@@ -149,7 +162,7 @@ __device__ __forceinline__ void finalize_tile(const GroupArgs& p, const GroupLay
             if (pos < 0 || pos >= L.max_len) continue;
         }
         if (L.y_op == EPTQ_Y_ADD_RESIDUAL) {
-            const uint2 rv = *reinterpret_cast<const uint2*>(L.residual + static_cast<size_t>(b) * 8 * L.M + o);
+            const uint2 rv = __ldcg(reinterpret_cast<const uint2*>(L.residual + static_cast<size_t>(b) * 8 * L.M + o));   // may be another block's store of this launch
             o01 = __hadd2(*reinterpret_cast<const __half2*>(&rv.x), o01);
             o23 = __hadd2(*reinterpret_cast<const __half2*>(&rv.y), o23);
         }
@@ -158,8 +171,15 @@ __device__ __forceinline__ void finalize_tile(const GroupArgs& p, const GroupLay
         outv.y = *reinterpret_cast<const unsigned*>(&o23);
         *reinterpret_cast<uint2*>(dst) = outv;
     }
+    if (p.done != nullptr) {
+        // Chained launch: count the finished tile of this phase (release: the stores above are visible to
+        // whoever sees the count).  32 counters per phase, one 128-byte line, so that the tiles of a phase do not
+        // queue on one address; a waiter sums the line.
+        __syncwarp();
+        if (lane == 0)
+            asm volatile("red.release.gpu.global.add.u32 [%0], 1;" :: "l"(p.done + L.phase * 32 + ((L.tile0 + rt) & 31)) : "memory");
+    }
 }
-
 
 // Take a ticket for row tile rt of layer L; the last of the expected arrivals (n_main GEMV partials and
 // 4 correction quarters) reads the tile's accumulators, zeroes them for the next launch and writes y.
@@ -254,7 +274,8 @@ __device__ __forceinline__ void correction_unit(const GroupArgs& p, const GroupL
 // Host: fills the per-launch description from the C-ABI arguments (everything except the work split, which
 // differs between the kernels: W, nw, corr_units, n_corr_warps).  Checks the fusion arguments.
 inline int fill_group_args(GroupArgs& a, const EptqLayer* layers, int n, const EptqFusion* fusions,
-                           const uint16_t* const* xs, uint16_t* const* ys, int B, void* workspace) {
+                           const uint16_t* const* xs, uint16_t* const* ys, int B, void* workspace,
+                           const int* phases = nullptr) {
     const bool e8 = layers[0].quantizer == EPTQ_E8;
     a.table16 = reinterpret_cast<const uint2*>(layers[0].table16);
     a.packed = e8 ? layers[0].table_packed : nullptr;
@@ -264,14 +285,18 @@ inline int fill_group_args(GroupArgs& a, const EptqLayer* layers, int n, const E
     a.B = B;
     a.x_norm = 0;
     a.norm_eps = 0.f;
+    a.n_phases = 1;
+    a.total_tiles = 0;
+    a.done = nullptr;
     if (fusions != nullptr) {
-        // Fused RMSNorm is a property of the launch: all layers or none, one shared input.
+        // Fused RMSNorm without phases is a property of the launch: all layers or none, one shared input.
         int normed = 0;
         for (int i = 0; i < n; ++i) {
             if (fusions[i].x_op == EPTQ_X_RMSNORM) ++normed;
+            else if (fusions[i].x_op == EPTQ_X_SILU_MUL) { if (phases == nullptr) return EPTQ_ERR_UNSUPPORTED; }
             else if (fusions[i].x_op != EPTQ_X_PLAIN) return EPTQ_ERR_UNSUPPORTED;
         }
-        if (normed != 0) {
+        if (normed != 0 && phases == nullptr) {
             if (normed != n) return EPTQ_ERR_UNSUPPORTED;
             for (int i = 0; i < n; ++i)
                 if (xs[i] != xs[0] || layers[i].N != layers[0].N || fusions[i].norm_eps != fusions[0].norm_eps)
@@ -282,6 +307,13 @@ inline int fill_group_args(GroupArgs& a, const EptqLayer* layers, int n, const E
             a.norm_eps = fusions[0].norm_eps;
         }
     }
+    if (phases != nullptr) {
+        if (phases[0] != 0) return EPTQ_ERR_SHAPE;
+        for (int i = 1; i < n; ++i)
+            if (phases[i] != phases[i - 1] && phases[i] != phases[i - 1] + 1) return EPTQ_ERR_SHAPE;
+        a.n_phases = phases[n - 1] + 1;
+    }
+    for (int k = 0; k < kMaxGroupLayers; ++k) { a.phase_unit0[k] = 0; a.phase_units[k] = 0; }
     long long strip0 = 0, poff = 0;
     int tile0 = 0, corr0 = 0, unit0 = 0;
     for (int i = 0; i < n; ++i) {
@@ -305,7 +337,27 @@ inline int fill_group_args(GroupArgs& a, const EptqLayer* layers, int n, const E
         G.rt64 = (L.M + 63) / 64;
         G.cc128 = (L.N + 127) / 128;
         G.unit0 = unit0;
+        G.phase = phases != nullptr ? phases[i] : 0;
+        G.wait_tiles = 0;
+        if (G.phase > 0) {
+            if (phases[i] != phases[i - 1]) {
+                a.phase_unit0[G.phase] = unit0;
+                int prev_tiles = 0;                          // row tiles of the previous phase
+                for (int j = i - 1; j >= 0 && phases[j] == phases[i - 1]; --j) prev_tiles += a.L[j].row_tiles;
+                G.wait_tiles = prev_tiles;
+            } else {
+                G.wait_tiles = a.L[i - 1].wait_tiles;
+            }
+        }
+        a.phase_units[G.phase] += G.rt64 * G.cc128;
         unit0 += G.rt64 * G.cc128;
+        G.x_op = fusions != nullptr ? fusions[i].x_op : EPTQ_X_PLAIN;
+        G.norm_eps = fusions != nullptr ? fusions[i].norm_eps : 0.f;
+        G.x_aux = fusions != nullptr ? reinterpret_cast<const __half*>(fusions[i].x_aux) : nullptr;
+        if (G.x_op == EPTQ_X_SILU_MUL) {
+            if (G.x_aux == nullptr) return EPTQ_ERR_NULL;
+            if (!aligned16(G.x_aux)) return EPTQ_ERR_ALIGN;
+        }
         int e = 0;
         std::frexp(L.h_absmax, &e);            // h_absmax = m * 2^e, m in [0.5, 1)  =>  2^-e <= 1/h_absmax
         G.x_scale = std::ldexp(1.0f, -e);
@@ -340,6 +392,7 @@ inline int fill_group_args(GroupArgs& a, const EptqLayer* layers, int n, const E
         tile0 += G.row_tiles;
         corr0 += G.row_tiles * 4;
     }
+    a.total_tiles = tile0;
     return EPTQ_OK;
 }
 

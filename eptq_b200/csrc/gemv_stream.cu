@@ -182,25 +182,121 @@ __device__ __forceinline__ unsigned pack_coords(uint2 v, float inv_unit) {
            ((static_cast<unsigned>(__float2int_rn(b.y * inv_unit)) & 0xFFu) << 24);
 }
 
-// Arrival at row tile rt16 with `weight`: a tile is complete when cc128 units (one per 64x128 unit of its
-// 64-row tile, whoever processed it) and four correction quarters have arrived.  Returns true for the
-// arrival that completes it.  Call with the whole warp; the adds of all lanes are released by lane 0.
-__device__ __forceinline__ bool tile_arrive(const GroupArgs& p, const GroupLayer& L, int rt16, unsigned weight, int lane) {
+// A run of units inside one 64-row tile of one layer: what a block processes between two flushes.
+struct Segment {
+    int l, rt, cc, n;
+    bool new_layer;          // the block has not prepared this layer's activations yet
+};
+// The block's work in order: for each phase its share [U*b/G, U*(b+1)/G) of the phase's units, cut at the ends
+// of 64-row tiles.  Producer, consumers and finalizer each walk the same sequence.
+struct SegmentWalk {
+    int k = -1;
+    unsigned pos = 0, end = 0;
+    int l = 0, last_l = -1;
+    __device__ __forceinline__ bool next(const GroupArgs& p, Segment& s) {
+        while (pos == end) {
+            if (++k >= p.n_phases) return false;
+            const unsigned U = static_cast<unsigned>(p.phase_units[k]), G = gridDim.x;      // U * G < 2^32 (host)
+            pos = static_cast<unsigned>(p.phase_unit0[k]) + (U * blockIdx.x) / G;
+            end = static_cast<unsigned>(p.phase_unit0[k]) + (U * (blockIdx.x + 1u)) / G;
+        }
+        while (l + 1 < p.n_layers && static_cast<unsigned>(p.L[l + 1].unit0) <= pos) ++l;
+        const int local = static_cast<int>(pos) - p.L[l].unit0;
+        s.l = l;
+        s.rt = local / p.L[l].cc128;
+        s.cc = local - s.rt * p.L[l].cc128;
+        s.n = min(static_cast<int>(end - pos), p.L[l].cc128 - s.cc);
+        s.new_layer = l != last_l;
+        last_l = l;
+        pos += static_cast<unsigned>(s.n);
+        return true;
+    }
+};
+__device__ __forceinline__ int block_units(const GroupArgs& p) {
+    int n = 0;
+    for (int k = 0; k < p.n_phases; ++k) {
+        const unsigned U = static_cast<unsigned>(p.phase_units[k]), G = gridDim.x;
+        n += static_cast<int>((U * (blockIdx.x + 1u)) / G - (U * blockIdx.x) / G);
+    }
+    return n;
+}
+
+// A layer of phase k may read its input once every row tile of phase k-1 is finalized (which implies the
+// phases before it).  Called by a whole warp: each lane reads one of the phase's 32 counters, the sum is the
+// number of finished tiles.  Polls with a pause, bounded by the global timer; false when the limit passes.
+__device__ __noinline__ bool wait_phase(const GroupArgs& p, int phase, int tiles, unsigned long long limit_ns) {
+    unsigned long long t0;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    const unsigned* line = p.done + (phase - 1) * 32 + (threadIdx.x & 31);
+    for (;;) {
+        unsigned v;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(line) : "memory");
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if (v >= static_cast<unsigned>(tiles)) return true;
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        if (t - t0 > limit_ns) return false;
+        __nanosleep(200);
+    }
+}
+
+// End of a warp that may finalize tiles (finalizer, correction warps) in a chained launch: the last such warp
+// of the whole launch puts the zeros back into the phase counters -- every tile is finalized by then.
+__device__ __forceinline__ void launch_exit(const GroupArgs& p, int lane) {
+    if (p.done == nullptr) return;
     __syncwarp();
     unsigned old = 0;
-    if (lane == 0)
-        asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], %2;" : "=r"(old) : "l"(p.counters + L.tile0 + rt16), "r"(weight) : "memory");
+    unsigned* finished = p.done + kMaxGroupLayers * 32;
+    if (lane == 0) asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(old) : "l"(finished) : "memory");
     old = __shfl_sync(0xffffffffu, old, 0);
-    return old + weight == static_cast<unsigned>(L.cc128) + 4u;
+    if (old + 1u == gridDim.x * kAuxWarps) {
+        for (int i = lane; i < p.n_phases * 32; i += 32) p.done[i] = 0u;
+        if (lane == 0) *finished = 0u;
+    }
+}
+
+// Activation of column c as the layer sees it before the RMSNorm factor: x, or silu(x) * x_aux with the
+// fp16 roundings of the two separate operations.  L2 loads: another block of this launch may have written x.
+__device__ __forceinline__ float activation_at(const GroupLayer& L, int c) {
+    const float xv = __half2float(__ldcg(L.x + c));
+    if (L.x_op != EPTQ_X_SILU_MUL) return xv;
+    const float s = __half2float(__float2half_rn(xv / (1.f + __expf(-xv))));
+    return __half2float(__float2half_rn(s * __half2float(__ldcg(L.x_aux + c))));
+}
+__device__ __forceinline__ void activations8(const GroupLayer& L, int c, float (&out)[8]) {
+    unpack8(__ldcg(reinterpret_cast<const uint4*>(L.x + c)), out);
+    if (L.x_op == EPTQ_X_SILU_MUL) {
+        float u[8];
+        unpack8(__ldcg(reinterpret_cast<const uint4*>(L.x_aux + c)), u);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const float sv = __half2float(__float2half_rn(out[e] / (1.f + __expf(-out[e]))));
+            out[e] = __half2float(__float2half_rn(sv * u[e]));
+        }
+    }
+}
+// rsqrt(mean(x^2) + eps) of a layer's input, by one warp (for a correction warp that finalizes a tile).
+__device__ __noinline__ float warp_inv_rms(const GroupLayer& L, int lane) {
+    float ss = 0.f;
+    for (int c = lane * 8; c < L.N; c += 256) {
+        float v[8];
+        unpack8(__ldcg(reinterpret_cast<const uint4*>(L.x + c)), v);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss = fmaf(v[e], v[e], ss);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    return rsqrtf(ss / static_cast<float>(L.N) + L.norm_eps);
 }
 
 // Critical blocks of 4 consecutive Q rows, batch 1: 8 lanes per row, two entries per lane and pass (the
 // correction warps run with 64 registers).  Adds sum (O - marker code) * h*x to the tile's accumulators and
-// arrives as one of the tile's four correction quarters.
+// arrives as one of the tile's four correction quarters; finalizes the tile if that completes it.
 template <typename WaitFn>
 __device__ __forceinline__ void stream_correction_unit(const GroupArgs& p, const GroupLayer& L, int qt, int lane,
-                                                       float c0, float c1, float c2, float c3, const float* inv_rms,
-                                                       WaitFn wait_dep) {
+                                                       float c0, float c1, float c2, float c3, float* inv_rms_slot,
+                                                       WaitFn wait_input) {
     const int row = qt * 4 + (lane >> 3);
     const int sub = lane & 7;
     const int rt = qt >> 2;
@@ -229,12 +325,12 @@ __device__ __forceinline__ void stream_correction_unit(const GroupArgs& p, const
                 ov[j] = make_uint4(0, 0, 0, 0);
             }
         }
-        if (first) { wait_dep(); first = false; }
+        if (first) { wait_input(); first = false; }
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
             float o8[8];
             unpack8(ov[j], o8);
-            const float xv = (col[j] >= 0) ? hv[j] * __half2float(__ldg(L.x + col[j])) : 0.f;
+            const float xv = (col[j] >= 0) ? hv[j] * activation_at(L, col[j]) : 0.f;
             acc[0] = fmaf(o8[0] - c0, xv, acc[0]); acc[1] = fmaf(o8[1] - c1, xv, acc[1]);
             acc[2] = fmaf(o8[2] - c2, xv, acc[2]); acc[3] = fmaf(o8[3] - c3, xv, acc[3]);
             acc[4] = fmaf(o8[4] - c0, xv, acc[4]); acc[5] = fmaf(o8[5] - c1, xv, acc[5]);
@@ -252,7 +348,22 @@ __device__ __forceinline__ void stream_correction_unit(const GroupArgs& p, const
         red_add4(dst, acc[0], acc[1], acc[2], acc[3]);
         red_add4(dst + 4, acc[4], acc[5], acc[6], acc[7]);
     }
-    if (tile_arrive(p, L, rt, 1u, lane)) finalize_tile(p, L, rt, lane, load_affine(L, rt, lane), inv_rms);
+    // One correction quarter arrives; a tile is complete at cc128 units + 4 quarters.
+    __syncwarp();
+    unsigned old = 0;
+    if (lane == 0)
+        asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(old) : "l"(p.counters + L.tile0 + rt) : "memory");
+    old = __shfl_sync(0xffffffffu, old, 0);
+    if (old + 1u == static_cast<unsigned>(L.cc128) + 4u) {
+        const float* inv_rms = nullptr;
+        if (L.x_op == EPTQ_X_RMSNORM) {
+            const float r = warp_inv_rms(L, lane);
+            if (lane == 0) *inv_rms_slot = r;
+            __syncwarp();
+            inv_rms = inv_rms_slot;
+        }
+        finalize_tile(p, L, rt, lane, load_affine(L, rt, lane), inv_rms);
+    }
 }
 
 __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __grid_constant__ StreamArgs P) {
@@ -268,10 +379,6 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
     asm volatile("griddepcontrol.launch_dependents;");
     EPTQ_STRACE(0, warp == 0);
 
-    const unsigned W32 = static_cast<unsigned>(p.W), nw32 = static_cast<unsigned>(p.nw);
-    const unsigned u_begin = (blockIdx.x * W32) / nw32, u_end = ((blockIdx.x + 1u) * W32) / nw32;   // W * nw < 2^32
-    const int n_units = static_cast<int>(u_end - u_begin);
-
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
             mbar_init(kFullBar + 8 * s, 1);
@@ -285,12 +392,6 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncthreads();
-
-    // Position of the block's first unit.
-    int l0 = 0;
-    while (l0 + 1 < p.n_layers && static_cast<unsigned>(p.L[l0 + 1].unit0) <= u_begin) ++l0;
-    const int local0 = static_cast<int>(u_begin) - p.L[l0].unit0;
-    const int rt0 = local0 / p.L[l0].cc128, cc0 = local0 - rt0 * p.L[l0].cc128;
     float* misc = reinterpret_cast<float*>(smem_raw + (kMisc - kBase));
 
     // Registers: the block starts with 96 per thread (640 threads); the warpgroup of the producer, the
@@ -304,53 +405,50 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
         // ------------------------------------------------------------ producer
         if (warp == kProducerWarp) {
             if (lane == 0) {
-                int l = l0, rt = rt0, cc = cc0, ncc = p.L[l0].cc128, nrt = p.L[l0].rt64;
-                int s = 0;
+                SegmentWalk walk;
+                Segment sg;
+                int s = 0, issued = 0;
                 unsigned ph = 0;
-                for (int i = 0; i < n_units; ++i) {
-                    if (i >= kStages && !mbar_wait(kEmptyBar + 8 * s, ph ^ 1u, P.wait_ns)) {
-                        atomicExch(P.status, EPTQ_ERR_TIMEOUT);
-                        break;
-                    }
-                    mbar_expect_tx(kFullBar + 8 * s, kStageBytes);
-                    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-                                 :: "r"(kRing + s * kStageBytes), "l"(&P.maps[l]), "r"(0), "r"(rt * 64), "r"(cc * 2), "r"(kFullBar + 8 * s)
-                                 : "memory");
-                    if (++cc == ncc) {
-                        cc = 0;
-                        if (++rt == nrt) {
-                            rt = 0;
-                            if (++l < p.n_layers) { ncc = p.L[l].cc128; nrt = p.L[l].rt64; }
+                bool ok = true;
+                while (ok && walk.next(p, sg)) {
+                    for (int j = 0; j < sg.n; ++j) {
+                        if (issued >= kStages && !mbar_wait(kEmptyBar + 8 * s, ph ^ 1u, P.wait_ns)) {
+                            atomicExch(P.status, EPTQ_ERR_TIMEOUT);
+                            ok = false;
+                            break;
                         }
+                        mbar_expect_tx(kFullBar + 8 * s, kStageBytes);
+                        asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                                     :: "r"(kRing + s * kStageBytes), "l"(&P.maps[sg.l]), "r"(0), "r"(sg.rt * 64), "r"((sg.cc + j) * 2),
+                                        "r"(kFullBar + 8 * s)
+                                     : "memory");
+                        ++issued;
+                        if (++s == kStages) { s = 0; ph ^= 1u; }
                     }
-                    if (++s == kStages) { s = 0; ph ^= 1u; }
                 }
             }
             EPTQ_STRACE(7, true);
             return;
         }
 
-        if (p.x_norm) asm volatile("bar.sync 2, %0;" :: "n"((kConsumerWarps + kAuxWarps) * 32) : "memory");
-        const float* inv_rms = p.x_norm ? misc + 40 : nullptr;
-
         // ------------------------------------------------------------ finalizer
-        // One flush per (layer, 64-row tile) the block's range touches, in order: the consumers leave the int32
-        // sums of the tile in a flush buffer; this warp turns them into floats, adds them to the accumulators
-        // in scratch, arrives at the four 16-row tiles and finalizes those it completes.
+        // One flush per segment, in order: the consumers leave the int32 sums of the tile in a flush buffer;
+        // this warp turns them into floats, adds them to the accumulators in scratch, arrives at the four
+        // 16-row tiles with the segment's units as weight and finalizes those it completes.
         if (warp == kFinalizerWarp) {
-            int l = l0, rt = rt0, cc = cc0;
-            int left = n_units;
+            SegmentWalk walk;
+            Segment sg;
             unsigned k = 0;
             bool waited = false;
-            while (left > 0) {
-                const GroupLayer& L = p.L[l];
-                const int seg = min(left, L.cc128 - cc);           // units of this tile in the range
+            while (walk.next(p, sg)) {
+                const GroupLayer& L = p.L[sg.l];
                 const unsigned b = k & 1u;
                 if (!mbar_wait(kRedFull + 8 * b, (k >> 1) & 1u, P.wait_ns)) {
                     if (lane == 0) atomicExch(P.status, EPTQ_ERR_TIMEOUT);
                     break;
                 }
                 const float scale = __uint_as_float(lds32(kMail + 16 * b + 12));
+                if (lane == 0) misc[48] = __uint_as_float(lds32(kMail + 16 * b + 8));       // this layer's RMSNorm factor
                 const unsigned buf = kRed + b * 4096;
                 // This lane: row lane>>1 of each 16-row tile, dimensions 4*(lane&1)..+3.  The buffer stores
                 // dimension d at d ^ 4*((row>>2)&1) ^ digit: the halves of a row swap when bit 2 of the row is
@@ -373,7 +471,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
                 Affine aff[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    const int rt16 = rt * 4 + j;
+                    const int rt16 = sg.rt * 4 + j;
                     if (rt16 < L.row_tiles) {
                         aff[j] = load_affine(L, rt16, lane);
                         float* dst = p.acc + L.acc_off + static_cast<size_t>(rt16) * p.B * 128 + lane * 4;
@@ -386,21 +484,20 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
                 // one round trip for the four arrivals
                 __syncwarp();
                 unsigned old = 0;
-                const unsigned weight = static_cast<unsigned>(seg);
-                if (lane < 4 && rt * 4 + lane < L.row_tiles)
+                const unsigned weight = static_cast<unsigned>(sg.n);
+                if (lane < 4 && sg.rt * 4 + lane < L.row_tiles)
                     asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], %2;"
-                                 : "=r"(old) : "l"(p.counters + L.tile0 + rt * 4 + lane), "r"(weight) : "memory");
+                                 : "=r"(old) : "l"(p.counters + L.tile0 + sg.rt * 4 + lane), "r"(weight) : "memory");
+                const float* inv_rms = L.x_op == EPTQ_X_RMSNORM ? misc + 48 : nullptr;
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const unsigned oj = __shfl_sync(0xffffffffu, old, j);
-                    if (rt * 4 + j < L.row_tiles && oj + weight == static_cast<unsigned>(L.cc128) + 4u)
-                        finalize_tile(p, L, rt * 4 + j, lane, aff[j], inv_rms);
+                    if (sg.rt * 4 + j < L.row_tiles && oj + weight == static_cast<unsigned>(L.cc128) + 4u)
+                        finalize_tile(p, L, sg.rt * 4 + j, lane, aff[j], inv_rms);
                 }
-                left -= seg;
-                cc = 0;
-                if (++rt == L.rt64) { rt = 0; ++l; }
                 ++k;
             }
+            launch_exit(p, lane);
             EPTQ_STRACE(5, true);
             return;
         }
@@ -413,14 +510,24 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
             const float c1 = static_cast<float>(static_cast<signed char>((e511 >> 8) & 0xFF)) * P.unit;
             const float c2 = static_cast<float>(static_cast<signed char>((e511 >> 16) & 0xFF)) * P.unit;
             const float c3 = static_cast<float>(static_cast<signed char>(e511 >> 24)) * P.unit;
-            bool waited = false;
+            bool dep_waited = false;
+            int waited_phase = 0;
+            bool ok = true;
             const int cw = blockIdx.x * kStreamCorrWarps + (warp - kFinalizerWarp - 1);
             int l = 0;
             for (int u = cw; u < p.corr_units; u += p.n_corr_warps) {
                 while (l + 1 < p.n_layers && p.L[l + 1].corr0 <= u) ++l;
-                stream_correction_unit(p, p.L[l], u - p.L[l].corr0, lane, c0, c1, c2, c3, inv_rms,
-                                       [&]() { if (!waited) { asm volatile("griddepcontrol.wait;" ::: "memory"); waited = true; } });
+                const GroupLayer& L = p.L[l];
+                stream_correction_unit(p, L, u - L.corr0, lane, c0, c1, c2, c3, misc + 49 + (warp - kFinalizerWarp), [&]() {
+                    if (!dep_waited) { asm volatile("griddepcontrol.wait;" ::: "memory"); dep_waited = true; }
+                    if (L.phase > waited_phase && ok) {
+                        ok = wait_phase(p, L.phase, L.wait_tiles, P.wait_ns);
+                        waited_phase = L.phase;
+                    }
+                });
             }
+            if (!ok && lane == 0) atomicExch(P.status, EPTQ_ERR_TIMEOUT);
+            launch_exit(p, lane);
             EPTQ_STRACE(6, warp == kFinalizerWarp + 1);
             return;
         }
@@ -450,40 +557,41 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
 
     bool ok = true;
     bool dep_waited = false;
-    float out_scale = 0.f;
+    float out_scale = 0.f, inv_rms_l = 1.f;
 
     // Digit planes (and the fused RMSNorm factor) of layer l.  Four chunks of 8 columns per thread stay in
     // registers between the maximum and the split into digits; longer rows reload the rest.
     auto prepare_layer = [&](int l) {
         const GroupLayer& L = p.L[l];
         if (!dep_waited) { asm volatile("griddepcontrol.wait;" ::: "memory"); dep_waited = true; }
+        if (L.phase > 0) {                                   // input written by the previous phase of this launch
+            if (warp == 0 && ok && !wait_phase(p, L.phase, L.wait_tiles, P.wait_ns) && lane == 0) misc[47] = 1.f;
+            consumer_barrier();
+            if (misc[47] != 0.f) ok = false;
+        }
         constexpr int kStride = kConsumerWarps * 32 * 8;
         float xh[4][8];
         float mx = 0.f, ss = 0.f;
-        {
-            uint4 xr[4], hr[4];
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const int c = tid * 8 + k * kStride;
-                xr[k] = make_uint4(0, 0, 0, 0); hr[k] = make_uint4(0, 0, 0, 0);
-                if (c < L.N) { xr[k] = ldg128(L.x + c); hr[k] = ldg128(L.h + c); }
-            }
+        for (int k = 0; k < 4; ++k) {
+            const int c = tid * 8 + k * kStride;
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                float xv[8], hv[8];
-                unpack8(xr[k], xv);
-                unpack8(hr[k], hv);
+            for (int e = 0; e < 8; ++e) xh[k][e] = 0.f;
+            if (c < L.N) {
+                float hv[8];
+                activations8(L, c, xh[k]);
+                unpack8(ldg128(L.h + c), hv);
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
-                    xh[k][e] = xv[e] * hv[e];
+                    ss = fmaf(xh[k][e], xh[k][e], ss);
+                    xh[k][e] *= hv[e];
                     mx = fmaxf(mx, fabsf(xh[k][e]));
-                    ss = fmaf(xv[e], xv[e], ss);
                 }
             }
         }
         for (int c = tid * 8 + 4 * kStride; c < L.N; c += kStride) {
             float xv[8], hv[8];
-            unpack8(ldg128(L.x + c), xv);
+            activations8(L, c, xv);
             unpack8(ldg128(L.h + c), hv);
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
@@ -505,7 +613,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
         for (int w = 0; w < kConsumerWarps; ++w) { mx = fmaxf(mx, misc[w]); tot += misc[16 + w]; }
         const float S = mx > 0.f ? 32000.f / mx : 1.f;
         out_scale = P.unit / S;
-        if (p.x_norm && tid == 0) misc[40] = rsqrtf(tot / static_cast<float>(L.N) + p.norm_eps);
+        inv_rms_l = L.x_op == EPTQ_X_RMSNORM ? rsqrtf(tot / static_cast<float>(L.N) + L.norm_eps) : 1.f;
         const int n_pad = L.cc128 * 128;
         auto digits = [&](int c, const float (&v)[8]) {
             unsigned lo[2] = {0u, 0u}, hi[2] = {0u, 0u};
@@ -522,21 +630,20 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
             const int c = tid * 8 + k * kStride;
-            if (c < L.N) digits(c, xh[k]);
-            else if (c < n_pad) { sts64(kPlane + c, 0u, 0u); sts64(kPlane + kStreamMaxN + c, 0u, 0u); }
+            if (c < n_pad) digits(c, xh[k]);                 // zeros beyond N
         }
         for (int c = tid * 8 + 4 * kStride; c < n_pad; c += kStride) {
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = 0.f;
             if (c < L.N) {
-                float xv[8], hv[8], v[8];
-                unpack8(ldg128(L.x + c), xv);
+                float hv[8];
+                activations8(L, c, v);
                 unpack8(ldg128(L.h + c), hv);
 #pragma unroll
-                for (int e = 0; e < 8; ++e) v[e] = xv[e] * hv[e];
-                digits(c, v);
-            } else {
-                sts64(kPlane + c, 0u, 0u);
-                sts64(kPlane + kStreamMaxN + c, 0u, 0u);
+                for (int e = 0; e < 8; ++e) v[e] *= hv[e];
             }
+            digits(c, v);
         }
         consumer_barrier();
     };
@@ -548,7 +655,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
         for (int c = 0; c < 4; ++c) acc[r][c] = 0;
     unsigned flush_no = 0;
 
-    // End of this block's part of a 64-row tile: leave the sums in a flush buffer for the finalizer warp.
+    // End of a segment: leave the sums in a flush buffer for the finalizer warp.
     auto flush = [&]() {
         const unsigned b = flush_no & 1u;
         if (flush_no >= 2u && ok) ok = mbar_wait(kRedFree + 8 * b, ((flush_no >> 1) - 1u) & 1u, P.wait_ns);
@@ -564,68 +671,63 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
                 asm volatile("red.shared.add.s32 [%0], %1;" :: "r"(mine + (r * 64 + d) * 4), "r"(acc[r][c]) : "memory");
                 acc[r][c] = 0;
             }
-        if (tid == 0) sts32(kMail + 16 * b + 12, __float_as_uint(out_scale));
+        if (tid == 0) {
+            sts32(kMail + 16 * b + 8, __float_as_uint(inv_rms_l));
+            sts32(kMail + 16 * b + 12, __float_as_uint(out_scale));
+        }
         mbar_arrive(kRedFull + 8 * b);
         ++flush_no;
     };
 
-    int l = l0, rt = rt0, cc = cc0;
-    int ncc = p.L[l0].cc128, nrt = p.L[l0].rt64;
+    if (tid == 0) misc[47] = 0.f;
+    const int n_units = block_units(p);
+    SegmentWalk walk;
+    Segment sg;
     unsigned q[8];
-    EPTQ_STRACE(1, warp == 0);
-    prepare_layer(l);                                        // its barriers also publish the table and the zeroed buffers
-    EPTQ_STRACE(2, warp == 0);
-    if (p.x_norm) asm volatile("bar.arrive 2, %0;" :: "n"((kConsumerWarps + kAuxWarps) * 32) : "memory");
-    ok = mbar_wait(kFullBar, 0u, P.wait_ns);
-    EPTQ_STRACE(3, warp == 0);
-    ldsm4(qm, q[0], q[1], q[2], q[3]);
-    ldsm4(qm + 4096, q[4], q[5], q[6], q[7]);
-    unsigned plane_c = plane + cc * 128;
     unsigned ph = 0;
-    int s = 0;
+    int s = 0, i = 0;
+    bool first = true;
     // One body for all stages (an unrolled ring would repeat the flush and the layer switch six times and no
     // longer fit the instruction cache).
-    for (int i = 0; i < n_units;) {
-        unsigned a[8][4];
-#pragma unroll
-        for (int r = 0; r < 8; ++r) {
-            const unsigned qq = q[r];
-            const unsigned qs = qq >> 16;
-            const unsigned ia = (qq & 0xFF80u) | lane_tab;
-            const unsigned ib = (qs & 0xFF80u) | lane_tab;
-            a[r][0] = lds32(ia);
-            a[r][1] = lds32(bitsel(qq << 7, ia, 0x3F80u));
-            a[r][2] = lds32(ib);
-            a[r][3] = lds32(bitsel(qs << 7, ib, 0x3F80u));
+    while (walk.next(p, sg)) {
+        if (sg.new_layer) prepare_layer(sg.l);               // its barriers also publish the table and the zeroed buffers
+        if (first) {
+            first = false;
+            ok = ok && mbar_wait(kFullBar, 0u, P.wait_ns);
+            ldsm4(qm, q[0], q[1], q[2], q[3]);
+            ldsm4(qm + 4096, q[4], q[5], q[6], q[7]);
         }
-        mbar_arrive(kEmptyBar + 8 * s);                     // every lane: its indices are in registers
-        const unsigned pv = lds16(plane_c);
-        const unsigned b0 = prmt(pv, 0u, sel0), b1 = prmt(pv, 0u, sel1);
-        bool tile_end = false, layer_end = false;
-        plane_c += 128;
-        if (++cc == ncc) {
-            cc = 0;
-            plane_c = plane;
-            tile_end = true;
-            if (++rt == nrt) {
-                rt = 0;
-                layer_end = true;
-                if (++l < p.n_layers) { ncc = p.L[l].cc128; nrt = p.L[l].rt64; }
+        unsigned plane_c = plane + sg.cc * 128;
+        for (int j = 0; j < sg.n; ++j) {
+            unsigned a[8][4];
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                const unsigned qq = q[r];
+                const unsigned qs = qq >> 16;
+                const unsigned ia = (qq & 0xFF80u) | lane_tab;
+                const unsigned ib = (qs & 0xFF80u) | lane_tab;
+                a[r][0] = lds32(ia);
+                a[r][1] = lds32(bitsel(qq << 7, ia, 0x3F80u));
+                a[r][2] = lds32(ib);
+                a[r][3] = lds32(bitsel(qs << 7, ib, 0x3F80u));
             }
-        }
-        ++i;
-        if (++s == kStages) { s = 0; ph ^= 1u; }
-        if (i < n_units) {
-            if (ok) ok = mbar_wait(kFullBar + 8 * s, ph, P.wait_ns);
-            const unsigned stage = qm + s * kStageBytes;
-            ldsm4(stage, q[0], q[1], q[2], q[3]);
-            ldsm4(stage + 4096, q[4], q[5], q[6], q[7]);
-        }
+            mbar_arrive(kEmptyBar + 8 * s);                 // every lane: its indices are in registers
+            const unsigned pv = lds16(plane_c);
+            const unsigned b0 = prmt(pv, 0u, sel0), b1 = prmt(pv, 0u, sel1);
+            plane_c += 128;
+            ++i;
+            if (++s == kStages) { s = 0; ph ^= 1u; }
+            if (i < n_units) {                              // the next unit of the block, whatever segment it is in
+                if (ok) ok = mbar_wait(kFullBar + 8 * s, ph, P.wait_ns);
+                const unsigned stage = qm + s * kStageBytes;
+                ldsm4(stage, q[0], q[1], q[2], q[3]);
+                ldsm4(stage + 4096, q[4], q[5], q[6], q[7]);
+            }
 #pragma unroll
-        for (int r = 0; r < 8; ++r) imma(acc[r], a[r][0], a[r][1], a[r][2], a[r][3], b0, b1);
+            for (int r = 0; r < 8; ++r) imma(acc[r], a[r][0], a[r][1], a[r][2], a[r][3], b0, b1);
+        }
         if (i == n_units) EPTQ_STRACE(4, warp == 0);
-        if (tile_end || i == n_units) flush();
-        if (layer_end && i < n_units) prepare_layer(l);
+        flush();
     }
     if (!ok && lane == 0) atomicExch(P.status, EPTQ_ERR_TIMEOUT);
 }
@@ -704,8 +806,12 @@ bool stream_gemv_supported(const EptqLayer* layers, int n, int B) {
     return units * 1024 < (1LL << 32);                     // owner arithmetic in 32 bits (blocks <= 1024)
 }
 
-int launch_gemv_stream(const EptqLayer* layers, int n, const EptqFusion* fusions, const uint16_t* const* xs,
-                       uint16_t* const* ys, int B, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+// `phases` (or null: one phase): phase of each layer, non-decreasing from 0.  Layers of phase k+1 may read
+// what phase k wrote (the kernel waits for the tiles of all earlier phases before it reads their inputs); with
+// more than one phase the launch is cooperative, so that every block is resident while others wait for it.
+int launch_gemv_stream(const EptqLayer* layers, int n, const EptqFusion* fusions, const int* phases,
+                       const uint16_t* const* xs, uint16_t* const* ys, int B, void* workspace, size_t workspace_bytes,
+                       cudaStream_t stream) {
     if (!stream_gemv_supported(layers, n, B)) return EPTQ_ERR_UNSUPPORTED;
     if (workspace == nullptr || workspace_bytes < kPartialOffset) return EPTQ_ERR_WORKSPACE;
     const int n_sms = stream_sm_count();
@@ -717,10 +823,17 @@ int launch_gemv_stream(const EptqLayer* layers, int n, const EptqFusion* fusions
     std::lock_guard<std::mutex> lock(args_mutex);
     StreamArgs& a = args;
     {
-        const int st = fill_group_args(a.g, layers, n, fusions, xs, ys, B, workspace);
+        const int st = fill_group_args(a.g, layers, n, fusions, xs, ys, B, workspace, phases);
         if (st != EPTQ_OK) return st;
     }
     for (int i = 0; i < n; ++i) if (!aligned16(xs[i])) return EPTQ_ERR_ALIGN;
+    const bool chained = a.g.n_phases > 1;
+    if (chained) {
+        // phase counters: the last 8 KB below the partial-sum region (the accumulators end far below it)
+        if (static_cast<size_t>(a.g.total_tiles) * B * 128 * sizeof(float) > kPartialOffset - kCounterBytes - 8192)
+            return EPTQ_ERR_UNSUPPORTED;
+        a.g.done = reinterpret_cast<unsigned*>(reinterpret_cast<char*>(workspace) + kPartialOffset - 8192);
+    }
     long long units = 0;
     int corr_units = 0;
     for (int i = 0; i < n; ++i) {
@@ -736,7 +849,9 @@ int launch_gemv_stream(const EptqLayer* layers, int n, const EptqFusion* fusions
         }
         a.maps[i] = it->second;
     }
-    const int blocks = units < n_sms ? static_cast<int>(units) : n_sms;
+    // Every phase is split over all blocks; a phase with fewer units than blocks leaves some without work in it.
+    const int blocks = chained ? n_sms : (units < n_sms ? static_cast<int>(units) : n_sms);
+    if (!chained) a.g.phase_units[0] = static_cast<int>(units);
     a.g.W = units;
     a.g.nw = blocks;
     a.g.corr_units = corr_units;
@@ -760,8 +875,13 @@ int launch_gemv_stream(const EptqLayer* layers, int n, const EptqFusion* fusions
     cfg.dynamicSmemBytes = kStreamSmemBytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    if (chained) {
+        attr[0].id = cudaLaunchAttributeCooperative;
+        attr[0].val.cooperative = 1;
+    } else {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+    }
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     const cudaError_t err = cudaLaunchKernelEx(&cfg, gemv_stream_kernel, a);

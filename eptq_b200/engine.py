@@ -132,6 +132,8 @@ class LlamaDecodeEngine:
         B, T = ids.shape
         hd, nh, nkv = self.head_dim, self.n_heads, self.n_kv_heads
         if T == 1 and B <= 2 and hd == 128 and (self.tp_group is None or self.comm is not None) and self._fusable():
+            if B == 1 and self.tp_group is None and self._chainable():
+                return self._forward_chained_decode(ids, positions)
             return self._forward_fused_decode(ids, positions)
         x = F.embedding(ids, self.embed).reshape(B * T, -1)                        # fresh tensor, updated in place
         fused_attention = T <= 8 and hd in (64, 128)
@@ -230,6 +232,65 @@ class LlamaDecodeEngine:
                 self.comm.all_reduce_(linear_forward_group(P["down"], [act], [L.down.out_features])[0], residual=x)
         hn = glue.add_rmsnorm(x, self.final_norm, self.eps)
         return F.linear(hn, self.lm_head).reshape(B, 1, -1)
+
+    # ---- one token, two launches per decoder layer ----------------------------------------------
+    def _chainable(self) -> bool:
+        """Batch-1 decode on one GPU with layers the streaming kernel takes (E8-D4 on the lattice, in_features a
+        multiple of 64): attention, then ONE chained launch for o -> gate/up -> down -> the next layer's q/k/v."""
+        if getattr(self, "_chain_ok", None) is None:
+            ok = self._fusable()
+            if ok:
+                for P in self._fused:
+                    for d in P["qkv"] + P["o"] + P["gate_up"] + P["down"]:
+                        ok = ok and bool(d.table8) and d.table8_scale > 0 and d.N % 64 == 0 and d.N <= 27648
+            self._chain_ok = bool(ok)
+        return self._chain_ok
+
+    def _forward_chained_decode(self, ids: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
+        """q/k/v of the first layer, then per layer: attention and one chained launch -- o (+ residual), gate/up
+        (RMSNorm folded in), down on silu(gate)*up (+ residual), q/k/v of the next layer (RMSNorm folded in,
+        rotary embedding, cache append)."""
+        from . import _lib
+        from .kernels import glue, linear_forward_chain, linear_forward_group
+        hd, nh = self.head_dim, self.n_heads
+        x = F.embedding(ids, self.embed).reshape(1, -1).contiguous()                # residual stream, updated in place
+        pos_ptr, freq_ptr = positions.data_ptr(), self.inv_freq.data_ptr()
+        inter = self.layers[0].gate.out_features
+        gate = torch.empty((1, inter), dtype=torch.float16, device=x.device)
+        up = torch.empty_like(gate)
+        qs = [torch.empty((1, nh * hd), dtype=torch.float16, device=x.device) for _ in range(2)]
+
+        def fus(x_op=_lib.X_PLAIN, y_op=_lib.Y_STORE, residual=None, x_aux=None):
+            f = _lib.EptqFusion()
+            f.x_op, f.y_op, f.norm_eps, f.rope_scaling, f.max_len = x_op, y_op, self.eps, self.rope_scaling, self.max_len
+            f.residual = None if residual is None else residual.data_ptr()
+            f.x_aux = None if x_aux is None else x_aux.data_ptr()
+            f.position, f.inv_freq = pos_ptr, freq_ptr
+            return f
+        qkv_f = [fus(_lib.X_RMSNORM, _lib.Y_ROPE), fus(_lib.X_RMSNORM, _lib.Y_ROPE_TO_CACHE),
+                 fus(_lib.X_RMSNORM, _lib.Y_TO_CACHE)]
+        mlp_f = [fus(y_op=_lib.Y_ADD_RESIDUAL, residual=x), fus(_lib.X_RMSNORM), fus(_lib.X_RMSNORM),
+                 fus(_lib.X_SILU_MUL, _lib.Y_ADD_RESIDUAL, residual=x, x_aux=up)]
+        n_layers = len(self.layers)
+        linear_forward_group(self._fused[0]["qkv"], [x, x, x], [0, 0, 0], fusions=qkv_f,
+                             ys=[qs[0], self.k_cache[0], self.v_cache[0]])
+        for li, P in enumerate(self._fused):
+            q = qs[li & 1]
+            att = glue.decode_attention(q, self.k_cache[li], self.v_cache[li], positions, 1)
+            descs = P["o"] + P["gate_up"] + P["down"]
+            phases = [0, 1, 1, 2]
+            xs = [att, x, x, gate]
+            ys = [x, gate, up, x]
+            fz = list(mlp_f)
+            if li + 1 < n_layers:
+                descs = descs + self._fused[li + 1]["qkv"]
+                phases += [3, 3, 3]
+                xs += [x, x, x]
+                ys += [qs[(li + 1) & 1], self.k_cache[li + 1], self.v_cache[li + 1]]
+                fz += qkv_f
+            linear_forward_chain(descs, phases, xs, [0] * len(descs), fz, ys=ys)
+        hn = glue.add_rmsnorm(x, self.final_norm, self.eps)
+        return F.linear(hn, self.lm_head).reshape(1, 1, -1)
 
     def forward_reference(self, ids: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
         """The same step in plain PyTorch ops, on any device and dtype: what `forward` is tested against,

@@ -22,8 +22,8 @@ import torch
 
 from .. import _lib
 
-__all__ = ["e8_forward", "e8d4_forward", "linear_forward", "linear_forward_group", "dequantize_layer",
-           "workspace_for"]
+__all__ = ["e8_forward", "e8d4_forward", "linear_forward", "linear_forward_group", "linear_forward_chain",
+           "dequantize_layer", "workspace_for", "workspace_status"]
 
 _workspaces: Dict[Tuple[int, int], torch.Tensor] = {}
 
@@ -306,6 +306,43 @@ def linear_forward_group(descs, xs, out_features, workspace: Optional[torch.Tens
             st = lib.eptq_linear_forward_group_fused(arr, n, fz, xp, yp, B, ws.data_ptr(), ws.numel(), _stream(dev))
     _lib.check(st, "eptq group forward")
     return ys
+
+
+def linear_forward_chain(descs, phases, xs, out_features, fusions, ys=None, workspace: Optional[torch.Tensor] = None):
+    """Layers in dependent phases in ONE launch (eptq_linear_forward_chain): a layer of phase k+1 may read
+    (as x, x_aux or residual) what a layer of phase k wrote.  Arguments as linear_forward_group plus
+    `phases`, the phase of each layer (non-decreasing from 0).  Batch 1, E8-D4 layers of the streaming
+    kernel; raises otherwise."""
+    lib = _lib.load()
+    n = len(descs)
+    B = xs[0].shape[0]
+    dev = xs[0].device
+    ys = list(ys) if ys is not None else [None] * n
+    for i, o in enumerate(out_features):
+        if ys[i] is None:
+            ys[i] = torch.empty((B, o), dtype=torch.float16, device=dev)
+    arr = (_lib.EptqLayer * n)(*descs)
+    ws = workspace if workspace is not None else workspace_for(dev, 1 << 20)
+    xp = (C.c_void_p * n)(*[x.data_ptr() for x in xs])
+    yp = (C.c_void_p * n)(*[y.data_ptr() for y in ys])
+    ph = (C.c_int * n)(*[int(v) for v in phases])
+    fz = (_lib.EptqFusion * n)(*fusions)
+    with torch.cuda.device(dev):
+        st = lib.eptq_linear_forward_chain(arr, n, fz, ph, xp, yp, B, ws.data_ptr(), ws.numel(), _stream(dev))
+    _lib.check(st, "eptq chained forward")
+    return ys
+
+
+def workspace_status(workspace: Optional[torch.Tensor] = None, device=None) -> int:
+    """Read and clear the status word of a scratch buffer (eptq_workspace_status): 0, or the code a kernel
+    left when one of its bounded waits ran out.  Synchronises the current stream."""
+    lib = _lib.load()
+    dev = workspace.device if workspace is not None else torch.device(device if device is not None else "cuda")
+    ws = workspace if workspace is not None else workspace_for(dev, 1 << 20)
+    out = C.c_int(0)
+    with torch.cuda.device(dev):
+        _lib.check(lib.eptq_workspace_status(ws.data_ptr(), C.addressof(out), _stream(dev)), "eptq workspace status")
+    return int(out.value)
 
 
 def dequantize_layer(Q: torch.Tensor, table32: torch.Tensor, g: torch.Tensor, h: torch.Tensor,

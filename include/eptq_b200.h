@@ -209,7 +209,7 @@ int eptq_linear_forward_group(const EptqLayer* layers, int n_layers,
  *         EPTQ_Y_TO_CACHE      no rotation, stored into a value cache likewise.
  *   The three head-wise ops need 8M a multiple of 128 (M % 16 == 0).  Fusions need B <= 2.
  */
-enum { EPTQ_X_PLAIN = 0, EPTQ_X_RMSNORM = 2 };
+enum { EPTQ_X_PLAIN = 0, EPTQ_X_RMSNORM = 2, EPTQ_X_SILU_MUL = 3 };
 enum { EPTQ_Y_STORE = 0, EPTQ_Y_ADD_RESIDUAL = 1, EPTQ_Y_ROPE = 2, EPTQ_Y_ROPE_TO_CACHE = 3, EPTQ_Y_TO_CACHE = 4 };
 
 typedef struct EptqFusion {
@@ -222,11 +222,42 @@ typedef struct EptqFusion {
     const uint16_t* residual;   /* fp16 (B, 8M) */
     const int64_t* position;    /* device scalar */
     const float* inv_freq;      /* device, 64 entries */
+    const uint16_t* x_aux;      /* EPTQ_X_SILU_MUL: second input, fp16 (B, N) */
 } EptqFusion;
 
 int eptq_linear_forward_group_fused(const EptqLayer* layers, int n_layers, const EptqFusion* fusions,
                                     const uint16_t* const* xs, uint16_t* const* ys, int B,
                                     void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Chained launch (no counterpart in the reference, which launches one kernel per
+ * layer): like eptq_linear_forward_group_fused, but the layers are ordered in
+ * phases (phases[i] non-decreasing from 0, steps of at most 1) and a layer of
+ * phase k+1 may take as x (or x_aux, or residual) what a layer of phase k wrote --
+ * o_proj, then gate/up on the updated residual stream, then down on
+ * silu(gate)*up, in ONE launch.  Inside the launch every phase is spread over
+ * all SMs and the weight stream of the next phase is prefetched while the last
+ * tiles of the previous one are finished.
+ *   x_op EPTQ_X_SILU_MUL: the layer sees silu(x) * x_aux, both (B, N) fp16,
+ *   with the fp16 roundings of two separate operations (only in chained launches).
+ *   EPTQ_X_RMSNORM may differ from layer to layer here.
+ * Requirements: the streaming kernel's (E8-D4 with table8, batch 1, N % 64 == 0,
+ * no group scales).  The launch is cooperative: it needs all SMs of the device
+ * and fails with EPTQ_ERR_LAUNCH if they cannot all hold a block.  Every wait
+ * inside is bounded (2 s); eptq_workspace_status tells whether one ran out.
+ */
+int eptq_linear_forward_chain(const EptqLayer* layers, int n_layers, const EptqFusion* fusions,
+                              const int* phases, const uint16_t* const* xs, uint16_t* const* ys,
+                              int B, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * The last counter word of a scratch buffer is its status word: a kernel whose
+ * bounded device-side wait ran out (the chained and streaming GEMV, the prefill
+ * GEMM) leaves EPTQ_ERR_TIMEOUT there and its output is not valid.  This copies
+ * the word to *host_out on `stream`, waits for that copy (it synchronises the
+ * stream: do not call it during capture) and clears the word.
+ */
+int eptq_workspace_status(void* workspace, int* host_out, void* stream);
 
 /*
  * Reconstruct the fp16 weight (8M, N) row-major, bit-for-bit what the
