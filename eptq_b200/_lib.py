@@ -53,6 +53,7 @@ class EptqLayer(C.Structure):
         ("O_vals", _vp), ("O_col", _vp), ("O_row_ptr", _vp), ("bias", _vp), ("S_group", _vp),
         ("table8", _vp), ("table8_scale", C.c_float), ("h_absmax", C.c_float),
         ("table_packed", _vp), ("table_packed_scale", C.c_float), ("reserved", C.c_int32),
+        ("crit_ptr", _vp), ("crit_pos", _vp), ("crit_O", _vp),
     ]
 
 

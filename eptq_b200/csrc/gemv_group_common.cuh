@@ -36,10 +36,14 @@ struct GroupLayer {
     int cc128;              // ceil(N / 128)
     // chained launches (gemv_stream.cu): layers of a later phase read what earlier phases wrote
     int phase;
-    int wait_tiles;         // row tiles of the previous phase: x may be read once that many of them are finalized
+    int wait_tiles;         // tiles of the previous phase: x may be read once that many of them are finalized
+                            // (16-row tiles, or 64-row tiles when the launch patches critical blocks from unit lists)
     int x_op;               // EPTQ_X_PLAIN, EPTQ_X_RMSNORM or EPTQ_X_SILU_MUL
     float norm_eps;
     const __half* x_aux;    // EPTQ_X_SILU_MUL: x = silu(x) * x_aux
+    const int* crit_ptr;    // critical blocks per 64 x 128 unit (EptqLayer.crit_*), or null
+    const unsigned* crit_pos;
+    const __half* crit_O;
     // fused epilogue (EptqFusion): what the finalizing warp does with a finished row tile
     const __half* residual;     // EPTQ_Y_ADD_RESIDUAL
     const long long* position;  // rotary angle / cache row (device scalar)
@@ -275,7 +279,7 @@ __device__ __forceinline__ void correction_unit(const GroupArgs& p, const GroupL
 // differs between the kernels: W, nw, corr_units, n_corr_warps).  Checks the fusion arguments.
 inline int fill_group_args(GroupArgs& a, const EptqLayer* layers, int n, const EptqFusion* fusions,
                            const uint16_t* const* xs, uint16_t* const* ys, int B, void* workspace,
-                           const int* phases = nullptr) {
+                           const int* phases = nullptr, bool tiles64 = false) {
     const bool e8 = layers[0].quantizer == EPTQ_E8;
     a.table16 = reinterpret_cast<const uint2*>(layers[0].table16);
     a.packed = e8 ? layers[0].table_packed : nullptr;
@@ -343,7 +347,8 @@ inline int fill_group_args(GroupArgs& a, const EptqLayer* layers, int n, const E
             if (phases[i] != phases[i - 1]) {
                 a.phase_unit0[G.phase] = unit0;
                 int prev_tiles = 0;                          // row tiles of the previous phase
-                for (int j = i - 1; j >= 0 && phases[j] == phases[i - 1]; --j) prev_tiles += a.L[j].row_tiles;
+                for (int j = i - 1; j >= 0 && phases[j] == phases[i - 1]; --j)
+                    prev_tiles += tiles64 ? a.L[j].rt64 : a.L[j].row_tiles;
                 G.wait_tiles = prev_tiles;
             } else {
                 G.wait_tiles = a.L[i - 1].wait_tiles;
@@ -351,6 +356,9 @@ inline int fill_group_args(GroupArgs& a, const EptqLayer* layers, int n, const E
         }
         a.phase_units[G.phase] += G.rt64 * G.cc128;
         unit0 += G.rt64 * G.cc128;
+        G.crit_ptr = L.crit_ptr;
+        G.crit_pos = L.crit_pos;
+        G.crit_O = reinterpret_cast<const __half*>(L.crit_O);
         G.x_op = fusions != nullptr ? fusions[i].x_op : EPTQ_X_PLAIN;
         G.norm_eps = fusions != nullptr ? fusions[i].norm_eps : 0.f;
         G.x_aux = fusions != nullptr ? reinterpret_cast<const __half*>(fusions[i].x_aux) : nullptr;

@@ -53,7 +53,7 @@ constexpr int kAuxWarps = 1 + kStreamCorrWarps;                     // finalizer
 constexpr int kStreamThreads = (kConsumerWarps + 1 + kAuxWarps) * 32;   // five warpgroups
 constexpr int kStages = 6;
 constexpr int kStageBytes = 64 * 128 * 2;
-constexpr int kStreamMaxN = 27648;                                  // columns the digit planes hold
+constexpr int kStreamMaxN = 25600;                                  // columns the digit planes hold
 // Shared memory by absolute shared-window address (dynamic shared memory starts at 0x400 on sm_100; the
 // kernel checks it).  The table sits on a 64 KB boundary so that a lookup address is (bits of q) | constant.
 constexpr unsigned kBase = 0x400u;
@@ -61,10 +61,12 @@ constexpr unsigned kFullBar = 0x400u;                               // kStages x
 constexpr unsigned kEmptyBar = 0x440u;
 constexpr unsigned kRedFull = 0x480u;                               // 2 x 8: a flush buffer holds a finished tile
 constexpr unsigned kRedFree = 0x490u;                               // 2 x 8: the finalizer has emptied it
-constexpr unsigned kMail = 0x4A0u;                                  // 2 x {layer, row tile, units, scale}
-constexpr unsigned kMisc = 0x500u;                                  // 64 floats of reductions and results
+constexpr unsigned kMail = 0x4A0u;                                  // 2 x {-, -, RMSNorm factor, scale}
+constexpr unsigned kPrep = 0x4C0u;                                  // 8: the digit planes of a layer are ready
+constexpr unsigned kMisc = 0x500u;                                  // 128 floats of reductions and results
 constexpr unsigned kRed = 0x800u;                                   // 2 x [digit][64 rows][8] int32
-constexpr unsigned kPlane = 0x2800u;                                // low digits, then high digits
+constexpr unsigned kCorr = 0x2800u;                                 // 2 x [64 rows][8] float: critical-block corrections
+constexpr unsigned kPlane = 0x3800u;                                // low digits, then high digits
 constexpr unsigned kTable = 0x10000u;
 constexpr unsigned kRing = 0x20000u;
 constexpr unsigned kSmemEnd = kRing + kStages * kStageBytes;        // 0x38000
@@ -76,6 +78,7 @@ struct StreamArgs {
     alignas(64) CUtensorMap maps[kMaxGroupLayers];
     float unit;                                   // table value = integer coordinate * unit
     float inv_unit;
+    int use_lists;                                // every layer brings its critical blocks as unit lists
     int* status;
     unsigned long long wait_ns;                   // limit of one mbarrier wait
 };
@@ -366,6 +369,91 @@ __device__ __forceinline__ void stream_correction_unit(const GroupArgs& p, const
     }
 }
 
+// A finished 64-row tile of a launch that patches critical blocks from unit lists (batch 1): the four 16-row
+// tiles at once, every load issued before the first use.  Same arithmetic as finalize_tile.
+__device__ __forceinline__ void finalize_tile64(const GroupArgs& p, const GroupLayer& L, int rt64, int lane,
+                                                const float* inv_rms) {
+    if (lane == 0) p.counters[L.tile0 + rt64 * 4] = 0u;
+    __syncwarp();      // lane 0's acquire (its ticket), then the warp barrier: every lane sees the other warps' adds
+    const bool rope = L.y_op == EPTQ_Y_ROPE || L.y_op == EPTQ_Y_ROPE_TO_CACHE;
+    const bool to_cache = L.y_op == EPTQ_Y_ROPE_TO_CACHE || L.y_op == EPTQ_Y_TO_CACHE;
+    float4 s[4];
+    uint2 gq[4], bq[4], rq[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int rt16 = rt64 * 4 + j;
+        const int row = rt16 * 16 + (lane >> 1);
+        const int o = row * 8 + (lane & 1) * 4;
+        s[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        gq[j] = make_uint2(0u, 0u); bq[j] = make_uint2(0u, 0u); rq[j] = make_uint2(0u, 0u);
+        if (rt16 < L.row_tiles) {
+            float* a = p.acc + L.acc_off + static_cast<size_t>(rt16) * 128 + lane * 4;
+            s[j] = __ldcg(reinterpret_cast<const float4*>(a));
+            __stcg(reinterpret_cast<float4*>(a), make_float4(0.f, 0.f, 0.f, 0.f));
+            if (row < L.M) {
+                gq[j] = __ldg(reinterpret_cast<const uint2*>(L.g + o));
+                if (L.bias != nullptr) bq[j] = __ldg(reinterpret_cast<const uint2*>(L.bias + o));
+                if (L.y_op == EPTQ_Y_ADD_RESIDUAL) rq[j] = __ldcg(reinterpret_cast<const uint2*>(L.residual + o));
+            }
+        }
+    }
+    long long pos = 0;
+    float cs[4] = {1.f, 1.f, 1.f, 1.f}, sn[4] = {0.f, 0.f, 0.f, 0.f};
+    if (rope || to_cache) pos = *L.position;
+    if (rope) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            float sv, cv;
+            sincosf(static_cast<float>(pos) * L.inv_freq[(lane & 15) * 4 + c], &sv, &cv);
+            cs[c] = __half2float(__float2half_rn(cv * L.rope_scaling));
+            sn[c] = __half2float(__float2half_rn(sv * L.rope_scaling));
+            if (lane < 16) sn[c] = -sn[c];
+        }
+    }
+    const float r = inv_rms != nullptr ? inv_rms[0] : 1.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int rt16 = rt64 * 4 + j;
+        if (rt16 >= L.row_tiles) continue;                 // warp-uniform
+        const int row = rt16 * 16 + (lane >> 1);
+        const int o = row * 8 + (lane & 1) * 4;
+        const float2 g01 = __half22float2(*reinterpret_cast<const __half2*>(&gq[j].x));
+        const float2 g23 = __half22float2(*reinterpret_cast<const __half2*>(&gq[j].y));
+        const float2 b01 = __half22float2(*reinterpret_cast<const __half2*>(&bq[j].x));
+        const float2 b23 = __half22float2(*reinterpret_cast<const __half2*>(&bq[j].y));
+        __half2 o01 = __floats2half2_rn(fmaf(s[j].x * r, g01.x, b01.x), fmaf(s[j].y * r, g01.y, b01.y));
+        __half2 o23 = __floats2half2_rn(fmaf(s[j].z * r, g23.x, b23.x), fmaf(s[j].w * r, g23.y, b23.y));
+        if (rope) {                                        // every row of the tile exists (checked on the host)
+            const float2 v01 = __half22float2(o01), v23 = __half22float2(o23);
+            const float v[4] = {v01.x, v01.y, v23.x, v23.y};
+            float q[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) q[c] = fmaf(v[c], cs[c], __shfl_xor_sync(0xffffffffu, v[c], 16) * sn[c]);
+            o01 = __floats2half2_rn(q[0], q[1]);
+            o23 = __floats2half2_rn(q[2], q[3]);
+        }
+        if (row >= L.M) continue;
+        __half* dst = L.y + o;
+        if (to_cache) {
+            dst = L.y + (static_cast<size_t>(rt16) * L.max_len + pos) * 128 + lane * 4;
+            if (pos < 0 || pos >= L.max_len) continue;
+        }
+        if (L.y_op == EPTQ_Y_ADD_RESIDUAL) {
+            o01 = __hadd2(*reinterpret_cast<const __half2*>(&rq[j].x), o01);
+            o23 = __hadd2(*reinterpret_cast<const __half2*>(&rq[j].y), o23);
+        }
+        uint2 outv;
+        outv.x = *reinterpret_cast<const unsigned*>(&o01);
+        outv.y = *reinterpret_cast<const unsigned*>(&o23);
+        *reinterpret_cast<uint2*>(dst) = outv;
+    }
+    if (p.done != nullptr) {                               // one count per 64-row tile in this mode
+        __syncwarp();
+        if (lane == 0)
+            asm volatile("red.release.gpu.global.add.u32 [%0], 1;" :: "l"(p.done + L.phase * 32 + (((L.tile0 >> 2) + rt64) & 31)) : "memory");
+    }
+}
+
 __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __grid_constant__ StreamArgs P) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     const GroupArgs& p = P.g;
@@ -385,9 +473,10 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
             mbar_init(kEmptyBar + 8 * s, kConsumerWarps * 32);
         }
         for (int b = 0; b < 2; ++b) {
-            mbar_init(kRedFull + 8 * b, kConsumerWarps * 32);
+            mbar_init(kRedFull + 8 * b, kConsumerWarps * 32 + (P.use_lists ? kStreamCorrWarps * 32 : 0));
             mbar_init(kRedFree + 8 * b, 32);
         }
+        mbar_init(kPrep, kConsumerWarps * 32);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -454,46 +543,62 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
                 // dimension d at d ^ 4*((row>>2)&1) ^ digit: the halves of a row swap when bit 2 of the row is
                 // set, and the high-digit words are pairwise exchanged.
                 uint4 lo[4], hi[4];
+                float4 cr[4];
                 const unsigned my = static_cast<unsigned>((lane * 4) ^ (((lane >> 3) & 1) << 2));
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     lo[j] = lds128(buf + (j * 128 + my) * 4);
                     const uint4 hsw = lds128(buf + 2048 + (j * 128 + my) * 4);
                     hi[j] = make_uint4(hsw.y, hsw.x, hsw.w, hsw.z);
+                    cr[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (P.use_lists) {
+                        const uint4 c = lds128(kCorr + b * 2048 + (j * 128 + lane * 4) * 4);
+                        cr[j] = make_float4(__uint_as_float(c.x), __uint_as_float(c.y), __uint_as_float(c.z), __uint_as_float(c.w));
+                    }
                 }
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     sts128(buf + (j * 128 + lane * 4) * 4, 0u, 0u, 0u, 0u);
                     sts128(buf + 2048 + (j * 128 + lane * 4) * 4, 0u, 0u, 0u, 0u);
+                    if (P.use_lists) sts128(kCorr + b * 2048 + (j * 128 + lane * 4) * 4, 0u, 0u, 0u, 0u);
                 }
                 mbar_arrive(kRedFree + 8 * b);
                 if (!waited) { asm volatile("griddepcontrol.wait;" ::: "memory"); waited = true; }
-                Affine aff[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const int rt16 = sg.rt * 4 + j;
                     if (rt16 < L.row_tiles) {
-                        aff[j] = load_affine(L, rt16, lane);
                         float* dst = p.acc + L.acc_off + static_cast<size_t>(rt16) * p.B * 128 + lane * 4;
-                        red_add4(dst, fmaf(256.f, static_cast<float>(static_cast<int>(hi[j].x)), static_cast<float>(static_cast<int>(lo[j].x))) * scale,
-                                 fmaf(256.f, static_cast<float>(static_cast<int>(hi[j].y)), static_cast<float>(static_cast<int>(lo[j].y))) * scale,
-                                 fmaf(256.f, static_cast<float>(static_cast<int>(hi[j].z)), static_cast<float>(static_cast<int>(lo[j].z))) * scale,
-                                 fmaf(256.f, static_cast<float>(static_cast<int>(hi[j].w)), static_cast<float>(static_cast<int>(lo[j].w))) * scale);
+                        red_add4(dst, (fmaf(256.f, static_cast<float>(static_cast<int>(hi[j].x)), static_cast<float>(static_cast<int>(lo[j].x))) + cr[j].x) * scale,
+                                 (fmaf(256.f, static_cast<float>(static_cast<int>(hi[j].y)), static_cast<float>(static_cast<int>(lo[j].y))) + cr[j].y) * scale,
+                                 (fmaf(256.f, static_cast<float>(static_cast<int>(hi[j].z)), static_cast<float>(static_cast<int>(lo[j].z))) + cr[j].z) * scale,
+                                 (fmaf(256.f, static_cast<float>(static_cast<int>(hi[j].w)), static_cast<float>(static_cast<int>(lo[j].w))) + cr[j].w) * scale);
                     }
                 }
-                // one round trip for the four arrivals
-                __syncwarp();
-                unsigned old = 0;
                 const unsigned weight = static_cast<unsigned>(sg.n);
-                if (lane < 4 && sg.rt * 4 + lane < L.row_tiles)
-                    asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], %2;"
-                                 : "=r"(old) : "l"(p.counters + L.tile0 + sg.rt * 4 + lane), "r"(weight) : "memory");
                 const float* inv_rms = L.x_op == EPTQ_X_RMSNORM ? misc + 48 : nullptr;
+                __syncwarp();
+                if (P.use_lists) {
+                    // one arrival for the 64-row tile: complete when all cc128 units of it have arrived
+                    unsigned old = 0;
+                    if (lane == 0)
+                        asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], %2;"
+                                     : "=r"(old) : "l"(p.counters + L.tile0 + sg.rt * 4), "r"(weight) : "memory");
+                    old = __shfl_sync(0xffffffffu, old, 0);
+                    if (old + weight == static_cast<unsigned>(L.cc128)) finalize_tile64(p, L, sg.rt, lane, inv_rms);
+                } else {
+                    // one round trip for the four arrivals; with the CSR corrections a 16-row tile is complete at
+                    // cc128 units + 4 correction quarters
+                    unsigned old = 0;
+                    if (lane < 4 && sg.rt * 4 + lane < L.row_tiles)
+                        asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], %2;"
+                                     : "=r"(old) : "l"(p.counters + L.tile0 + sg.rt * 4 + lane), "r"(weight) : "memory");
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const unsigned oj = __shfl_sync(0xffffffffu, old, j);
-                    if (sg.rt * 4 + j < L.row_tiles && oj + weight == static_cast<unsigned>(L.cc128) + 4u)
-                        finalize_tile(p, L, sg.rt * 4 + j, lane, aff[j], inv_rms);
+                    for (int j = 0; j < 4; ++j) {
+                        const unsigned oj = __shfl_sync(0xffffffffu, old, j);
+                        if (sg.rt * 4 + j < L.row_tiles && oj + weight == static_cast<unsigned>(L.cc128) + 4u)
+                            finalize_tile(p, L, sg.rt * 4 + j, lane, load_affine(L, sg.rt * 4 + j, lane), inv_rms);
+                    }
                 }
                 ++k;
             }
@@ -503,13 +608,66 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
         }
 
         // ------------------------------------------------------------ correction warps
+        // What the main loop adds for a marker: entry (class 3, code 127) in both halves.
+        const unsigned e511 = pack_coords(__ldg(p.table16 + 511), P.inv_unit);
+        const float c0 = static_cast<float>(static_cast<signed char>(e511 & 0xFF)) * P.unit;
+        const float c1 = static_cast<float>(static_cast<signed char>((e511 >> 8) & 0xFF)) * P.unit;
+        const float c2 = static_cast<float>(static_cast<signed char>((e511 >> 16) & 0xFF)) * P.unit;
+        const float c3 = static_cast<float>(static_cast<signed char>(e511 >> 24)) * P.unit;
+        if (P.use_lists) {
+            // Unit lists: the critical blocks of a segment are one contiguous run of (position, 8 values); the two
+            // warps take alternate entries, read the activation digits the consumers prepared and add
+            // (O - marker code) / unit * digits to the segment's correction tile, in step with the flushes.
+            SegmentWalk walk;
+            Segment sg;
+            unsigned k = 0, n_prep = 0;
+            bool ok = true;
+            const int me = (warp - kFinalizerWarp - 1) * 32 + lane;            // 0..63
+            while (walk.next(p, sg)) {
+                const GroupLayer& L = p.L[sg.l];
+                const int u0 = sg.rt * L.cc128 + sg.cc;
+                const int e0 = __ldg(L.crit_ptr + u0), e1 = __ldg(L.crit_ptr + u0 + sg.n);
+                // first entries of this lane: loaded before any wait
+                unsigned pos[2];
+                uint4 ov[2];
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const int e = e0 + me + 64 * j;
+                    pos[j] = 0u; ov[j] = make_uint4(0, 0, 0, 0);
+                    if (e < e1) { pos[j] = __ldg(L.crit_pos + e); ov[j] = ldg128(L.crit_O + static_cast<size_t>(e) * 8); }
+                }
+                if (sg.new_layer) {
+                    if (ok) ok = mbar_wait(kPrep, n_prep & 1u, P.wait_ns);
+                    ++n_prep;
+                }
+                const unsigned b = k & 1u;
+                if (k >= 2u && ok) ok = mbar_wait(kRedFree + 8 * b, ((k >> 1) - 1u) & 1u, P.wait_ns);
+                const unsigned tile = kCorr + b * 2048;
+                auto apply = [&](unsigned ps, const uint4& o) {
+                    const unsigned col = ps & 0xFFFFu, row = ps >> 16;
+                    short dl, dh;
+                    asm volatile("ld.shared.s8 %0, [%1];" : "=h"(dl) : "r"(kPlane + col));
+                    asm volatile("ld.shared.s8 %0, [%1];" : "=h"(dh) : "r"(kPlane + kStreamMaxN + col));
+                    const float f = static_cast<float>(static_cast<int>(dl) + 256 * static_cast<int>(dh)) * P.inv_unit;
+                    float o8[8];
+                    unpack8(o, o8);
+                    const float cm[4] = {c0, c1, c2, c3};
+#pragma unroll
+                    for (int d = 0; d < 8; ++d)
+                        asm volatile("red.shared.add.f32 [%0], %1;" :: "r"(tile + (row * 8 + d) * 4), "f"((o8[d] - cm[d & 3]) * f) : "memory");
+                };
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+                    if (e0 + me + 64 * j < e1) apply(pos[j], ov[j]);
+                for (int e = e0 + me + 128; e < e1; e += 64) apply(__ldg(L.crit_pos + e), ldg128(L.crit_O + static_cast<size_t>(e) * 8));
+                mbar_arrive(kRedFull + 8 * b);
+                ++k;
+            }
+            if (!ok && lane == 0) atomicExch(P.status, EPTQ_ERR_TIMEOUT);
+            launch_exit(p, lane);
+            return;
+        }
         {
-            // What the main loop adds for a marker: entry (class 3, code 127) in both halves.
-            const unsigned e511 = pack_coords(__ldg(p.table16 + 511), P.inv_unit);
-            const float c0 = static_cast<float>(static_cast<signed char>(e511 & 0xFF)) * P.unit;
-            const float c1 = static_cast<float>(static_cast<signed char>((e511 >> 8) & 0xFF)) * P.unit;
-            const float c2 = static_cast<float>(static_cast<signed char>((e511 >> 16) & 0xFF)) * P.unit;
-            const float c3 = static_cast<float>(static_cast<signed char>(e511 >> 24)) * P.unit;
             bool dep_waited = false;
             int waited_phase = 0;
             bool ok = true;
@@ -542,7 +700,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
 #pragma unroll
         for (int c = 0; c < 8; ++c) sts128(kTable + tid * 128 + ((c + tid) & 7) * 16, v, v, v, v);
     }
-    for (int i = tid; i < 2048; i += kConsumerWarps * 32) sts32(kRed + 4 * i, 0u);
+    for (int i = tid; i < 2048 + 1024; i += kConsumerWarps * 32) sts32(kRed + 4 * i, 0u);      // flush and correction tiles
 
     const int g = lane >> 2, t = lane & 3;
     const int chunk64 = warp >> 3, w8 = warp & 7;
@@ -558,35 +716,62 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
     bool ok = true;
     bool dep_waited = false;
     float out_scale = 0.f, inv_rms_l = 1.f;
+    unsigned flush_no = 0, prep_no = 0;
 
     // Digit planes (and the fused RMSNorm factor) of layer l.  Four chunks of 8 columns per thread stay in
-    // registers between the maximum and the split into digits; longer rows reload the rest.
+    // registers between the maximum and the split into digits; longer rows reload the rest.  All loads of the
+    // four chunks are issued before the first use, the column scales (weights) before the wait for the phase.
     auto prepare_layer = [&](int l) {
         const GroupLayer& L = p.L[l];
+        constexpr int kStride = kConsumerWarps * 32 * 8;
+        uint4 hr[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int c = tid * 8 + k * kStride;
+            hr[k] = make_uint4(0, 0, 0, 0);
+            if (c < L.N) hr[k] = ldg128(L.h + c);
+        }
         if (!dep_waited) { asm volatile("griddepcontrol.wait;" ::: "memory"); dep_waited = true; }
+        if (P.use_lists && flush_no > 0u && ok) {            // the correction warps still read the previous layer's planes
+            const unsigned kf = flush_no - 1u;
+            ok = mbar_wait(kRedFull + 8 * (kf & 1u), (kf >> 1) & 1u, P.wait_ns);
+        }
         if (L.phase > 0) {                                   // input written by the previous phase of this launch
             if (warp == 0 && ok && !wait_phase(p, L.phase, L.wait_tiles, P.wait_ns) && lane == 0) misc[47] = 1.f;
             consumer_barrier();
             if (misc[47] != 0.f) ok = false;
         }
-        constexpr int kStride = kConsumerWarps * 32 * 8;
+        uint4 xr[4], ur[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int c = tid * 8 + k * kStride;
+            xr[k] = make_uint4(0, 0, 0, 0); ur[k] = make_uint4(0, 0, 0, 0);
+            if (c < L.N) {
+                xr[k] = __ldcg(reinterpret_cast<const uint4*>(L.x + c));
+                if (L.x_op == EPTQ_X_SILU_MUL) ur[k] = __ldcg(reinterpret_cast<const uint4*>(L.x_aux + c));
+            }
+        }
         float xh[4][8];
         float mx = 0.f, ss = 0.f;
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-            const int c = tid * 8 + k * kStride;
-#pragma unroll
-            for (int e = 0; e < 8; ++e) xh[k][e] = 0.f;
-            if (c < L.N) {
-                float hv[8];
-                activations8(L, c, xh[k]);
-                unpack8(ldg128(L.h + c), hv);
+            float hv[8];
+            unpack8(xr[k], xh[k]);
+            unpack8(hr[k], hv);
+            if (L.x_op == EPTQ_X_SILU_MUL && tid * 8 + k * kStride < L.N) {
+                float u[8];
+                unpack8(ur[k], u);
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
-                    ss = fmaf(xh[k][e], xh[k][e], ss);
-                    xh[k][e] *= hv[e];
-                    mx = fmaxf(mx, fabsf(xh[k][e]));
+                    const float sv = __half2float(__float2half_rn(__fdividef(xh[k][e], 1.f + __expf(-xh[k][e]))));
+                    xh[k][e] = __half2float(__float2half_rn(sv * u[e]));
                 }
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                ss = fmaf(xh[k][e], xh[k][e], ss);
+                xh[k][e] *= hv[e];                           // zero beyond N: both factors were zero-filled
+                mx = fmaxf(mx, fabsf(xh[k][e]));
             }
         }
         for (int c = tid * 8 + 4 * kStride; c < L.N; c += kStride) {
@@ -604,13 +789,16 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
             ss += __shfl_xor_sync(0xffffffffu, ss, o);
         }
-        consumer_barrier();                                 // the previous layer's readers of misc and planes are done
-        if (lane == 0) { misc[warp] = mx; misc[16 + warp] = ss; }
-        consumer_barrier();
+        // misc[0..31] alternate with the layer count, so that this layer's partial results do not meet the
+        // previous layer's readers: one barrier less.
+        float* part = misc + 64 + (prep_no & 1u) * 32;
+        ++prep_no;
+        if (lane == 0) { part[warp] = mx; part[16 + warp] = ss; }
+        consumer_barrier();                                 // also: the previous layer's readers of the planes are done
         float tot = 0.f;
         mx = 0.f;
 #pragma unroll
-        for (int w = 0; w < kConsumerWarps; ++w) { mx = fmaxf(mx, misc[w]); tot += misc[16 + w]; }
+        for (int w = 0; w < kConsumerWarps; ++w) { mx = fmaxf(mx, part[w]); tot += part[16 + w]; }
         const float S = mx > 0.f ? 32000.f / mx : 1.f;
         out_scale = P.unit / S;
         inv_rms_l = L.x_op == EPTQ_X_RMSNORM ? rsqrtf(tot / static_cast<float>(L.N) + L.norm_eps) : 1.f;
@@ -646,6 +834,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
             digits(c, v);
         }
         consumer_barrier();
+        if (P.use_lists) mbar_arrive(kPrep);                 // release: the planes are visible to the correction warps
     };
 
     int acc[8][4];
@@ -653,7 +842,6 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
     for (int r = 0; r < 8; ++r)
 #pragma unroll
         for (int c = 0; c < 4; ++c) acc[r][c] = 0;
-    unsigned flush_no = 0;
 
     // End of a segment: leave the sums in a flush buffer for the finalizer warp.
     auto flush = [&]() {
@@ -822,8 +1010,13 @@ int launch_gemv_stream(const EptqLayer* layers, int n, const EptqFusion* fusions
     static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> maps;
     std::lock_guard<std::mutex> lock(args_mutex);
     StreamArgs& a = args;
+    a.use_lists = 1;
+    for (int i = 0; i < n; ++i)
+        if (layers[i].crit_ptr == nullptr || (layers[i].n_masked != 0 && (layers[i].crit_pos == nullptr || layers[i].crit_O == nullptr)) ||
+            (layers[i].crit_O != nullptr && !aligned16(layers[i].crit_O)))
+            a.use_lists = 0;
     {
-        const int st = fill_group_args(a.g, layers, n, fusions, xs, ys, B, workspace, phases);
+        const int st = fill_group_args(a.g, layers, n, fusions, xs, ys, B, workspace, phases, a.use_lists != 0);
         if (st != EPTQ_OK) return st;
     }
     for (int i = 0; i < n; ++i) if (!aligned16(xs[i])) return EPTQ_ERR_ALIGN;

@@ -216,8 +216,27 @@ def h_absmax(h: torch.Tensor) -> float:
     return v
 
 
+def critical_lists(O_vals: torch.Tensor, O_col: torch.Tensor, O_row_ptr: torch.Tensor, N: int):
+    """The critical blocks regrouped by the 64-row x 128-column unit of Q they fall into (fields crit_ptr,
+    crit_pos, crit_O of struct EptqLayer), from the CSR side tables: (int32 (units+1), int32 (n) bit pattern of
+    uint32 (row % 64) << 16 | col, fp16 (n, 8))."""
+    M = O_row_ptr.shape[0] - 1
+    dev = O_col.device
+    counts = (O_row_ptr[1:] - O_row_ptr[:-1]).to(torch.int64)
+    rows = torch.repeat_interleave(torch.arange(M, device=dev), counts)
+    cols = O_col.to(torch.int64)
+    cc = (N + 127) // 128
+    units = ((M + 63) // 64) * cc
+    unit = (rows // 64) * cc + cols // 128
+    order = torch.argsort(unit, stable=True)
+    ptr = torch.zeros(units + 1, dtype=torch.int32, device=dev)
+    ptr[1:] = torch.bincount(unit, minlength=units).cumsum(0).to(torch.int32)
+    pos = (((rows % 64) << 16) | cols)[order].to(torch.int32)
+    return ptr.contiguous(), pos.contiguous(), O_vals.reshape(-1, 8)[order].contiguous()
+
+
 def _make_desc(quantizer_type: str, Q, table32, table16, g, h, O_vals, O_col, O_row_ptr, bias, S_group,
-               qb_size: int) -> _lib.EptqLayer:
+               qb_size: int, crit=None) -> _lib.EptqLayer:
     d = _lib.EptqLayer()
     d.quantizer = _lib.QUANTIZER_ID[quantizer_type]
     d.M, d.N = Q.shape
@@ -234,6 +253,9 @@ def _make_desc(quantizer_type: str, Q, table32, table16, g, h, O_vals, O_col, O_
     d.table8, d.table8_scale = None, 0.0
     d.h_absmax = h_absmax(h) if Q.is_cuda else 0.0
     d.table_packed, d.table_packed_scale = None, 0.0
+    d.crit_ptr = d.crit_pos = d.crit_O = None
+    if crit is not None:
+        d.crit_ptr, d.crit_pos, d.crit_O = crit[0].data_ptr(), _ptr(crit[1]), _ptr(crit[2])
     if quantizer_type == "e8_lattice" and Q.is_cuda:
         packed = e8_packed(table32 if table32 is not None else table16)
         if packed is not None:

@@ -24,7 +24,7 @@ import torch.nn as nn
 import ctypes as C
 
 from .. import _lib
-from . import _make_desc, dequantize_layer, linear_forward, linear_forward_group, workspace_for
+from . import _make_desc, critical_lists, dequantize_layer, linear_forward, linear_forward_group, workspace_for
 
 MARKER = 32767     # int16 value that marks a critical block (index 65535 - 32768)
 
@@ -85,6 +85,12 @@ class EPTQLinear(nn.Module):
         self.register_buffer("_materialized_weight",
                              materialized_weight.contiguous() if materialized_weight is not None else None)
         self.qb_size = self.out_features // S_group.shape[0] if S_group is not None else 0
+        # Critical blocks regrouped by 64 x 128 unit of Q for the streaming GEMV: derived like the CSR tables,
+        # not part of the saved state.
+        crit = (critical_lists(self.O_vals, self.O_col, self.O_row_ptr, self.in_features)
+                if quantizer_type == "e8_d4" and S_group is None else (None, None, None))
+        for name, t in zip(("crit_ptr", "crit_pos", "crit_O"), crit):
+            self.register_buffer(name, t, persistent=False)
 
         # Shared between layers, therefore plain attributes, not buffers.
         self._codebook = codebook
@@ -195,8 +201,9 @@ class EPTQLinear(nn.Module):
 
     def descriptor(self):
         """The C-ABI description (struct EptqLayer) of this layer's device buffers."""
+        crit = (self.crit_ptr, self.crit_pos, self.crit_O) if self.crit_ptr is not None else None
         return _make_desc(self.quantizer_type, self.Q, self._codebook32, self._codebook, self.g, self.h,
-                          self.O_vals, self.O_col, self.O_row_ptr, self.bias, self.S_group, self.qb_size)
+                          self.O_vals, self.O_col, self.O_row_ptr, self.bias, self.S_group, self.qb_size, crit)
 
     def extra_repr(self) -> str:
         return (f"in={self.in_features}, out={self.out_features}, quantizer={self.quantizer_type}, "

@@ -71,6 +71,14 @@ enum { EPTQ_E8 = 0, EPTQ_E8D4 = 1 };
  *   O_vals     fp16 (n_masked, 8), ordered by row-major position of the markers.
  *   O_col      int32 (n_masked) column of each marker, same order.
  *   O_row_ptr  int32 (M+1) CSR row pointers into O_vals / O_col.
+ *   crit_ptr, crit_pos, crit_O   optional side table of the same kind as O_col / O_row_ptr, derived at load
+ *              time: the critical blocks grouped by the 64-row x 128-column unit of Q
+ *              they fall into, units in row-tile-major order (unit = (row/64) *
+ *              ceil(N/128) + col/128).  crit_ptr int32 (units + 1) offsets; crit_pos
+ *              uint32 (n_masked) = (row % 64) << 16 | col; crit_O fp16 (n_masked, 8) =
+ *              O_vals in that order.  With it the streaming GEMV patches critical blocks
+ *              in step with the index stream instead of walking the CSR; all three NULL
+ *              otherwise.
  *   bias       fp16 (8*M) or NULL.
  *   S_group    fp16 (8*M/qb_size, N) group scales or NULL (then qb_size = 0).
  *              qb_size must be a multiple of 8.
@@ -98,6 +106,9 @@ typedef struct EptqLayer {
     const uint32_t* table_packed; /* E8 only, optional: 65536 packed entries, see below */
     float table_packed_scale;
     int32_t reserved;
+    const int32_t* crit_ptr;
+    const uint32_t* crit_pos;
+    const uint16_t* crit_O;
 } EptqLayer;
 
 /* ABI version of the loaded library (EPTQ_ABI_VERSION at build time). */
