@@ -77,7 +77,7 @@ class ClockSampler:
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "20",
                  "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -112,6 +112,13 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------- CPU path
+
+def host_threads() -> int:
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
 
 def cpu_reference_path(batch: int, reps: int, threads: int | None = None):
     """Reference's CPU path on one decoder layer's seven linears: reconstruct once
@@ -152,8 +159,9 @@ def run_reference_arm(args):
     if rank != 0:
         return
     t0 = time.perf_counter()
-    reps = max(args.steps, 3)
-    res = cpu_reference_path(args.batch, reps)
+    reps = max(min(args.steps, 30), 3)
+    # torch.distributed.run exports OMP_NUM_THREADS=1: take the cores this process may run on instead
+    res = cpu_reference_path(args.batch, reps, threads=host_threads())
     line = {
         "impl": "reference", "metric": METRIC, "value": res["value"], "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": res["ms_per_layer_set"] * N_LAYERS,
@@ -280,6 +288,39 @@ def run_gpu_arm(args):
             for y in reduce_ys:
                 all_reduce(y)
 
+    # Tensor-parallel check before anything is timed: the all-reduced output of the sharded row-parallel layers
+    # of decoder layer 0 against the unsharded layer, and the push all-reduce against NCCL on a seeded vector.
+    tp_check = None
+    if world > 1:
+        errs = []
+        for i, (name, (out_f, in_f)) in enumerate(LLAMA2_7B_LINEARS.items()):
+            if name.split(".")[-1] not in ROW_PARALLEL:
+                continue
+            full = EPTQLinear.from_quantized_data(make_layer(out_f, in_f, seed=i, device=str(dev)), table, kind)
+            xf = torch.randn(1, in_f, device=dev, generator=torch.Generator(device=dev).manual_seed(77)).half()
+            want = full(xf).float()
+            shard = layers[i][1]
+            cols = in_f // world
+            part = shard(xf[:, rank * cols:(rank + 1) * cols].contiguous())
+            all_reduce(part)
+            errs.append(float((part.float() - want).abs().max() / want.abs().max()))
+            del full
+        v = torch.randn(8192, device=dev, generator=torch.Generator(device=dev).manual_seed(100 + rank)).half()
+        ref = v.clone()
+        dist.all_reduce(ref)
+        got = v.clone()
+        all_reduce(got)
+        ar_err = float((got.float() - ref.float()).abs().max() / ref.float().abs().max())
+        t = torch.tensor([max(errs), ar_err], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        tp_check = {"row_parallel_max_rel": float(t[0]), "allreduce_max_rel": float(t[1]),
+                    "ok": bool(float(t[0]) <= 2e-3 and float(t[1]) <= 2e-3)}
+        if not tp_check["ok"]:
+            if rank == 0:
+                print(json.dumps({"metric": METRIC, "error": "tensor-parallel check failed", "tp_check": tp_check}))
+            sys.stdout.flush()
+            os._exit(3)
+
     side = torch.cuda.Stream(device=dev)
     with torch.cuda.stream(side):
         step_abi()
@@ -378,6 +419,155 @@ def run_gpu_arm(args):
     ms_e2e, _ = timed(e2e_step, args.steps, args.warmup)
     h2d = sum(v.numel() * 2 for v in x_host.values())
     d2h = y_host.numel() * 2
+
+    # ---- extra figures on the same weights (one GPU): what a decoder layer can really issue, larger batches
+    peak_hbm = measured_peaks()[0]
+    realistic, chained_stats, batch_stats = None, None, {}
+    if world == 1 and group == 7 and args.codebook == "e8d4" and not args.no_extras:
+        names = [n.split(".")[-1] for n, _ in layers[:7]]
+        idx = {n: k for k, n in enumerate(names)}
+        H, FF = layers[idx["q_proj"]][1].in_features, layers[idx["gate_proj"]][1].out_features
+        att = torch.randn(1, H, device=dev).half() * 0.1
+        xres = torch.randn(1, H, device=dev).half()
+        gbuf = torch.empty(1, FF, device=dev, dtype=torch.float16)
+        ubuf = torch.empty_like(gbuf)
+        qkv_out = [torch.empty(1, H, device=dev, dtype=torch.float16) for _ in range(3)]
+
+        def ptrs(ts):
+            return (C.c_void_p * len(ts))(*[t.data_ptr() for t in ts])
+
+        # (1) the dependent chain of a decoder layer as four group launches: {q,k,v} -> {o} -> {gate,up} -> {down}
+        sets = []
+        for li in range(n_layers):
+            d = descs[li * 7:(li + 1) * 7]
+            for members, xin, outs in ((("q_proj", "k_proj", "v_proj"), [xres] * 3, qkv_out),
+                                       (("o_proj",), [att], [qkv_out[0]]),
+                                       (("gate_proj", "up_proj"), [xres] * 2, [gbuf, ubuf]),
+                                       (("down_proj",), [gbuf], [qkv_out[1]])):
+                arr = (_lib.EptqLayer * len(members))(*[d[idx[m]] for m in members])
+                sets.append((arr, len(members), ptrs(xin), ptrs(outs)))
+
+        def step_realistic():
+            stream = torch.cuda.current_stream().cuda_stream
+            for arr, n, xp, yp in sets:
+                st = lib.eptq_linear_forward_group(arr, n, xp, yp, 1, ws.data_ptr(), ws.numel(), stream)
+                if st != 0:
+                    raise RuntimeError(lib.eptq_strerror(st).decode())
+
+        def graphed(fn):
+            with torch.cuda.stream(side):
+                fn()
+                torch.cuda.synchronize()
+                g_ = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g_, stream=side):
+                    fn()
+            torch.cuda.synchronize()
+            return g_
+        g_real = graphed(step_realistic)
+        ms_real, _ = timed(g_real.replay, args.steps, args.warmup)
+        v = total_bytes / (ms_real / args.steps * 1e-3) / 1e9
+        realistic = {"value": v, "unit": UNIT, "ms_per_step": ms_real / args.steps, "frac_of_hbm_peak": v / peak_hbm,
+                     "launches_per_step": len(sets),
+                     "note": "per decoder layer four stream-ordered group launches {q,k,v} -> {o} -> {gate,up} -> {down}: "
+                             "the grouping a model can issue"}
+        del g_real
+
+        # (2) the same work as ONE chained launch per decoder layer: o -> gate/up -> down -> q/k/v, with the
+        # fused input ops the decode engine uses (residual add, RMSNorm factor, silu*up)
+        def fus(x_op=_lib.X_PLAIN, y_op=_lib.Y_STORE, residual=None, x_aux=None):
+            f = _lib.EptqFusion()
+            f.x_op, f.y_op, f.norm_eps = x_op, y_op, 1e-5
+            f.residual = None if residual is None else residual.data_ptr()
+            f.x_aux = None if x_aux is None else x_aux.data_ptr()
+            return f
+        order = ("o_proj", "gate_proj", "up_proj", "down_proj", "q_proj", "k_proj", "v_proj")
+        phases = (C.c_int * 7)(0, 1, 1, 2, 3, 3, 3)
+        fz = (_lib.EptqFusion * 7)(fus(), fus(_lib.X_RMSNORM), fus(_lib.X_RMSNORM), fus(_lib.X_SILU_MUL, x_aux=ubuf),
+                                   fus(_lib.X_RMSNORM), fus(_lib.X_RMSNORM), fus(_lib.X_RMSNORM))
+        y_o = torch.empty(1, H, device=dev, dtype=torch.float16)
+        y_d = torch.empty(1, H, device=dev, dtype=torch.float16)
+        cxs, cys = ptrs([att, y_o, y_o, gbuf, y_d, y_d, y_d]), ptrs([y_o, gbuf, ubuf, y_d] + qkv_out)
+        chains = [(_lib.EptqLayer * 7)(*[descs[li * 7 + idx[m]] for m in order]) for li in range(n_layers)]
+
+        def step_chain():
+            stream = torch.cuda.current_stream().cuda_stream
+            for arr in chains:
+                st = lib.eptq_linear_forward_chain(arr, 7, fz, phases, cxs, cys, 1, ws.data_ptr(), ws.numel(), stream)
+                if st != 0:
+                    raise RuntimeError(lib.eptq_strerror(st).decode())
+        try:
+            g_chain = graphed(step_chain)
+            ms_c, _ = timed(g_chain.replay, args.steps, args.warmup)
+            v = total_bytes / (ms_c / args.steps * 1e-3) / 1e9
+            chained_stats = {"value": v, "unit": UNIT, "ms_per_step": ms_c / args.steps, "frac_of_hbm_peak": v / peak_hbm,
+                             "launches_per_step": len(chains),
+                             "note": "one cooperative launch per decoder layer, four dependent phases "
+                                     "o -> gate/up -> down(silu*up) -> q/k/v"}
+            del g_chain
+        except RuntimeError as exc:
+            chained_stats = {"unavailable": str(exc)}
+
+        # (3) batches 4 and 16 of the baseline's second configuration, grouped as the headline
+        for Bx in (4, 16):
+            xb = {n: torch.randn(Bx, n, device=dev).half() for n in xs}
+            yb = [torch.empty(Bx, l.out_features, device=dev, dtype=torch.float16) for _, l in layers[:7]]
+            bcalls, need = [], 0
+            for i in range(0, len(layers), 7):
+                arr = (_lib.EptqLayer * 7)(*descs[i:i + 7])
+                need = max(need, lib.eptq_group_workspace_bytes(arr, 7, Bx))
+                bcalls.append((arr, ptrs([xb[l.in_features] for _, l in layers[i:i + 7]]), ptrs(yb)))
+            wsb = ws if need <= ws.numel() else torch.zeros(need, dtype=torch.uint8, device=dev)
+
+            def step_b():
+                stream = torch.cuda.current_stream().cuda_stream
+                for arr, xp, yp in bcalls:
+                    st = lib.eptq_linear_forward_group(arr, 7, xp, yp, Bx, wsb.data_ptr(), wsb.numel(), stream)
+                    if st != 0:
+                        raise RuntimeError(lib.eptq_strerror(st).decode())
+            g_b = graphed(step_b)
+            ms_b, _ = timed(g_b.replay, max(3, args.steps // 4), 3)
+            per = ms_b / max(3, args.steps // 4)
+            bytes_b = total_bytes + sum(2 * (Bx - 1) * (l.in_features + l.out_features) for _, l in layers)
+            batch_stats[f"batch{Bx}"] = {"value": bytes_b / (per * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": per,
+                                         "frac_of_hbm_peak": bytes_b / (per * 1e-3) / 1e9 / peak_hbm,
+                                         "step_time_vs_batch1": per / (ms_dev / args.steps)}
+            del g_b, bcalls
+
+    # ---- prefill GEMM, baseline's fourth configuration: Llama-3-8B shapes, group scales qb=128, 2048 tokens
+    gemm_stats = None
+    if world == 1 and not args.no_extras and args.codebook == "e8d4":
+        from eptq_b200.synthetic import LLAMA3_8B_LINEARS
+        pk = ROOT / "MEASURED_PEAKS.json"
+        tensor_peak = json.loads(pk.read_text())["bf16_tflops"] if pk.exists() else 1590.0
+        T = 2048
+        gemm_stats = {"tokens": T, "peak_tflops": tensor_peak, "peak_kind": "measured bf16 burst" if pk.exists() else "fallback",
+                      "shapes": {}}
+        seen, tot_flops, tot_ms = set(), 0.0, 0.0
+        for name, (o, i) in LLAMA3_8B_LINEARS.items():
+            if (o, i) in seen:
+                continue
+            seen.add((o, i))
+            lin = EPTQLinear.from_quantized_data(make_layer(o, i, seed=42, device=str(dev), qb_size=128), table, KIND)
+            xg = torch.randn(T, i, device=dev).half()
+            for _ in range(3):
+                lin(xg)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(5):
+                lin(xg)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / 5
+            fl = 2.0 * T * o * i
+            count = sum(1 for v in LLAMA3_8B_LINEARS.values() if v == (o, i))
+            tot_flops += fl * count
+            tot_ms += ms * count
+            gemm_stats["shapes"][f"{o}x{i}"] = {"ms": ms, "tflops": fl / ms / 1e9, "frac_of_peak": fl / ms / 1e9 / tensor_peak}
+            del lin, xg
+        gemm_stats["layer_tflops"] = tot_flops / tot_ms / 1e9
+        gemm_stats["layer_frac_of_peak"] = tot_flops / tot_ms / 1e9 / tensor_peak
+        torch.cuda.empty_cache()
 
     # The same layer set with the E8 codebook (radius 1.6) through the same grouped launch: the codebook of the
     # baseline's first, third and fifth configurations.  Reported as an extra figure.
@@ -505,9 +695,15 @@ def run_gpu_arm(args):
         "clocks": clocks,
         "decode": decode_stats or None,
         "e8_layer_set": e8_stats,
+        "realistic_grouping": realistic,
+        "chained_layer": chained_stats,
+        "batch4": batch_stats.get("batch4"),
+        "batch16": batch_stats.get("batch16"),
+        "gemm": gemm_stats,
+        "tp_check": tp_check,
     }
     if not args.no_cpu_baseline and world == 1:
-        res = cpu_reference_path(B, 10)
+        res = cpu_reference_path(B, 10, threads=host_threads())
         line["cpu_baseline"] = {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")}
     print(json.dumps(line))
     if world > 1:
@@ -518,8 +714,8 @@ def run_gpu_arm(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--layers", type=int, default=N_LAYERS)
@@ -528,6 +724,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true", help="skip the whole-model decode tokens/s arm")
     ap.add_argument("--no-e8", action="store_true", help="skip the E8-codebook layer-set figure")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the realistic-grouping, chained-layer, batch 4/16 and prefill-GEMM figures")
     ap.add_argument("--nccl", action="store_true", help="tensor-parallel runs: NCCL all-reduce instead of the push kernel")
     ap.add_argument("--codebook", default="e8d4", choices=["e8d4", "e8"],
                     help="codebook of the timed layer set (the headline is e8d4)")
