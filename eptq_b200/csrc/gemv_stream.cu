@@ -78,6 +78,7 @@ struct StreamArgs {
     alignas(64) CUtensorMap maps[kMaxGroupLayers];
     float unit;                                   // table value = integer coordinate * unit
     float inv_unit;
+    unsigned zero;                                // 0: addend that keeps q * 128 + zero a multiply-add (FMA pipe, not the shifter)
     int use_lists;                                // every layer brings its critical blocks as unit lists
     int* status;
     unsigned long long wait_ns;                   // limit of one mbarrier wait
@@ -119,8 +120,10 @@ __device__ __noinline__ bool mbar_wait_slow(unsigned bar, unsigned parity, unsig
     unsigned long long t0;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
     for (;;) {
-        for (int i = 0; i < 64; ++i)
+        for (int i = 0; i < 16; ++i) {
             if (mbar_try(bar, parity)) return true;
+            __nanosleep(250);                               // leave the issue slots to the warps that have work
+        }
         unsigned long long t;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
         if (t - t0 > limit_ns) return false;
@@ -713,9 +716,9 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
     // ldmatrix row address of this lane inside a stage: matrix lane>>3 = row group, row lane&7, 128-byte swizzle.
     const unsigned qm = kRing + static_cast<unsigned>(chunk64 * 8192 + ((lane >> 3) * 8 + (lane & 7)) * 128 + ((w8 ^ (lane & 7)) << 4));
 
+    const unsigned zr = P.zero;
     bool ok = true;
     bool dep_waited = false;
-    float out_scale = 0.f, inv_rms_l = 1.f;
     unsigned flush_no = 0, prep_no = 0;
 
     // Digit planes (and the fused RMSNorm factor) of layer l.  Four chunks of 8 columns per thread stay in
@@ -800,8 +803,10 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
 #pragma unroll
         for (int w = 0; w < kConsumerWarps; ++w) { mx = fmaxf(mx, part[w]); tot += part[16 + w]; }
         const float S = mx > 0.f ? 32000.f / mx : 1.f;
-        out_scale = P.unit / S;
-        inv_rms_l = L.x_op == EPTQ_X_RMSNORM ? rsqrtf(tot / static_cast<float>(L.N) + L.norm_eps) : 1.f;
+        if (tid == 0) {                                      // read back by thread 0 at each flush of this layer
+            misc[56] = L.x_op == EPTQ_X_RMSNORM ? rsqrtf(tot / static_cast<float>(L.N) + L.norm_eps) : 1.f;
+            misc[57] = P.unit / S;
+        }
         const int n_pad = L.cc128 * 128;
         auto digits = [&](int c, const float (&v)[8]) {
             unsigned lo[2] = {0u, 0u}, hi[2] = {0u, 0u};
@@ -860,8 +865,8 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
                 acc[r][c] = 0;
             }
         if (tid == 0) {
-            sts32(kMail + 16 * b + 8, __float_as_uint(inv_rms_l));
-            sts32(kMail + 16 * b + 12, __float_as_uint(out_scale));
+            sts32(kMail + 16 * b + 8, __float_as_uint(misc[56]));
+            sts32(kMail + 16 * b + 12, __float_as_uint(misc[57]));
         }
         mbar_arrive(kRedFull + 8 * b);
         ++flush_no;
@@ -887,22 +892,33 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
         }
         unsigned plane_c = plane + sg.cc * 128;
         for (int j = 0; j < sg.n; ++j) {
-            unsigned a[8][4];
+            // Two halves of four row groups: the second half's lookups are in flight while the first half's
+            // products issue (16 registers of table words instead of 32).
+            unsigned a[4][4];
+            auto lookups = [&](int half) {
 #pragma unroll
-            for (int r = 0; r < 8; ++r) {
-                const unsigned qq = q[r];
-                const unsigned qs = qq >> 16;
-                const unsigned ia = (qq & 0xFF80u) | lane_tab;
-                const unsigned ib = (qs & 0xFF80u) | lane_tab;
-                a[r][0] = lds32(ia);
-                a[r][1] = lds32(bitsel(qq << 7, ia, 0x3F80u));
-                a[r][2] = lds32(ib);
-                a[r][3] = lds32(bitsel(qs << 7, ib, 0x3F80u));
-            }
-            mbar_arrive(kEmptyBar + 8 * s);                 // every lane: its indices are in registers
+                for (int r = 0; r < 4; ++r) {
+                    const unsigned qq = q[4 * half + r];
+                    const unsigned qs = qq >> 16;
+                    const unsigned ia = (qq & 0xFF80u) | lane_tab;
+                    const unsigned ib = (qs & 0xFF80u) | lane_tab;
+                    unsigned ta, tb;
+                    asm("mad.lo.u32 %0, %1, 128, %2;" : "=r"(ta) : "r"(qq), "r"(zr));
+                    asm("mad.lo.u32 %0, %1, 128, %2;" : "=r"(tb) : "r"(qs), "r"(zr));
+                    a[r][0] = lds32(ia);
+                    a[r][1] = lds32(bitsel(ta, ia, 0x3F80u));
+                    a[r][2] = lds32(ib);
+                    a[r][3] = lds32(bitsel(tb, ib, 0x3F80u));
+                }
+            };
             const unsigned pv = lds16(plane_c);
             const unsigned b0 = prmt(pv, 0u, sel0), b1 = prmt(pv, 0u, sel1);
             plane_c += 128;
+            lookups(0);
+#pragma unroll
+            for (int r = 0; r < 4; ++r) imma(acc[r], a[r][0], a[r][1], a[r][2], a[r][3], b0, b1);
+            lookups(1);
+            mbar_arrive(kEmptyBar + 8 * s);                 // every lane: its indices are in registers
             ++i;
             if (++s == kStages) { s = 0; ph ^= 1u; }
             if (i < n_units) {                              // the next unit of the block, whatever segment it is in
@@ -912,7 +928,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
                 ldsm4(stage + 4096, q[4], q[5], q[6], q[7]);
             }
 #pragma unroll
-            for (int r = 0; r < 8; ++r) imma(acc[r], a[r][0], a[r][1], a[r][2], a[r][3], b0, b1);
+            for (int r = 0; r < 4; ++r) imma(acc[4 + r], a[r][0], a[r][1], a[r][2], a[r][3], b0, b1);
         }
         if (i == n_units) EPTQ_STRACE(4, warp == 0);
         flush();
@@ -1052,6 +1068,7 @@ int launch_gemv_stream(const EptqLayer* layers, int n, const EptqFusion* fusions
     a.unit = layers[0].table8_scale;
     a.inv_unit = 1.0f / layers[0].table8_scale;
     a.status = reinterpret_cast<int*>(workspace) + (kMaxCounters - 1);
+    a.zero = 0u;
     a.wait_ns = 2000000000ull;
 
     static bool attr_done[64] = {};            // guarded by args_mutex
