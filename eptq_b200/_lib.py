@@ -36,6 +36,9 @@ EXPORTS = {
     "eptq_allreduce_data_bytes": (_sz, [_i, _i]),
     "eptq_allreduce_flag_bytes": (_sz, [_i]),
     "eptq_allreduce_push": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _vp]),
+    "eptq_allreduce_set_wait_ns": (None, [C.c_uint64]),
+    "eptq_lm_head_workspace_bytes": (_sz, [_i]),
+    "eptq_lm_head_argmax": (_i, [_vp, _vp, _vp, C.c_float, _vp, _vp, _i, _i, _i, _vp, _sz, _vp]),
     "eptq_add_rmsnorm": (_i, [_vp, _vp, _vp, _vp, _i, _i, C.c_float, _vp]),
     "eptq_silu_mul": (_i, [_vp, _vp, _vp, _sz, _vp]),
     "eptq_rope_append": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, C.c_float, _vp]),

@@ -24,7 +24,8 @@ namespace {
 constexpr int kArBlocks = 8;
 constexpr int kArThreads = 128;
 constexpr int kArMaxRanks = 8;
-constexpr unsigned long long kArWaitNs = 2000000000ull;   // a wait gives up after two seconds
+constexpr unsigned long long kArWaitNs = 2000000000ull;   // default: a wait gives up after two seconds
+unsigned long long g_ar_wait_ns = kArWaitNs;              // changed only by eptq_allreduce_set_wait_ns
 
 struct PushArgs {
     __half* data[kArMaxRanks];        // every rank's data buffer (this rank's own included)
@@ -35,6 +36,7 @@ struct PushArgs {
     unsigned* seq;                    // kArBlocks call counters of this rank
     int* status;                      // set to EPTQ_ERR_TIMEOUT if a wait ran out
     int rank, T, n, n_max;
+    unsigned long long wait_ns;       // limit of the wait for the peers' words
 };
 
 __global__ void __launch_bounds__(kArThreads) allreduce_push_kernel(const PushArgs a) {
@@ -48,16 +50,18 @@ __global__ void __launch_bounds__(kArThreads) allreduce_push_kernel(const PushAr
     __syncthreads();
     const unsigned seq = s_seq;
     const unsigned parity = seq & 1u;
-    // A word is two fp16 values plus the call number, written with ONE 8-byte store: the receiver polls the
-    // word itself, so no fence and no separate flag are needed (the payload and its flag cannot be seen apart).
+    // A word is two fp16 values plus the call number in ONE 64-bit register, written with one b64 store and read
+    // with one b64 load (single-copy atomic when 8-byte aligned): the receiver polls the word itself, so no
+    // fence and no separate flag are needed (the payload and its tag cannot be seen apart).
     const int words = a.n >> 1, words_max = a.n_max >> 1;
     const size_t my_slot = (static_cast<size_t>(parity) * a.T + a.rank) * words_max;
     const unsigned* x32 = reinterpret_cast<const unsigned*>(a.x);
     for (int w = b * kArThreads + tid; w < words; w += kArBlocks * kArThreads) {
         const unsigned v = x32[w];
         for (int r = 0; r < a.T; ++r) {
-            uint2* dst = reinterpret_cast<uint2*>(a.data[r]) + my_slot + w;
-            asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1,%2};" :: "l"(dst), "r"(v), "r"(seq) : "memory");
+            unsigned long long* dst = reinterpret_cast<unsigned long long*>(a.data[r]) + my_slot + w;
+            const unsigned long long word = static_cast<unsigned long long>(v) | (static_cast<unsigned long long>(seq) << 32);
+            asm volatile("st.relaxed.sys.global.b64 [%0], %1;" :: "l"(dst), "l"(word) : "memory");
         }
     }
     const uint2* mine = reinterpret_cast<const uint2*>(a.data[a.rank]) + static_cast<size_t>(parity) * a.T * words_max;
@@ -77,7 +81,10 @@ __global__ void __launch_bounds__(kArThreads) allreduce_push_kernel(const PushAr
             for (int r = 0; r < kArMaxRanks; ++r)
                 if ((missing >> r) & 1u) {
                     const uint2* src = mine + static_cast<size_t>(r) * words_max + w;
-                    asm volatile("ld.relaxed.sys.global.v2.u32 {%0,%1}, [%2];" : "=r"(lo[r]), "=r"(flag[r]) : "l"(src) : "memory");
+                    unsigned long long word;
+                    asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(word) : "l"(src) : "memory");
+                    lo[r] = static_cast<unsigned>(word);
+                    flag[r] = static_cast<unsigned>(word >> 32);
                 }
 #pragma unroll
             for (int r = 0; r < kArMaxRanks; ++r)
@@ -86,7 +93,7 @@ __global__ void __launch_bounds__(kArThreads) allreduce_push_kernel(const PushAr
                 unsigned long long now;
                 asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
                 if (t_start == 0) t_start = now;
-                else if (now - t_start > kArWaitNs) { ok = false; break; }
+                else if (now - t_start > a.wait_ns) { ok = false; break; }
             }
         }
         if (!ok) { atomicExch(a.status, static_cast<int>(EPTQ_ERR_TIMEOUT)); break; }
@@ -145,6 +152,7 @@ extern "C" int eptq_allreduce_push(const uint16_t* x, uint16_t* out, const uint1
     a.out = reinterpret_cast<__half*>(out);
     a.residual = reinterpret_cast<const __half*>(residual);
     a.rank = rank; a.T = n_ranks; a.n = n; a.n_max = n_max;
+    a.wait_ns = g_ar_wait_ns;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(kArBlocks);
     cfg.blockDim = dim3(kArThreads);
@@ -158,3 +166,7 @@ extern "C" int eptq_allreduce_push(const uint16_t* x, uint16_t* out, const uint1
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return cudaGetLastError() == cudaSuccess ? EPTQ_OK : EPTQ_ERR_LAUNCH;
 }
+
+// Limit of the device-side wait of later eptq_allreduce_push calls, in nanoseconds (0 restores the default of
+// two seconds).  For tests of the timeout path; process-wide.
+extern "C" void eptq_allreduce_set_wait_ns(unsigned long long ns) { g_ar_wait_ns = ns == 0 ? kArWaitNs : ns; }

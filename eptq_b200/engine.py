@@ -84,6 +84,7 @@ class LlamaDecodeEngine:
         self.position = torch.zeros((1,), dtype=torch.long, device=dev)
         self.next_token = torch.zeros((self.batch,), dtype=torch.long, device=dev)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self._pick: Optional[torch.Tensor] = None     # where a fused step writes its token (set inside _step)
         self._fused = None           # descriptors for the fully fused one-token step, False if not eligible
 
     # ---- construction -------------------------------------------------------------------------
@@ -230,8 +231,7 @@ class LlamaDecodeEngine:
                 linear_forward_group(P["down"], [act], [0], fusions=res_f, ys=[x])
             else:
                 self.comm.all_reduce_(linear_forward_group(P["down"], [act], [L.down.out_features])[0], residual=x)
-        hn = glue.add_rmsnorm(x, self.final_norm, self.eps)
-        return F.linear(hn, self.lm_head).reshape(B, 1, -1)
+        return self._head(x, B)
 
     # ---- one token, two launches per decoder layer ----------------------------------------------
     def _chainable(self) -> bool:
@@ -289,8 +289,19 @@ class LlamaDecodeEngine:
                 ys += [qs[(li + 1) & 1], self.k_cache[li + 1], self.v_cache[li + 1]]
                 fz += qkv_f
             linear_forward_chain(descs, phases, xs, [0] * len(descs), fz, ys=ys)
+        return self._head(x, 1)
+
+    def _head(self, x: torch.Tensor, B: int) -> torch.Tensor:
+        """Final RMSNorm and lm_head of a one-token step.  While a step is being taken (`_pick` set by `_step`),
+        the library's fused norm + projection + greedy pick writes the next token and the logits are not
+        materialised; otherwise logits (B, 1, V)."""
+        from .kernels import glue
+        H = x.shape[-1]
+        if self._pick is not None and B <= 4 and H % 256 == 0 and H <= 8192:
+            glue.lm_head_argmax(x, self.lm_head, self.final_norm, self.eps, tokens=self._pick)
+            return None
         hn = glue.add_rmsnorm(x, self.final_norm, self.eps)
-        return F.linear(hn, self.lm_head).reshape(1, 1, -1)
+        return F.linear(hn, self.lm_head).reshape(B, 1, -1)
 
     def forward_reference(self, ids: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
         """The same step in plain PyTorch ops, on any device and dtype: what `forward` is tested against,
@@ -345,7 +356,15 @@ class LlamaDecodeEngine:
         return self.forward(ids, positions) if fused else self.forward_reference(ids, positions)
 
     def _step(self) -> None:
-        logits = self._fwd(self.token, self.position)
+        self._pick = self.next_token if (self.token.is_cuda and self.dtype == torch.float16) else None
+        try:
+            logits = self._fwd(self.token, self.position)
+        finally:
+            self._pick = None
+        if logits is None:                                   # the fused head already wrote next_token
+            self.token.copy_(self.next_token[:, None])
+            self.position.add_(1)
+            return
         nxt = logits[:, -1].argmax(dim=-1)
         self.next_token.copy_(nxt)
         self.token.copy_(nxt[:, None])

@@ -83,3 +83,33 @@ def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
                                    _stream(q.device))
     _lib.check(st, "eptq decode_attention")
     return out
+
+
+_lm_ws: Dict[tuple, torch.Tensor] = {}
+
+
+def lm_head_argmax(x: torch.Tensor, weight: torch.Tensor, norm_weight: Optional[torch.Tensor] = None,
+                   eps: float = 0.0, want_logits: bool = False, tokens: Optional[torch.Tensor] = None):
+    """Greedy pick through the un-quantized output projection (eptq_lm_head_argmax): x (B, H) fp16, weight
+    (V, H) fp16 -> int64 tokens (B,), the first index of the maximum of fp16(weight @ x_b).  `norm_weight`
+    applies the model's final RMSNorm to x on the way in.  Returns (tokens, logits or None)."""
+    _need(x=x, weight=weight, norm_weight=norm_weight, tokens=tokens)
+    if x.dtype != torch.float16 or weight.dtype != torch.float16:
+        raise RuntimeError("eptq_b200: lm_head_argmax takes fp16 tensors")
+    lib = _lib.load()
+    B, H = x.shape
+    V = weight.shape[0]
+    need = lib.eptq_lm_head_workspace_bytes(B)
+    if need == 0:
+        raise RuntimeError("eptq_b200: lm_head_argmax takes 1..4 rows")
+    key = (x.device, torch.cuda.current_stream(x.device).cuda_stream)
+    ws = _lm_ws.get(key)
+    if ws is None or ws.numel() < need:
+        ws = _lm_ws[key] = torch.zeros(need, dtype=torch.uint8, device=x.device)
+    tokens = torch.empty(B, dtype=torch.int64, device=x.device) if tokens is None else tokens
+    logits = torch.empty((B, V), dtype=torch.float16, device=x.device) if want_logits else None
+    st = lib.eptq_lm_head_argmax(weight.data_ptr(), x.data_ptr(), None if norm_weight is None else norm_weight.data_ptr(),
+                                 float(eps), None if logits is None else logits.data_ptr(), tokens.data_ptr(),
+                                 V, H, B, ws.data_ptr(), ws.numel(), _stream(x.device))
+    _lib.check(st, "eptq lm_head_argmax")
+    return tokens, logits

@@ -343,6 +343,21 @@ int eptq_decode_attention(const uint16_t* q, const uint16_t* k_cache,
                           size_t workspace_bytes, void* stream);
 
 /*
+ * Un-quantized output projection fused with the greedy pick.  The reference keeps
+ * lm_head in fp16 (quantize.py:86-90) and picks the token from the logits of a
+ * library GEMM (bench_decode.py:35-41).  W fp16 (V, H) row-major, x fp16 (B, H);
+ * tokens[b] = first index of the maximum of fp16(W x_b), int64 on the device.
+ * `norm_weight` (fp16 (H), or NULL) applies the model's final RMSNorm to x on the way
+ * in: x_b <- norm_weight * fp16(x_b * rsqrt(mean(x_b^2) + eps)).  `logits` (fp16
+ * (B, V), or NULL) also receives the logits.  H a multiple of 256 up to 8192, B <= 4.
+ * Scratch: eptq_lm_head_workspace_bytes(B) bytes, 256-byte aligned, zero-filled once.
+ */
+size_t eptq_lm_head_workspace_bytes(int B);
+int eptq_lm_head_argmax(const uint16_t* W, const uint16_t* x, const uint16_t* norm_weight, float eps,
+                        uint16_t* logits, int64_t* tokens, int V, int H, int B, void* workspace,
+                        size_t workspace_bytes, void* stream);
+
+/*
  * (No counterpart in the reference, which is single-GPU.)  One-shot all-reduce (sum)
  * of a small fp16 vector over the GPUs of one node, for the partial outputs of
  * row-parallel layers in tensor-parallel decode.  Each rank owns a data buffer of
@@ -365,6 +380,9 @@ size_t eptq_allreduce_flag_bytes(int n_ranks);
 int eptq_allreduce_push(const uint16_t* x, uint16_t* out, const uint16_t* residual, int n,
                         void* const* peer_data, void* const* peer_flags, int rank, int n_ranks,
                         int n_max, void* stream);
+/* Limit of that wait for later calls, in nanoseconds (0 = the default, two seconds).  Process-wide; meant
+ * for tests that make the wait run out. */
+void eptq_allreduce_set_wait_ns(unsigned long long ns);
 
 #ifdef __cplusplus
 }

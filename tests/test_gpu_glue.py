@@ -82,3 +82,30 @@ def test_decode_attention(B, T, nh, nkv, hd, max_len, p0):
     mask = (torch.arange(max_len, device="cuda")[None, :] <= pos[:, None])[None, None]
     ref = F.scaled_dot_product_attention(qh, kf, vf, attn_mask=mask).transpose(1, 2).reshape(B * T, nh * hd)
     assert float((out.float() - ref).abs().max()) <= 3e-3 * max(1.0, float(ref.abs().max()))
+
+
+@pytest.mark.parametrize("B,V,H,norm", [(1, 32000, 4096, True), (2, 1000, 512, False), (4, 517, 256, True)])
+def test_lm_head_argmax_matches_torch(B, V, H, norm):
+    """Fused final norm + fp16 projection + greedy pick against the same steps in PyTorch (fp32 matmul of the
+    fp16 operands, logits rounded to fp16, first index of the maximum)."""
+    from eptq_b200.kernels import glue
+    g = torch.Generator(device="cuda").manual_seed(B * 1000 + V)
+    W = (0.05 * torch.randn(V, H, generator=g, device="cuda")).half()
+    x = torch.randn(B, H, generator=g, device="cuda").half()
+    w = (1 + 0.1 * torch.randn(H, generator=g, device="cuda")).half() if norm else None
+    eps = 1e-5
+    hn = x
+    if norm:
+        xf = x.float()
+        hn = w * (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).half()
+    want_logits = (hn.float() @ W.float().T)
+    for _ in range(2):                                    # twice: the ticket in scratch must come back to zero
+        tokens, logits = glue.lm_head_argmax(x, W, w, eps, want_logits=True)
+        torch.cuda.synchronize()
+        assert float((logits.float() - want_logits).abs().max()) <= 2e-3 * float(want_logits.abs().max())
+        # the pick is the first maximum of the kernel's own fp16 logits, and a maximum of the reference within rounding
+        assert torch.equal(tokens, logits.float().argmax(dim=-1))
+        picked = want_logits.gather(1, tokens[:, None])[:, 0]
+        assert bool((want_logits.max(dim=-1).values - picked <= 2e-3 * want_logits.abs().max()).all())
+        t2, none = glue.lm_head_argmax(x, W, w, eps)
+        assert none is None and torch.equal(t2, tokens)
