@@ -20,10 +20,13 @@ EXPORTS = {
     "eptq_abi_version": (_i, []),
     "eptq_strerror": (C.c_char_p, [_i]),
     "eptq_launch_count": (C.c_uint64, []),
+    "eptq_kernel_launch_count": (C.c_uint64, [_i]),
     "eptq_workspace_bytes": (_sz, [_i, _i, _i]),
+    "eptq_layer_workspace_bytes": (_sz, [_vp, _i]),
     "eptq_prepare_d4_table8": (_i, [_vp, _vp, _vp]),
     "eptq_e8_forward": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _sz, _vp]),
     "eptq_e8d4_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _sz, _vp]),
+    "eptq_forget_codebook": (None, [_vp]),
     "eptq_linear_forward": (_i, [_vp, _vp, _vp, _i, _vp, _sz, _vp]),
     "eptq_dequantize": (_i, [_vp, _vp, _vp]),
     "eptq_group_workspace_bytes": (_sz, [_vp, _i, _i]),
@@ -99,6 +102,13 @@ def check(status: int, what: str) -> None:
     if status != 0:
         msg = load().eptq_strerror(status).decode()
         raise RuntimeError(f"{what}: {msg} (eptq status {status})")
+
+
+KERNEL_GEMV_STREAM, KERNEL_GEMV_GROUP, KERNEL_GEMV_MMA, KERNEL_GEMV_SIMT, KERNEL_GEMM, KERNEL_OTHER = range(6)
+
+
+def kernel_launch_count(kernel: int) -> int:
+    return int(load().eptq_kernel_launch_count(kernel))
 
 
 def launch_count() -> int:

@@ -3,12 +3,18 @@
 // (csrc/eptq_kernels.cu:466-558) and the pybind module (csrc/binding.cpp:4-16).
 
 #include <cmath>
+#include <mutex>
+#include <unordered_map>
+#include <vector>
 
 #include "common.cuh"
+
+extern "C" int eptq_prepare_d4_table8(const float* table, uint8_t* out, float* scale);
 
 namespace eptq {
 
 std::atomic<uint64_t> g_launches{0};
+std::atomic<uint64_t> g_kernel_launches[EPTQ_KERNEL_COUNT];
 
 int launch_dequant(const EptqLayer& L, uint16_t* W, cudaStream_t stream);
 int launch_gemv_simt(const EptqLayer& L, const uint16_t* x, uint16_t* y, int B,
@@ -89,6 +95,35 @@ int forward_checked(const EptqLayer& L, const uint16_t* x, uint16_t* y, int B,
     return launch_gemv_simt(L, x, y, B, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
+// E8-D4 tables seen by the reference-signature entry point, keyed by device pointer: the scale of the table as
+// a multiple of the D4 lattice (0 = not such a multiple), found by reading the 4 KB table back once.
+std::mutex g_codebook_mutex;
+std::unordered_map<const void*, float> g_codebook_unit;
+const uint8_t g_table8_marker[4] = {0, 0, 0, 0};     // non-null EptqLayer.table8: "table8_scale is valid"
+
+float d4_unit_of(const uint16_t* codes, cudaStream_t stream) {
+    {
+        std::lock_guard<std::mutex> lock(g_codebook_mutex);
+        auto it = g_codebook_unit.find(codes);
+        if (it != g_codebook_unit.end()) return it->second;
+    }
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) return 0.f;   // no copy inside a capture
+    std::vector<uint16_t> raw(2048);
+    if (cudaMemcpy(raw.data(), codes, 4096, cudaMemcpyDeviceToHost) != cudaSuccess) return 0.f;
+    std::vector<float> tab(2048);
+    for (int i = 0; i < 2048; ++i) {
+        const __half_raw hr = {raw[i]};
+        tab[i] = __half2float(__half(hr));
+    }
+    std::vector<uint8_t> out(2048);
+    float scale = 0.f;
+    if (eptq_prepare_d4_table8(tab.data(), out.data(), &scale) != EPTQ_OK) scale = 0.f;
+    std::lock_guard<std::mutex> lock(g_codebook_mutex);
+    g_codebook_unit[codes] = scale;
+    return scale;
+}
+
 }  // namespace
 }  // namespace eptq
 
@@ -115,6 +150,11 @@ const char* eptq_strerror(int status) {
 
 uint64_t eptq_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
+uint64_t eptq_kernel_launch_count(int kernel) {
+    if (kernel < 0 || kernel >= EPTQ_KERNEL_COUNT) return 0;
+    return g_kernel_launches[kernel].load(std::memory_order_relaxed);
+}
+
 size_t eptq_workspace_bytes(int M, int N, int B) {
     if (M <= 0 || N <= 0 || B <= 0) return 0;
     int cols = 0;
@@ -132,6 +172,13 @@ size_t eptq_workspace_bytes(int M, int N, int B) {
         if (grp > bytes) bytes = grp;
     }
     return (bytes + 255) & ~static_cast<size_t>(255);
+}
+
+size_t eptq_layer_workspace_bytes(const EptqLayer* layer, int B) {
+    if (layer == nullptr || B <= 0) return 0;
+    // Above the GEMV batch limit a layer the tensor-core GEMM takes needs the counter block only.
+    if (B > kGemmMinBatch && gemm_supported(*layer, B)) return kPartialOffset;
+    return eptq_workspace_bytes(layer->M, layer->N, B);
 }
 
 size_t eptq_group_workspace_bytes(const EptqLayer* layers, int n_layers, int B) {
@@ -247,7 +294,17 @@ int eptq_e8d4_forward(const int16_t* Q, const uint16_t* codes,
     L.n_masked = (O_vals != nullptr && O_col != nullptr) ? -1 : 0;
     L.Q = Q; L.table16 = codes; L.g = g; L.h = h;
     L.O_vals = O_vals; L.O_col = O_col; L.O_row_ptr = O_row_ptr; L.bias = bias;
+    if (codes != nullptr && B == 1) {                  // the streaming kernel needs the table as a lattice multiple
+        const float unit = d4_unit_of(codes, static_cast<cudaStream_t>(stream));
+        if (unit > 0.f) { L.table8 = g_table8_marker; L.table8_scale = unit; }
+    }
     return forward_checked(L, x, y, B, workspace, workspace_bytes, stream);
+}
+
+void eptq_forget_codebook(const void* codes) {
+    std::lock_guard<std::mutex> lock(g_codebook_mutex);
+    if (codes == nullptr) g_codebook_unit.clear();
+    else g_codebook_unit.erase(codes);
 }
 
 int eptq_linear_forward(const EptqLayer* layer, const uint16_t* x, uint16_t* y,

@@ -163,7 +163,7 @@ extern "C" int eptq_allreduce_push(const uint16_t* x, uint16_t* out, const uint1
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     cudaLaunchKernelEx(&cfg, allreduce_push_kernel, a);
-    g_launches.fetch_add(1, std::memory_order_relaxed);
+    count_launch(EPTQ_KERNEL_OTHER);
     return cudaGetLastError() == cudaSuccess ? EPTQ_OK : EPTQ_ERR_LAUNCH;
 }
 

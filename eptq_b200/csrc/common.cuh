@@ -20,6 +20,11 @@ constexpr int kMaxSplits = 16;              // column splits a GEMV may use (siz
 constexpr int kRowsPerCta = 8;              // Q rows (groups of 8 outputs) per SIMT GEMV block
 
 extern std::atomic<uint64_t> g_launches;    // kernels launched by this library
+extern std::atomic<uint64_t> g_kernel_launches[EPTQ_KERNEL_COUNT];   // the same per kernel family (EPTQ_KERNEL_*)
+inline void count_launch(int which) {
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    g_kernel_launches[which].fetch_add(1, std::memory_order_relaxed);
+}
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 

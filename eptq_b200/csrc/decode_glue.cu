@@ -382,7 +382,7 @@ void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t st
 }
 
 int finish_launch() {
-    g_launches.fetch_add(1, std::memory_order_relaxed);
+    count_launch(EPTQ_KERNEL_OTHER);
     return cudaGetLastError() == cudaSuccess ? EPTQ_OK : EPTQ_ERR_LAUNCH;
 }
 

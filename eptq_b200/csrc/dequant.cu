@@ -111,7 +111,7 @@ int launch_dequant(const EptqLayer& L, uint16_t* W, cudaStream_t stream) {
     } else {
         dequant_kernel<EPTQ_E8D4><<<static_cast<unsigned>(grid), block, 0, stream>>>(L, Wh, chunks);
     }
-    g_launches.fetch_add(1, std::memory_order_relaxed);
+    count_launch(EPTQ_KERNEL_OTHER);
     return cudaPeekAtLastError() == cudaSuccess ? EPTQ_OK : EPTQ_ERR_LAUNCH;
 }
 

@@ -49,7 +49,7 @@ constexpr unsigned kLBO = 128;      // bytes between core matrices adjacent in K
 constexpr unsigned kSBO = (kChunkK / 8) * 128;   // bytes between 8-row groups
 constexpr int kTileBytes = 128 * kChunkK * 2;    // 16 KB per operand tile
 constexpr unsigned kTmemCols = 128;
-constexpr int kSpinLimit = 20000000;
+constexpr unsigned long long kWaitNs = 2000000000ull;     // limit of one mbarrier wait
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) {
     return static_cast<unsigned>(__cvta_generic_to_shared(p));
@@ -72,7 +72,10 @@ __device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(count));
 }
 __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
-    for (int it = 0; it < kSpinLimit; ++it) {
+    // Bounded by wall time (two seconds of the global timer, looked at every 1024 polls), not by a poll count
+    // whose length would depend on the clock.
+    unsigned long long t0 = 0;
+    for (unsigned it = 0;; ++it) {
         unsigned done;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
@@ -80,8 +83,13 @@ __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
             "selp.u32 %0, 1, 0, p;\n\t}"
             : "=r"(done) : "r"(bar), "r"(parity) : "memory");
         if (done) return true;
+        if ((it & 1023u) == 1023u) {
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kWaitNs) return false;
+        }
     }
-    return false;
 }
 
 // Rank of column n among the markers of a row (markers are sorted by column).
@@ -309,7 +317,7 @@ int launch_gemm_tcgen05(const EptqLayer& L, const uint16_t* x, uint16_t* y, int 
     if (grid.y > 65535u) return EPTQ_ERR_SHAPE;
     if (L.quantizer == EPTQ_E8) gemm_tcgen05_kernel<EPTQ_E8><<<grid, kGemmThreads, 0, stream>>>(a);
     else gemm_tcgen05_kernel<EPTQ_E8D4><<<grid, kGemmThreads, 0, stream>>>(a);
-    g_launches.fetch_add(1, std::memory_order_relaxed);
+    count_launch(EPTQ_KERNEL_GEMM);
     return cudaPeekAtLastError() == cudaSuccess ? EPTQ_OK : EPTQ_ERR_LAUNCH;
 }
 

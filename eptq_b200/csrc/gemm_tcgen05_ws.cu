@@ -48,7 +48,7 @@ constexpr unsigned kB_LBO = 144;                        // bytes between core ma
 constexpr unsigned kB_SBO = (kChunkK / 8) * kB_LBO;     // bytes between 8-row groups (1152)
 constexpr int kProducerWarps = 16;                      // reconstruction is latency-bound: many warps
 constexpr int kWsThreads = (2 + kProducerWarps) * 32;   // 576
-constexpr int kSpinLimit = 20000000;
+constexpr unsigned long long kWaitNs = 2000000000ull;     // limit of one mbarrier wait
 
 // Stages that fit in 227 KB next to the 8 KB table: 2 for 512x128 tiles (80 KB each), 3 for 256x256 (64 KB each).
 __host__ __device__ constexpr int ws_stage_bytes(int tm, int nt) { return tm * kATileBytes + (nt / 8) * static_cast<int>(kB_SBO); }
@@ -68,7 +68,10 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(unsigned bar, unsigned byt
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
-    for (int it = 0; it < kSpinLimit; ++it) {
+    // Bounded by wall time (two seconds of the global timer, looked at every 1024 polls), not by a poll count
+    // whose length would depend on the clock.
+    unsigned long long t0 = 0;
+    for (unsigned it = 0;; ++it) {
         unsigned done;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
@@ -76,8 +79,13 @@ __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
             "selp.u32 %0, 1, 0, p;\n\t}"
             : "=r"(done) : "r"(bar), "r"(parity) : "memory");
         if (done) return true;
+        if ((it & 1023u) == 1023u) {
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kWaitNs) return false;
+        }
     }
-    return false;
 }
 
 // A tile: K-major, 128-byte swizzle (what the bulk-tensor load writes): 8-row groups 1024 B apart.
@@ -412,7 +420,7 @@ int launch_ws(const CUtensorMap& tmap, const GemmWsArgs& a, dim3 grid, cudaStrea
         attr_done[dev] = true;
     }
     gemm_tcgen05_ws_kernel<KIND, TM, NT><<<grid, kWsThreads, ws_smem_bytes(TM, NT), stream>>>(tmap, a);
-    g_launches.fetch_add(1, std::memory_order_relaxed);
+    count_launch(EPTQ_KERNEL_GEMM);
     return cudaPeekAtLastError() == cudaSuccess ? EPTQ_OK : EPTQ_ERR_LAUNCH;
 }
 

@@ -189,6 +189,12 @@ __global__ void __launch_bounds__(kGroupThreads, 1) gemv_group_kernel(const __gr
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const unsigned base = smem_addr(smem_raw);                 // 0x400 on sm_100: the first KB is reserved
+    // The table address is a constant of the lookup arithmetic: if dynamic shared memory does not start where
+    // this layout assumes, refuse (status word of the scratch) instead of reading outside the allocation.
+    if (base != 0x400u) {
+        if (threadIdx.x == 0) atomicExch(reinterpret_cast<int*>(p.counters) + (kMaxCounters - 1), static_cast<int>(EPTQ_ERR_LAUNCH));
+        return;
+    }
     unsigned char* tab = smem_raw + (kTableAddr - base);       // generic pointer to shared address 0x10000
 
     asm volatile("griddepcontrol.launch_dependents;");
@@ -660,7 +666,7 @@ int launch_gemv_group_pass(const EptqLayer* layers, int n, const EptqFusion* fus
     const cudaError_t err =
         e8 ? (B == 1 ? cudaLaunchKernelEx(&cfg, gemv_group_kernel<EPTQ_E8, 1>, a) : cudaLaunchKernelEx(&cfg, gemv_group_kernel<EPTQ_E8, 2>, a))
            : (B == 1 ? cudaLaunchKernelEx(&cfg, gemv_group_kernel<EPTQ_E8D4, 1>, a) : cudaLaunchKernelEx(&cfg, gemv_group_kernel<EPTQ_E8D4, 2>, a));
-    g_launches.fetch_add(1, std::memory_order_relaxed);
+    count_launch(EPTQ_KERNEL_GEMV_GROUP);
     return err == cudaSuccess ? EPTQ_OK : EPTQ_ERR_LAUNCH;
 }
 

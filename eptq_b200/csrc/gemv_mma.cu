@@ -563,7 +563,7 @@ int launch_variant(const MmaGemvArgs& a, dim3 grid, cudaStream_t stream) {
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     const cudaError_t err = cudaLaunchKernelEx(&cfg, gemv_mma_d4_kernel<WC, NBP>, a);
-    g_launches.fetch_add(1, std::memory_order_relaxed);
+    count_launch(EPTQ_KERNEL_GEMV_MMA);
     return err == cudaSuccess ? EPTQ_OK : EPTQ_ERR_LAUNCH;
 }
 

@@ -235,7 +235,7 @@ int launch_simt_kind(const GemvArgs& a, int bt, dim3 grid, cudaStream_t stream) 
         case 2: gemv_simt_kernel<KIND, 2><<<grid, 256, 0, stream>>>(a); break;
         default: gemv_simt_kernel<KIND, 4><<<grid, 256, 0, stream>>>(a); break;
     }
-    g_launches.fetch_add(1, std::memory_order_relaxed);
+    count_launch(EPTQ_KERNEL_GEMV_SIMT);
     return cudaPeekAtLastError() == cudaSuccess ? EPTQ_OK : EPTQ_ERR_LAUNCH;
 }
 

@@ -1095,7 +1095,7 @@ int launch_gemv_stream(const EptqLayer* layers, int n, const EptqFusion* fusions
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     const cudaError_t err = cudaLaunchKernelEx(&cfg, gemv_stream_kernel, a);
-    g_launches.fetch_add(1, std::memory_order_relaxed);
+    count_launch(EPTQ_KERNEL_GEMV_STREAM);
     return err == cudaSuccess ? EPTQ_OK : EPTQ_ERR_LAUNCH;
 }
 

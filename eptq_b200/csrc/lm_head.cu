@@ -202,6 +202,6 @@ extern "C" int eptq_lm_head_argmax(const uint16_t* W, const uint16_t* x, const u
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     const cudaError_t err = cudaLaunchKernelEx(&cfg, lm_head_argmax_kernel, a);
-    g_launches.fetch_add(1, std::memory_order_relaxed);
+    count_launch(EPTQ_KERNEL_OTHER);
     return err == cudaSuccess ? EPTQ_OK : EPTQ_ERR_LAUNCH;
 }

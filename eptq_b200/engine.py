@@ -346,10 +346,22 @@ class LlamaDecodeEngine:
             raise ValueError("prompt does not fit the engine's batch / cache length")
         pos = torch.arange(T, device=self.device)
         logits = self._fwd(ids, pos)
+        self._check_device_status("prefill")
         first = logits[:, -1].argmax(dim=-1)
         self.token.copy_(first[:, None])
         self.position.fill_(T)
         return first
+
+    def _check_device_status(self, what: str) -> None:
+        """A kernel whose bounded device-side wait ran out (prefill GEMM, streaming or chained GEMV) leaves a code
+        in the status word of the scratch it used: read it (one stream synchronisation) and raise."""
+        if self.device.type != "cuda":
+            return
+        from . import _lib
+        from .kernels import workspace_status_all
+        code = workspace_status_all(self.device)
+        if code != 0:
+            _lib.check(code, f"eptq_b200 {what} (device-side wait)")
 
     def _fwd(self, ids: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
         fused = ids.is_cuda and self.dtype == torch.float16
@@ -419,6 +431,7 @@ class LlamaDecodeEngine:
         torch.cuda.synchronize(self.device)
         dev_s = start.elapsed_time(stop) * 1e-3
         n = max(max_new_tokens - 1, 1) * self.batch
+        self._check_device_status("decode")
         return out, {"prefill_s": t1 - t0, "decode_s": dev_s, "tokens_per_s": n / max(dev_s, 1e-9),
                      "ms_per_token": 1e3 * dev_s / max(max_new_tokens - 1, 1)}
 

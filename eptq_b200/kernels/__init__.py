@@ -23,7 +23,7 @@ import torch
 from .. import _lib
 
 __all__ = ["e8_forward", "e8d4_forward", "linear_forward", "linear_forward_group", "linear_forward_chain",
-           "dequantize_layer", "workspace_for", "workspace_status"]
+           "dequantize_layer", "workspace_for", "workspace_status", "workspace_status_all"]
 
 _workspaces: Dict[Tuple[int, int], torch.Tensor] = {}
 
@@ -82,9 +82,12 @@ def _forward_impl(kind: str, Q, table, g, h, x, O_vals, O_col, O_row_ptr, bias) 
     ws = workspace_for(x.device, nbytes)
     with torch.cuda.device(x.device):
         if kind == "e8_lattice":
-            st = lib.eptq_e8_forward(Q.data_ptr(), table.data_ptr(), table.shape[0], g.data_ptr(), h.data_ptr(),
-                                     x.data_ptr(), _ptr(O_vals), _ptr(O_col), O_row_ptr.data_ptr(), _ptr(bias),
-                                     y.data_ptr(), M, N, B, ws.data_ptr(), ws.numel(), _stream(x.device))
+            # through the descriptor, so that the packed table (made once per codebook tensor) reaches the
+            # persistent kernel; eptq_e8_forward itself only knows the fp16 table
+            desc = _make_desc("e8_lattice", Q, None, table, g, h, O_vals, O_col, O_row_ptr,
+                              None if bias is None or bias.numel() == 0 else bias, None, 0)
+            st = lib.eptq_linear_forward(C.byref(desc), x.data_ptr(), y.data_ptr(), B,
+                                         ws.data_ptr(), ws.numel(), _stream(x.device))
         else:
             if table.numel() != 2048:
                 raise RuntimeError("E8-D4 codes must hold 512 x 4 values")
@@ -126,6 +129,18 @@ def _(Q, codes, g, h, x, O_vals, O_col, O_row_ptr, bias):
 
 
 _table8_cache: Dict[tuple, Optional[Tuple[torch.Tensor, float]]] = {}
+# Derived values are cached by the address of their source tensor; the cache keeps that tensor alive, so that the
+# allocator cannot hand the address to another tensor while an entry is valid.  clear_derived_caches() drops all.
+_cache_sources: Dict[tuple, torch.Tensor] = {}
+
+
+def clear_derived_caches() -> None:
+    """Forget every table / scale derived from a tensor (int8 and packed tables, max |h|)."""
+    _table8_cache.clear()
+    _packed_cache.clear()
+    _absmax_cache.clear()
+    _cache_sources.clear()
+
 
 
 def d4_table8(table: torch.Tensor):
@@ -148,6 +163,7 @@ def d4_table8(table: torch.Tensor):
     if len(_table8_cache) > 64:
         _table8_cache.clear()
     _table8_cache[key] = res
+    _cache_sources[("t8",) + key] = table          # the keyed tensor stays alive: its address cannot be reused
     return res
 
 
@@ -197,6 +213,7 @@ def e8_packed(table: torch.Tensor) -> Optional[Tuple[torch.Tensor, float]]:
         if len(_packed_cache) > 64:
             _packed_cache.clear()
         _packed_cache[key] = pack_e8_table(table)
+        _cache_sources[("packed",) + key] = table
     return _packed_cache[key]
 
 
@@ -211,8 +228,11 @@ def h_absmax(h: torch.Tensor) -> float:
     if v is None:
         v = float(h.abs().max().item()) if h.numel() else 0.0
         if len(_absmax_cache) > 4096:
+            for k in [k for k in _cache_sources if k[0] == "absmax"]:
+                del _cache_sources[k]
             _absmax_cache.clear()
         _absmax_cache[key] = v
+        _cache_sources[("absmax",) + key] = h
     return v
 
 
@@ -285,7 +305,7 @@ def linear_forward(x: torch.Tensor, Q: torch.Tensor, table16: torch.Tensor, tabl
     if B == 0:
         return y
     desc = _make_desc(quantizer_type, Q, table32, table16, g, h, O_vals, O_col, O_row_ptr, bias, S_group, qb_size)
-    ws = workspace_for(x.device, lib.eptq_workspace_bytes(M, N, B))
+    ws = workspace_for(x.device, lib.eptq_layer_workspace_bytes(C.byref(desc), B))
     with torch.cuda.device(x.device):
         st = lib.eptq_linear_forward(C.byref(desc), x.data_ptr(), y.data_ptr(), B,
                                      ws.data_ptr(), ws.numel(), _stream(x.device))
@@ -365,6 +385,19 @@ def workspace_status(workspace: Optional[torch.Tensor] = None, device=None) -> i
     with torch.cuda.device(dev):
         _lib.check(lib.eptq_workspace_status(ws.data_ptr(), C.addressof(out), _stream(dev)), "eptq workspace status")
     return int(out.value)
+
+
+def workspace_status_all(device) -> int:
+    """workspace_status of every scratch buffer this module made on `device` (one per stream that ran the
+    kernels, e.g. the stream a CUDA graph was captured on): the first non-zero code, or 0."""
+    dev = torch.device(device)
+    index = dev.index if dev.index is not None else torch.cuda.current_device()
+    first = 0
+    for (d, _stream_id), ws in list(_workspaces.items()):
+        if d == index:
+            code = workspace_status(ws)
+            first = first or code
+    return first
 
 
 def dequantize_layer(Q: torch.Tensor, table32: torch.Tensor, g: torch.Tensor, h: torch.Tensor,

@@ -42,7 +42,9 @@ def _shared_table(codebook: torch.Tensor, dtype: torch.dtype, quantizer_type: st
     tab = tab.reshape(512, 4) if quantizer_type == "e8_d4" else tab
     tab = tab.contiguous()
     if len(_table_cache) > 64:
+        from . import clear_derived_caches
         _table_cache.clear()
+        clear_derived_caches()                 # their entries are keyed by the tensors dropped here
     _table_cache[key] = tab
     return tab
 
@@ -179,7 +181,7 @@ class EPTQLinear(nn.Module):
         y = torch.empty((B, self.out_features), dtype=torch.float16, device=x2.device)
         if B == 0:
             return y
-        ws = workspace_for(x2.device, lib.eptq_workspace_bytes(self.Q.shape[0], self.Q.shape[1], B))
+        ws = workspace_for(x2.device, lib.eptq_layer_workspace_bytes(C.byref(d), B))
         if x2.device.index is not None and x2.device.index != torch.cuda.current_device():
             with torch.cuda.device(x2.device):
                 st = lib.eptq_linear_forward(C.byref(self._desc), x2.data_ptr(), y.data_ptr(), B, ws.data_ptr(),

@@ -120,6 +120,10 @@ const char* eptq_strerror(int status);
 /* Number of kernels this library has launched in the calling process since it
  * was loaded (all entry points, all streams).  For launch accounting only. */
 uint64_t eptq_launch_count(void);
+/* The same per kernel family, to tell which kernel a call reached. */
+enum { EPTQ_KERNEL_GEMV_STREAM = 0, EPTQ_KERNEL_GEMV_GROUP = 1, EPTQ_KERNEL_GEMV_MMA = 2, EPTQ_KERNEL_GEMV_SIMT = 3,
+       EPTQ_KERNEL_GEMM = 4, EPTQ_KERNEL_OTHER = 5, EPTQ_KERNEL_COUNT = 6 };
+uint64_t eptq_kernel_launch_count(int kernel);
 
 /*
  * Host-side, no GPU involved: express an E8-D4 table (512 x 4 fp32, already
@@ -141,6 +145,9 @@ int eptq_prepare_d4_table8(const float* table, uint8_t* out, float* scale);
  * read.  Calls that may overlap on the GPU need separate scratch.
  */
 size_t eptq_workspace_bytes(int M, int N, int B);
+/* The same from the layer itself: smaller for prefill-sized B when the tensor-core GEMM takes the layer
+ * (it needs the first 1 MiB only), eptq_workspace_bytes(M, N, B) otherwise. */
+size_t eptq_layer_workspace_bytes(const EptqLayer* layer, int B);
 
 /*
  * Fused dequantise + matrix-vector product for decode, the replacement of
@@ -169,6 +176,17 @@ int eptq_e8d4_forward(const int16_t* Q, const uint16_t* codes,
                       const int32_t* O_row_ptr, const uint16_t* bias,
                       uint16_t* y, int M, int N, int B,
                       void* workspace, size_t workspace_bytes, void* stream);
+/*
+ * At batch 1 eptq_e8d4_forward runs the streaming kernel when `codes` is a multiple of the D4 lattice.  The
+ * library finds that out the first time it sees a `codes` pointer outside a stream capture: it copies the
+ * 4 KB table to the host (this first call synchronises) and remembers the answer for the pointer.  Make that
+ * first call before capturing a graph; if the table behind a pointer is replaced, call
+ * eptq_forget_codebook(pointer) (NULL forgets all).  eptq_linear_forward with table8_scale set needs none of
+ * this and also takes the critical-block unit lists.  eptq_e8_forward has no such shortcut (its packed table
+ * is 256 KB of device memory, which this library does not allocate): use eptq_linear_forward with
+ * table_packed for E8 layers.
+ */
+void eptq_forget_codebook(const void* codes);
 
 /*
  * Layer forward from the full descriptor: y (B, 8M) fp16 = x (B, N) fp16

@@ -1,15 +1,38 @@
 """Fused prologue / epilogues of the group GEMV (eptq_linear_forward_group_fused) against the same
-work done by separate calls."""
+work done by separate calls, and against an fp32 PyTorch statement on oracle-reconstructed weights."""
+import numpy as np
 import pytest
 import torch
 
+import oracle
+from tests.util import qld_arrays
+
 pytestmark = pytest.mark.gpu
+_ORACLE_W = {}
 
 
 def _layer(out_f, in_f, seed, table):
     from eptq_b200.kernels.linear import EPTQLinear
     from eptq_b200.synthetic import make_layer
-    return EPTQLinear.from_quantized_data(make_layer(out_f, in_f, seed=seed, device="cuda"), table, "e8_d4")
+    qd = make_layer(out_f, in_f, seed=seed, device="cpu")
+    lin = EPTQLinear.from_quantized_data(qd, _cpu_table(table), "e8_d4").cuda()
+    _ORACLE_W[id(lin)] = torch.from_numpy(oracle.dequantize_layer(qld_arrays(qd), oracle.d4_table(1.75)).astype(np.float32)).cuda()
+    return lin
+
+
+_CPU_TABLE = {}
+
+
+def _cpu_table(table):
+    """One CPU copy of the table for all layers of this module: layers of one launch must share a codebook."""
+    if "t" not in _CPU_TABLE:
+        _CPU_TABLE["t"] = table.cpu()
+    return _CPU_TABLE["t"]
+
+
+def _oracle_w(lin):
+    """fp32 copy of the fp16 weight the reference's dequantize_layer gives for this layer."""
+    return _ORACLE_W[id(lin)]
 
 
 @pytest.fixture(scope="module")
@@ -50,6 +73,11 @@ def test_fused_rmsnorm_and_residual(table, B):
     for _ in range(2):
         y0, y1 = linear_forward_group(descs, [x, x], [512, 256], fusions=fz)
     assert _close(y0, want0) and _close(y1, want1)
+    # the same in fp32 PyTorch on the oracle's weights: LlamaRMSNorm (round, then weight), fp32 matmul
+    xf = x.float()
+    hn32 = (w.float() * (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5)).half().float()).half().float()
+    assert _close(y0, (res.float() + (hn32 @ _oracle_w(lins[0]).T).half().float()).half())
+    assert _close(y1, (hn32 @ _oracle_w(lins[1]).T).half())
     # in place: the residual stream is the output
     stream = res.clone()
     f = _lib.EptqFusion()
@@ -85,4 +113,17 @@ def test_fused_rope_and_cache(table, B):
                               [nh * hd, 0, 0], fusions=fz, ys=[None, kc2, vc2])[0]
     assert _close(q2, q, 3e-3)
     assert _close(kc2, kc, 3e-3) and _close(vc2, vc, 3e-3)
+    # against fp32 PyTorch on the oracle's weights: rotary embedding with fp16 cos/sin, pairs (i, i + 64)
+    ang = float(pos0) * inv_freq
+    cos = torch.cat((ang.cos(), ang.cos())).half().float()
+    sin = torch.cat((ang.sin(), ang.sin())).half().float()
+
+    def rot(t, heads):
+        t = t.float().reshape(B, heads, hd)
+        half = torch.cat((-t[..., hd // 2:], t[..., :hd // 2]), dim=-1)
+        return (t * cos + half * sin).reshape(B, heads * hd)
+    xq = x.float()
+    assert _close(q2, rot((xq @ _oracle_w(q_l).T).half(), nh), 3e-3)
+    assert _close(kc2[:, :, pos0].reshape(B, -1), rot((xq @ _oracle_w(k_l).T).half(), nkv), 3e-3)
+    assert _close(vc2[:, :, pos0].reshape(B, -1), (xq @ _oracle_w(v_l).T).half(), 3e-3)
     assert float(kc2[:, :, :pos0].abs().max()) == 0 and float(kc2[:, :, pos0 + 1:].abs().max()) == 0

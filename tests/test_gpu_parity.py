@@ -182,3 +182,43 @@ def test_launch_counter_moves():
     lin(make_activations(1, 256).to(DEV))
     torch.cuda.synchronize()
     assert _lib.launch_count() == before + 1
+
+
+def test_reference_signature_entry_reaches_streaming_kernel():
+    """eptq_e8d4_forward takes exactly the reference's arguments (csrc/eptq_kernels.h:31-41); at batch 1 on a
+    lattice table it must run the streaming kernel, not a side path, and match the oracle.  The Python
+    e8_forward op must reach the persistent E8 kernel likewise."""
+    import ctypes as C
+    import oracle
+    from eptq_b200 import _lib
+    from eptq_b200.kernels import e8_forward, workspace_for
+    from eptq_b200.kernels.linear import EPTQLinear
+    from eptq_b200.synthetic import make_activations, make_layer
+    lib = _lib.load()
+    qd = make_layer(4096, 4096, seed=77)
+    lin = EPTQLinear.from_quantized_data(qd, torch.from_numpy(oracle.d4_table(1.75)), "e8_d4").cuda()
+    x = make_activations(1, 4096, seed=3).cuda()
+    y = torch.empty(1, 4096, dtype=torch.float16, device="cuda")
+    ws = workspace_for(x.device, lib.eptq_workspace_bytes(512, 4096, 1))
+    lib.eptq_forget_codebook(None)
+    before = _lib.kernel_launch_count(_lib.KERNEL_GEMV_STREAM)
+    st = lib.eptq_e8d4_forward(lin.Q.data_ptr(), lin._codebook.data_ptr(), lin.g.data_ptr(), lin.h.data_ptr(),
+                               x.data_ptr(), lin.O_vals.data_ptr(), lin.O_col.data_ptr(), lin.O_row_ptr.data_ptr(),
+                               None, y.data_ptr(), 512, 4096, 1, ws.data_ptr(), ws.numel(),
+                               torch.cuda.current_stream().cuda_stream)
+    assert st == 0
+    torch.cuda.synchronize()
+    assert _lib.kernel_launch_count(_lib.KERNEL_GEMV_STREAM) == before + 1
+    W16 = oracle.dequantize_layer(util.qld_arrays(qd), oracle.d4_table(1.75))
+    assert util.max_rel_err(y.float().cpu().numpy(), oracle.linear_reference(x.cpu().numpy(), W16, None)) <= util.REL_TOL
+    # E8 through the Python op of the reference's signature
+    qd8 = make_layer(4096, 4096, seed=78)
+    tab8 = torch.from_numpy(oracle.e8_table(1.6))
+    lin8 = EPTQLinear.from_quantized_data(qd8, tab8, "e8_lattice").cuda()
+    before = _lib.kernel_launch_count(_lib.KERNEL_GEMV_GROUP)
+    y8 = e8_forward(lin8.Q, lin8._codebook, lin8.g, lin8.h, x, lin8.O_vals, lin8.O_col, lin8.O_row_ptr,
+                    torch.empty(0, dtype=torch.float16, device="cuda"))
+    torch.cuda.synchronize()
+    assert _lib.kernel_launch_count(_lib.KERNEL_GEMV_GROUP) == before + 1
+    W8 = oracle.dequantize_layer(util.qld_arrays(qd8), oracle.e8_table(1.6))
+    assert util.max_rel_err(y8.float().cpu().numpy(), oracle.linear_reference(x.cpu().numpy(), W8, None)) <= util.REL_TOL

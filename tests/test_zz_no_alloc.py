@@ -18,18 +18,21 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
-def _layer(out_f, in_f, seed):
+def _layer(out_f, in_f, seed, with_oracle=False):
     qd = make_layer(out_f, in_f, seed=seed, outlier_frac=0.004, bias=True)
     lin = EPTQLinear.from_quantized_data(qd, torch.from_numpy(oracle.d4_table(1.75)), "e8_d4").to(DEV)
     desc = _make_desc(lin.quantizer_type, lin.Q, lin._codebook32, lin._codebook, lin.g, lin.h, lin.O_vals,
                       lin.O_col, lin.O_row_ptr, lin.bias, lin.S_group, lin.qb_size)
+    if with_oracle:
+        W16 = oracle.dequantize_layer(util.qld_arrays(qd), oracle.d4_table(1.75))
+        return lin, desc, (W16, qd.bias.numpy())
     return lin, desc
 
 
 @pytest.mark.parametrize("out_f,in_f,batch", [(4096, 4096, 1), (1024, 2752, 3), (11008, 4096, 2)])
 def test_static_scratch_matches_regular_entry_point(out_f, in_f, batch):
     lib = _lib.load()
-    lin, desc = _layer(out_f, in_f, seed=out_f + batch)
+    lin, desc, (W16, bias) = _layer(out_f, in_f, seed=out_f + batch, with_oracle=True)
     stream = torch.cuda.current_stream().cuda_stream
     ws = torch.zeros(lib.eptq_workspace_bytes(out_f // 8, in_f, batch), dtype=torch.uint8, device=DEV)
     for call in range(2):                                   # two calls in a row share the built-in scratch
@@ -45,6 +48,9 @@ def test_static_scratch_matches_regular_entry_point(out_f, in_f, batch):
         # output tolerance of the suite, max|a-b| / max|b| <= 2e-3
         err = float((y_new.float() - y_ref.float()).abs().max() / y_ref.float().abs().max())
         assert err <= util.REL_TOL, err
+        # and against the oracle: fp32 product with the reconstructed fp16 weight
+        want = oracle.linear_reference(x.cpu().numpy(), W16, bias)
+        assert util.max_rel_err(y_new.float().cpu().numpy(), want) <= util.REL_TOL
 
 
 def test_static_scratch_limits():
