@@ -65,7 +65,8 @@ constexpr unsigned kMail = 0x4A0u;                                  // 2 x {-, -
 constexpr unsigned kPrep = 0x4C0u;                                  // 8: the digit planes of a layer are ready
 constexpr unsigned kMisc = 0x500u;                                  // 128 floats of reductions and results
 constexpr unsigned kRed = 0x800u;                                   // 2 x [digit][64 rows][8] int32
-constexpr unsigned kCorr = 0x2800u;                                 // 2 x [64 rows][8] float: critical-block corrections
+constexpr unsigned kCorr = 0x2800u;                                 // 2 x [64 rows][8] int32, 1/16 units: critical-block corrections
+constexpr float kCorrStep = 1.f / 16.f;                               // fixed-point step of the correction sums
 constexpr unsigned kPlane = 0x3800u;                                // low digits, then high digits
 constexpr unsigned kTable = 0x10000u;
 constexpr unsigned kRing = 0x20000u;
@@ -78,26 +79,37 @@ struct StreamArgs {
     alignas(64) CUtensorMap maps[kMaxGroupLayers];
     float unit;                                   // table value = integer coordinate * unit
     float inv_unit;
-    unsigned zero;                                // 0: addend that keeps q * 128 + zero a multiply-add (FMA pipe, not the shifter)
+    unsigned zero;                                // 0: addend of the index multiplications
+    unsigned mul[2];                              // 128 and 1 << 16 as run-time values: the shifts of the index words
+                                                  // stay multiplications (FMA pipe) instead of ALU-pipe shifts
     int use_lists;                                // every layer brings its critical blocks as unit lists
     int* status;
     unsigned long long wait_ns;                   // limit of one mbarrier wait
 };
 
 // Phase time stamps for latency studies: compiled in only with -DEPTQ_STREAM_TRACE (never in the shipped
-// library).  Slot k of block b is g_stream_trace[b * 8 + k], nanoseconds of the global timer.
+// library).  Slot k of block b is g_stream_trace[b * 64 + k] (k = 8 * phase + event), nanoseconds of the global timer.
 #ifdef EPTQ_STREAM_TRACE
 __device__ unsigned long long* g_stream_trace = nullptr;
 __device__ __forceinline__ void stream_trace(int slot) {
     if ((threadIdx.x & 31) == 0 && g_stream_trace != nullptr) {
         unsigned long long t;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        g_stream_trace[blockIdx.x * 8 + slot] = t;
+        g_stream_trace[blockIdx.x * 64 + slot] = t;
     }
 }
 #define EPTQ_STRACE(slot, cond) do { if (cond) stream_trace(slot); } while (0)
+__device__ __forceinline__ void stream_trace_max(int slot) {
+    if ((threadIdx.x & 31) == 0 && g_stream_trace != nullptr) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        atomicMax(g_stream_trace + blockIdx.x * 64 + slot, t);
+    }
+}
+#define EPTQ_STRACE_MAX(slot) stream_trace_max(slot)
 #else
 #define EPTQ_STRACE(slot, cond) do { } while (0)
+#define EPTQ_STRACE_MAX(slot) do { } while (0)
 #endif
 
 __device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
@@ -468,7 +480,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
         return;
     }
     asm volatile("griddepcontrol.launch_dependents;");
-    EPTQ_STRACE(0, warp == 0);
+    EPTQ_STRACE(56, warp == 0);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -519,7 +531,6 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
                     }
                 }
             }
-            EPTQ_STRACE(7, true);
             return;
         }
 
@@ -535,10 +546,19 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
             while (walk.next(p, sg)) {
                 const GroupLayer& L = p.L[sg.l];
                 const unsigned b = k & 1u;
+                if (P.use_lists) {
+                    // Whichever block completes this 64-row tile finalizes it; its epilogue operands (1 KB each of
+                    // output scale, bias and residual) are asked into L2 now, while the segment is still streaming.
+                    const size_t line = static_cast<size_t>(sg.rt) * 512 + (lane & 7) * 64;      // halves
+                    const __half* src = lane < 8 ? L.g : lane < 16 ? L.bias : lane < 24 && L.y_op == EPTQ_Y_ADD_RESIDUAL ? L.residual : nullptr;
+                    if (src != nullptr && line < static_cast<size_t>(L.M) * 8)
+                        asm volatile("prefetch.global.L2 [%0];" :: "l"(src + line));
+                }
                 if (!mbar_wait(kRedFull + 8 * b, (k >> 1) & 1u, P.wait_ns)) {
                     if (lane == 0) atomicExch(P.status, EPTQ_ERR_TIMEOUT);
                     break;
                 }
+                EPTQ_STRACE(8 * L.phase + 5, true);
                 const float scale = __uint_as_float(lds32(kMail + 16 * b + 12));
                 if (lane == 0) misc[48] = __uint_as_float(lds32(kMail + 16 * b + 8));       // this layer's RMSNorm factor
                 const unsigned buf = kRed + b * 4096;
@@ -556,7 +576,8 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
                     cr[j] = make_float4(0.f, 0.f, 0.f, 0.f);
                     if (P.use_lists) {
                         const uint4 c = lds128(kCorr + b * 2048 + (j * 128 + lane * 4) * 4);
-                        cr[j] = make_float4(__uint_as_float(c.x), __uint_as_float(c.y), __uint_as_float(c.z), __uint_as_float(c.w));
+                        cr[j] = make_float4(static_cast<float>(static_cast<int>(c.x)) * kCorrStep, static_cast<float>(static_cast<int>(c.y)) * kCorrStep,
+                                            static_cast<float>(static_cast<int>(c.z)) * kCorrStep, static_cast<float>(static_cast<int>(c.w)) * kCorrStep);
                     }
                 }
 #pragma unroll
@@ -588,7 +609,8 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
                         asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], %2;"
                                      : "=r"(old) : "l"(p.counters + L.tile0 + sg.rt * 4), "r"(weight) : "memory");
                     old = __shfl_sync(0xffffffffu, old, 0);
-                    if (old + weight == static_cast<unsigned>(L.cc128)) finalize_tile64(p, L, sg.rt, lane, inv_rms);
+                    EPTQ_STRACE(8 * L.phase + 6, true);
+                    if (old + weight == static_cast<unsigned>(L.cc128)) { finalize_tile64(p, L, sg.rt, lane, inv_rms); EPTQ_STRACE(8 * L.phase + 7, true); }
                 } else {
                     // one round trip for the four arrivals; with the CSR corrections a 16-row tile is complete at
                     // cc128 units + 4 correction quarters
@@ -606,7 +628,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
                 ++k;
             }
             launch_exit(p, lane);
-            EPTQ_STRACE(5, true);
+            EPTQ_STRACE(57, true);
             return;
         }
 
@@ -622,23 +644,35 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
             // warps take alternate entries, read the activation digits the consumers prepared and add
             // (O - marker code) / unit * digits to the segment's correction tile, in step with the flushes.
             SegmentWalk walk;
-            Segment sg;
+            Segment sg, nxt;
             unsigned k = 0, n_prep = 0;
             bool ok = true;
             const int me = (warp - kFinalizerWarp - 1) * 32 + lane;            // 0..63
-            while (walk.next(p, sg)) {
+            constexpr int kAhead = 4;                                           // entries per lane in flight
+            // The entry range of a segment is read one segment ahead, and its first 256 entries before any wait:
+            // a short segment's corrections are then one memory round trip behind its start, not three.
+            auto range_of = [&](const Segment& g, int& a, int& b) {
+                const GroupLayer& G = p.L[g.l];
+                const int u0 = g.rt * G.cc128 + g.cc;
+                a = __ldg(G.crit_ptr + u0);
+                b = __ldg(G.crit_ptr + u0 + g.n);
+            };
+            bool have = walk.next(p, sg);
+            int e0 = 0, e1 = 0;
+            if (have) range_of(sg, e0, e1);
+            while (have) {
                 const GroupLayer& L = p.L[sg.l];
-                const int u0 = sg.rt * L.cc128 + sg.cc;
-                const int e0 = __ldg(L.crit_ptr + u0), e1 = __ldg(L.crit_ptr + u0 + sg.n);
-                // first entries of this lane: loaded before any wait
-                unsigned pos[2];
-                uint4 ov[2];
+                unsigned pos[kAhead];
+                uint4 ov[kAhead];
 #pragma unroll
-                for (int j = 0; j < 2; ++j) {
+                for (int j = 0; j < kAhead; ++j) {
                     const int e = e0 + me + 64 * j;
                     pos[j] = 0u; ov[j] = make_uint4(0, 0, 0, 0);
                     if (e < e1) { pos[j] = __ldg(L.crit_pos + e); ov[j] = ldg128(L.crit_O + static_cast<size_t>(e) * 8); }
                 }
+                const bool have_next = walk.next(p, nxt);
+                int n0 = 0, n1 = 0;
+                if (have_next) range_of(nxt, n0, n1);
                 if (sg.new_layer) {
                     if (ok) ok = mbar_wait(kPrep, n_prep & 1u, P.wait_ns);
                     ++n_prep;
@@ -651,20 +685,36 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
                     short dl, dh;
                     asm volatile("ld.shared.s8 %0, [%1];" : "=h"(dl) : "r"(kPlane + col));
                     asm volatile("ld.shared.s8 %0, [%1];" : "=h"(dh) : "r"(kPlane + kStreamMaxN + col));
-                    const float f = static_cast<float>(static_cast<int>(dl) + 256 * static_cast<int>(dh)) * P.inv_unit;
+                    const float f = static_cast<float>(static_cast<int>(dl) + 256 * static_cast<int>(dh)) * (P.inv_unit / kCorrStep);
                     float o8[8];
                     unpack8(o, o8);
                     const float cm[4] = {c0, c1, c2, c3};
+                    // integer adds (shared-memory float adds are compare-and-swap loops); the sums of a row stay
+                    // below 2^31 by the precondition on the lists (sum |O - code| / unit < 3900 per row)
 #pragma unroll
                     for (int d = 0; d < 8; ++d)
-                        asm volatile("red.shared.add.f32 [%0], %1;" :: "r"(tile + (row * 8 + d) * 4), "f"((o8[d] - cm[d & 3]) * f) : "memory");
+                        asm volatile("red.shared.add.s32 [%0], %1;" :: "r"(tile + (row * 8 + d) * 4),
+                                     "r"(__float2int_rn((o8[d] - cm[d & 3]) * f)) : "memory");
                 };
+                EPTQ_STRACE_MAX(48 + 2 * L.phase);
 #pragma unroll
-                for (int j = 0; j < 2; ++j)
+                for (int j = 0; j < kAhead; ++j)
                     if (e0 + me + 64 * j < e1) apply(pos[j], ov[j]);
-                for (int e = e0 + me + 128; e < e1; e += 64) apply(__ldg(L.crit_pos + e), ldg128(L.crit_O + static_cast<size_t>(e) * 8));
+                EPTQ_STRACE_MAX(49 + 2 * L.phase);
+                for (int base = e0 + 64 * kAhead; base < e1; base += 64 * kAhead) {        // long segments: batches of 256
+#pragma unroll
+                    for (int j = 0; j < kAhead; ++j) {
+                        const int e = base + me + 64 * j;
+                        if (e < e1) { pos[j] = __ldg(L.crit_pos + e); ov[j] = ldg128(L.crit_O + static_cast<size_t>(e) * 8); }
+                    }
+#pragma unroll
+                    for (int j = 0; j < kAhead; ++j)
+                        if (base + me + 64 * j < e1) apply(pos[j], ov[j]);
+                }
                 mbar_arrive(kRedFull + 8 * b);
+                EPTQ_STRACE_MAX(32 + 4 * L.phase + 3);
                 ++k;
+                sg = nxt; e0 = n0; e1 = n1; have = have_next;
             }
             if (!ok && lane == 0) atomicExch(P.status, EPTQ_ERR_TIMEOUT);
             launch_exit(p, lane);
@@ -689,7 +739,6 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
             }
             if (!ok && lane == 0) atomicExch(P.status, EPTQ_ERR_TIMEOUT);
             launch_exit(p, lane);
-            EPTQ_STRACE(6, warp == kFinalizerWarp + 1);
             return;
         }
     }
@@ -716,7 +765,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
     // ldmatrix row address of this lane inside a stage: matrix lane>>3 = row group, row lane&7, 128-byte swizzle.
     const unsigned qm = kRing + static_cast<unsigned>(chunk64 * 8192 + ((lane >> 3) * 8 + (lane & 7)) * 128 + ((w8 ^ (lane & 7)) << 4));
 
-    const unsigned zr = P.zero;
+    const unsigned zr = P.zero, m128 = P.mul[0], m64k = P.mul[1];
     bool ok = true;
     bool dep_waited = false;
     unsigned flush_no = 0, prep_no = 0;
@@ -734,13 +783,15 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
             hr[k] = make_uint4(0, 0, 0, 0);
             if (c < L.N) hr[k] = ldg128(L.h + c);
         }
-        if (!dep_waited) { asm volatile("griddepcontrol.wait;" ::: "memory"); dep_waited = true; }
+        if (!dep_waited) { asm volatile("griddepcontrol.wait;" ::: "memory"); dep_waited = true; EPTQ_STRACE(58, warp == 0); }
         if (P.use_lists && flush_no > 0u && ok) {            // the correction warps still read the previous layer's planes
             const unsigned kf = flush_no - 1u;
             ok = mbar_wait(kRedFull + 8 * (kf & 1u), (kf >> 1) & 1u, P.wait_ns);
         }
         if (L.phase > 0) {                                   // input written by the previous phase of this launch
+            EPTQ_STRACE(8 * L.phase + 0, warp == 0);
             if (warp == 0 && ok && !wait_phase(p, L.phase, L.wait_tiles, P.wait_ns) && lane == 0) misc[47] = 1.f;
+            EPTQ_STRACE(8 * L.phase + 1, warp == 0);
             consumer_barrier();
             if (misc[47] != 0.f) ok = false;
         }
@@ -787,6 +838,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
                 ss = fmaf(xv[e], xv[e], ss);
             }
         }
+        EPTQ_STRACE(32 + 4 * L.phase + 0, warp == 0);
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
@@ -798,11 +850,17 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
         ++prep_no;
         if (lane == 0) { part[warp] = mx; part[16 + warp] = ss; }
         consumer_barrier();                                 // also: the previous layer's readers of the planes are done
-        float tot = 0.f;
-        mx = 0.f;
+        EPTQ_STRACE(32 + 4 * L.phase + 1, warp == 0);
+        // lanes 0..15 hold the warps' maxima, lanes 16..31 their sums of squares
+        float vmax = part[lane], vsum = vmax;
 #pragma unroll
-        for (int w = 0; w < kConsumerWarps; ++w) { mx = fmaxf(mx, part[w]); tot += part[16 + w]; }
-        const float S = mx > 0.f ? 32000.f / mx : 1.f;
+        for (int o = 8; o > 0; o >>= 1) {
+            vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, o));
+            vsum += __shfl_xor_sync(0xffffffffu, vsum, o);
+        }
+        mx = __shfl_sync(0xffffffffu, vmax, 0);
+        const float tot = __shfl_sync(0xffffffffu, vsum, 16);
+        const float S = mx > 0.f ? __fdividef(32000.f, mx) : 1.f;
         if (tid == 0) {                                      // read back by thread 0 at each flush of this layer
             misc[56] = L.x_op == EPTQ_X_RMSNORM ? rsqrtf(tot / static_cast<float>(L.N) + L.norm_eps) : 1.f;
             misc[57] = P.unit / S;
@@ -839,6 +897,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
             digits(c, v);
         }
         consumer_barrier();
+        EPTQ_STRACE(8 * L.phase + 2, warp == 0);
         if (P.use_lists) mbar_arrive(kPrep);                 // release: the planes are visible to the correction warps
     };
 
@@ -899,12 +958,15 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
 #pragma unroll
                 for (int r = 0; r < 4; ++r) {
                     const unsigned qq = q[4 * half + r];
-                    const unsigned qs = qq >> 16;
+                    // high index of the word: the upper half of the 64-bit product q * 2^16
+                    unsigned ta, tb;
+                    unsigned long long wide;
+                    asm("mul.wide.u32 %0, %1, %2;" : "=l"(wide) : "r"(qq), "r"(m64k));
+                    const unsigned qs = static_cast<unsigned>(wide >> 32);
+                    asm("mad.lo.u32 %0, %1, %2, %3;" : "=r"(ta) : "r"(qq), "r"(m128), "r"(zr));
+                    asm("mad.lo.u32 %0, %1, %2, %3;" : "=r"(tb) : "r"(qs), "r"(m128), "r"(zr));
                     const unsigned ia = (qq & 0xFF80u) | lane_tab;
                     const unsigned ib = (qs & 0xFF80u) | lane_tab;
-                    unsigned ta, tb;
-                    asm("mad.lo.u32 %0, %1, 128, %2;" : "=r"(ta) : "r"(qq), "r"(zr));
-                    asm("mad.lo.u32 %0, %1, 128, %2;" : "=r"(tb) : "r"(qs), "r"(zr));
                     a[r][0] = lds32(ia);
                     a[r][1] = lds32(bitsel(ta, ia, 0x3F80u));
                     a[r][2] = lds32(ib);
@@ -930,8 +992,10 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
 #pragma unroll
             for (int r = 0; r < 4; ++r) imma(acc[4 + r], a[r][0], a[r][1], a[r][2], a[r][3], b0, b1);
         }
-        if (i == n_units) EPTQ_STRACE(4, warp == 0);
+        EPTQ_STRACE(8 * p.L[sg.l].phase + 3, warp == 0);
         flush();
+        EPTQ_STRACE(8 * p.L[sg.l].phase + 4, warp == 0);
+        EPTQ_STRACE_MAX(32 + 4 * p.L[sg.l].phase + 2);
     }
     if (!ok && lane == 0) atomicExch(P.status, EPTQ_ERR_TIMEOUT);
 }
@@ -1069,6 +1133,7 @@ int launch_gemv_stream(const EptqLayer* layers, int n, const EptqFusion* fusions
     a.inv_unit = 1.0f / layers[0].table8_scale;
     a.status = reinterpret_cast<int*>(workspace) + (kMaxCounters - 1);
     a.zero = 0u;
+    a.mul[0] = 128u; a.mul[1] = 1u << 16;
     a.wait_ns = 2000000000ull;
 
     static bool attr_done[64] = {};            // guarded by args_mutex

@@ -236,14 +236,28 @@ def h_absmax(h: torch.Tensor) -> float:
     return v
 
 
-def critical_lists(O_vals: torch.Tensor, O_col: torch.Tensor, O_row_ptr: torch.Tensor, N: int):
+CRIT_ROW_LIMIT = 3900.0
+
+
+def critical_lists(O_vals: torch.Tensor, O_col: torch.Tensor, O_row_ptr: torch.Tensor, N: int,
+                   unit: Optional[float] = None, code_max: float = 0.0):
     """The critical blocks regrouped by the 64-row x 128-column unit of Q they fall into (fields crit_ptr,
     crit_pos, crit_O of struct EptqLayer), from the CSR side tables: (int32 (units+1), int32 (n) bit pattern of
-    uint32 (row % 64) << 16 | col, fp16 (n, 8))."""
+    uint32 (row % 64) << 16 | col, fp16 (n, 8)).
+
+    The streaming kernel sums the corrections of a row in 32-bit fixed point; with ``unit`` (the codebook's
+    coordinate step) given, a layer whose rows could exceed that range -- sum over a row's critical blocks of
+    (|O| + code_max) / unit >= CRIT_ROW_LIMIT in some dimension -- gets (None, None, None) and runs from the CSR
+    tables instead."""
     M = O_row_ptr.shape[0] - 1
     dev = O_col.device
     counts = (O_row_ptr[1:] - O_row_ptr[:-1]).to(torch.int64)
     rows = torch.repeat_interleave(torch.arange(M, device=dev), counts)
+    if unit is not None and rows.numel() > 0:
+        mag = (O_vals.reshape(-1, 8).float().abs() + code_max) / unit
+        per_row = torch.zeros(M, 8, device=dev).index_add_(0, rows, mag)
+        if float(per_row.max()) >= CRIT_ROW_LIMIT:
+            return None, None, None
     cols = O_col.to(torch.int64)
     cc = (N + 127) // 128
     units = ((M + 63) // 64) * cc

@@ -24,7 +24,7 @@ import torch.nn as nn
 import ctypes as C
 
 from .. import _lib
-from . import _make_desc, critical_lists, dequantize_layer, linear_forward, linear_forward_group, workspace_for
+from . import _make_desc, critical_lists, d4_table8, dequantize_layer, linear_forward, linear_forward_group, workspace_for
 
 MARKER = 32767     # int16 value that marks a critical block (index 65535 - 32768)
 
@@ -89,8 +89,11 @@ class EPTQLinear(nn.Module):
         self.qb_size = self.out_features // S_group.shape[0] if S_group is not None else 0
         # Critical blocks regrouped by 64 x 128 unit of Q for the streaming GEMV: derived like the CSR tables,
         # not part of the saved state.
-        crit = (critical_lists(self.O_vals, self.O_col, self.O_row_ptr, self.in_features)
-                if quantizer_type == "e8_d4" and S_group is None else (None, None, None))
+        crit = (None, None, None)
+        if quantizer_type == "e8_d4" and S_group is None:
+            t8 = d4_table8(codebook)                     # None for a warped codebook: no streaming kernel, no range to check
+            crit = critical_lists(self.O_vals, self.O_col, self.O_row_ptr, self.in_features,
+                                  unit=t8[1] if t8 is not None else None, code_max=float(codebook.abs().max()))
         for name, t in zip(("crit_ptr", "crit_pos", "crit_O"), crit):
             self.register_buffer(name, t, persistent=False)
 
