@@ -681,8 +681,8 @@ def run_gpu_arm(args):
                    "all_reduce_note": comm_note},
         "decode_tokens_per_s_linears_only": 1e3 / step_ms * B,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": (52379392 if (group == 7 and B == 1 and world == 1 and args.codebook == "e8d4") else None),
-                     "traffic_source": "dram read+write of one 7-linear launch, ncu capture in profiles/",
+                     "traffic": (52291840 if (group == 7 and B == 1 and world == 1 and args.codebook == "e8d4") else None),
+                     "traffic_source": "dram read+write of one 7-linear launch of gemv_stream_kernel, ncu capture summarised in profiles/gemv_stream_kernel_llama7b_layer_set.md",
                      "peak_kind": f"{peak_kind} copy bandwidth",
                      "per_launch_bytes": per_launch_bytes, "per_launch_us": per_launch_us},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,

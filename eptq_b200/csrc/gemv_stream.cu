@@ -1122,6 +1122,8 @@ int launch_gemv_stream(const EptqLayer* layers, int n, const EptqFusion* fusions
         }
         a.maps[i] = it->second;
     }
+    // the kernel cuts shares with 32-bit products units * blocks
+    if (units * n_sms >= (1ll << 32)) return EPTQ_ERR_UNSUPPORTED;
     // Every phase is split over all blocks; a phase with fewer units than blocks leaves some without work in it.
     const int blocks = chained ? n_sms : (units < n_sms ? static_cast<int>(units) : n_sms);
     if (!chained) a.g.phase_units[0] = static_cast<int>(units);

@@ -1,17 +1,23 @@
 """Decode engine for LLaMA-architecture models whose decoder linears are EPTQLinear modules.
 
 The reference decodes through the HuggingFace forward wrapped in torch.compile and CUDA graphs
-(bench_decode.py:35-83, 149).  Here the per-token step is written out once with static shapes --
-RMSNorm, one grouped launch for q/k/v, rotary embedding, append to a preallocated key/value cache,
-attention over the cache with a position mask, o projection, RMSNorm, one grouped launch for gate/up,
-SiLU*up, down projection, final norm, lm_head, greedy pick -- and captured into ONE CUDA graph that
-also advances the position and feeds the picked token back, so a decoded token costs one graph launch
-and no host work.  The same step runs eagerly for the prefill (many tokens: the linears then take the
-tensor-core GEMM path).
+(bench_decode.py:35-83, 149).  Here the per-token step is written out once with static shapes and
+captured into ONE CUDA graph that also advances the position and feeds the picked token back, so a
+decoded token costs one graph launch and no host work.  Three statements of the same step:
+
+* batch 1, one GPU, E8-D4: per decoder layer the attention kernel and ONE chained launch of the streaming
+  GEMV -- o (+ residual) -> gate/up (RMSNorm folded in) -> down (SiLU(gate)*up formed as it reads its input,
+  + residual) -> the next layer's q/k/v (RMSNorm folded in, rotary embedding and cache append in the
+  epilogue) -- then the final norm, lm_head and greedy pick in the library's own kernel;
+* batch <= 2 otherwise (E8, tensor parallel): the same work as separate grouped launches;
+* anything else, and the prefill: RMSNorm, grouped q/k/v, rotary embedding + cache append, attention, o,
+  RMSNorm, grouped gate/up, SiLU*up, down as separate kernels (many tokens: the linears then take the
+  tensor-core GEMM path).
 
 Tensor parallelism: with a process group, q/k/v/gate/up hold this rank's output rows (its attention
-heads) and o/down this rank's input columns; their partial outputs are all-reduced (NCCL, captured in
-the graph).  Embedding, norms and lm_head are replicated.
+heads) and o/down this rank's input columns.  Their partial outputs are summed by the push all-reduce
+kernel (peer stores, replayed inside the token's graph) when a `PushAllReduce` is given, by NCCL
+otherwise and for prefill-sized tensors.  Embedding, norms and lm_head are replicated.
 """
 from __future__ import annotations
 

@@ -78,7 +78,10 @@ enum { EPTQ_E8 = 0, EPTQ_E8D4 = 1 };
  *              uint32 (n_masked) = (row % 64) << 16 | col; crit_O fp16 (n_masked, 8) =
  *              O_vals in that order.  With it the streaming GEMV patches critical blocks
  *              in step with the index stream instead of walking the CSR; all three NULL
- *              otherwise.
+ *              otherwise.  The kernel sums a row's corrections in 32-bit fixed point:
+ *              pass the lists only if, for every Q row and each of the 8 dimensions, the
+ *              sum over the row's critical blocks of (|O| + max|code|) / table8_scale stays
+ *              below 3900 (the Python module checks this and falls back to the CSR tables).
  *   bias       fp16 (8*M) or NULL.
  *   S_group    fp16 (8*M/qb_size, N) group scales or NULL (then qb_size = 0).
  *              qb_size must be a multiple of 8.

@@ -1,4 +1,7 @@
-"""The tensor-core E8-D4 GEMV (batch 1) against the oracle and against the general kernel."""
+"""E8-D4 at batch 1 through EPTQLinear against the oracle, over shapes that land in each kernel behind it:
+the streaming kernel (N a multiple of 64), the group kernel (N a multiple of 32 only) and the general SIMT
+kernel (ragged N, tiny layers).  The per-layer tensor-core kernel of the static-scratch entry point has its
+own oracle comparison in test_zz_no_alloc.py."""
 import numpy as np
 import pytest
 import torch
@@ -35,7 +38,7 @@ def test_shapes(out_f, in_f, bias):
 
 @pytest.mark.parametrize("scale", [1e-4, 1e-2, 30.0, 200.0])
 def test_activation_magnitudes(scale):
-    """The per-block power-of-two scaling keeps precision whatever the magnitude of x."""
+    """The scaling of the activations (two int8 digits of x*h / max|x*h|) keeps precision whatever the magnitude of x."""
     qd = make_layer(1024, 2048, seed=3)
     x = (make_activations(1, 2048, seed=12).float() * scale).half()
     y = build(qd)(x.to(DEV)).float().cpu().numpy()
@@ -65,7 +68,7 @@ def test_marker_density(frac):
 @pytest.mark.parametrize("batch", [2, 3, 4])
 @pytest.mark.parametrize("out_f,in_f", [(4096, 4096), (264, 2752), (11008, 4096), (4096, 11008), (40, 96)])
 def test_small_batches(batch, out_f, in_f):
-    """Batches up to 4 ride on the same tensor-core kernel (two batch rows per MMA column set)."""
+    """Batches 2..4 run in the group kernel (two batch rows per pass)."""
     qd = make_layer(out_f, in_f, seed=out_f + in_f + batch, outlier_frac=0.004, bias=True)
     x = make_activations(batch, in_f, seed=21)
     x[batch - 1] *= 37.0                      # rows with very different magnitudes get their own scale
