@@ -29,6 +29,9 @@ bool gemm_supported(const EptqLayer& L, int T);
 int launch_gemm_tcgen05(const EptqLayer& L, const uint16_t* x, uint16_t* y, int T, int* status, cudaStream_t stream);
 bool gemm_ws_supported(const EptqLayer& L, const void* x, int T);
 int launch_gemm_tcgen05_ws(const EptqLayer& L, const uint16_t* x, uint16_t* y, int T, int* status, cudaStream_t stream);
+bool gemm_dense_supported(int T, int N, const void* x, const void* y, const void* bias);
+int launch_gemm_dense(const uint16_t* W16, const uint16_t* x, uint16_t* y, const uint16_t* bias, int T, int out, int N,
+                      int* status, cudaStream_t stream);
 bool group_gemv_supported(const EptqLayer* layers, int n, int B);
 size_t group_workspace_bytes(const EptqLayer* layers, int n, int B, int n_sms);
 int launch_gemv_group(const EptqLayer* layers, int n, const EptqFusion* fusions, const uint16_t* const* xs,
@@ -60,6 +63,11 @@ int check_layer_common(const EptqLayer* L) {
     return EPTQ_OK;
 }
 
+// Bytes of the reconstructed fp16 weight (8M x N) behind the first MiB of scratch.
+size_t dense_weight_bytes(int M, int N) {
+    return (static_cast<size_t>(8) * M * N * sizeof(uint16_t) + 255) & ~static_cast<size_t>(255);
+}
+
 int forward_checked(const EptqLayer& L, const uint16_t* x, uint16_t* y, int B,
                     void* workspace, size_t workspace_bytes, void* stream) {
     int st = check_layer_common(&L);
@@ -72,6 +80,13 @@ int forward_checked(const EptqLayer& L, const uint16_t* x, uint16_t* y, int B,
     if (B > kGemmMinBatch && gemm_supported(L, B) && aligned16(y) && (L.bias == nullptr || aligned16(L.bias)) &&
         workspace != nullptr && workspace_bytes >= kCounterBytes) {
         int* status = reinterpret_cast<int*>(workspace) + (kMaxCounters - 1);     // last counter word: never a tile
+        // Long prefill and a scratch buffer that holds the fp16 weight: reconstruct once, then a dense GEMM.
+        if (gemm_dense_supported(B, L.N, x, y, L.bias) && workspace_bytes >= kPartialOffset + dense_weight_bytes(L.M, L.N)) {
+            uint16_t* W16 = reinterpret_cast<uint16_t*>(reinterpret_cast<char*>(workspace) + kPartialOffset);
+            st = launch_dequant(L, W16, static_cast<cudaStream_t>(stream));
+            if (st != EPTQ_OK) return st;
+            return launch_gemm_dense(W16, x, y, L.bias, B, 8 * L.M, L.N, status, static_cast<cudaStream_t>(stream));
+        }
         if (gemm_ws_supported(L, x, B))
             return launch_gemm_tcgen05_ws(L, x, y, B, status, static_cast<cudaStream_t>(stream));
         return launch_gemm_tcgen05(L, x, y, B, status, static_cast<cudaStream_t>(stream));
@@ -171,13 +186,16 @@ size_t eptq_workspace_bytes(int M, int N, int B) {
         const size_t grp = group_workspace_bytes(&shape, 1, B, 0);
         if (grp > bytes) bytes = grp;
     }
+    if (B >= kDenseMinTokens && (N % 8) == 0 && kPartialOffset + dense_weight_bytes(M, N) > bytes)
+        bytes = kPartialOffset + dense_weight_bytes(M, N);
     return (bytes + 255) & ~static_cast<size_t>(255);
 }
 
 size_t eptq_layer_workspace_bytes(const EptqLayer* layer, int B) {
     if (layer == nullptr || B <= 0) return 0;
     // Above the GEMV batch limit a layer the tensor-core GEMM takes needs the counter block only.
-    if (B > kGemmMinBatch && gemm_supported(*layer, B)) return kPartialOffset;
+    if (B > kGemmMinBatch && gemm_supported(*layer, B))
+        return kPartialOffset + (B >= kDenseMinTokens ? dense_weight_bytes(layer->M, layer->N) : 0);
     return eptq_workspace_bytes(layer->M, layer->N, B);
 }
 

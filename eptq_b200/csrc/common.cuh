@@ -38,6 +38,7 @@ constexpr size_t kCounterBytes = 4096;
 constexpr size_t kPartialOffset = 1u << 20;
 constexpr int kMaxCounters = static_cast<int>(kCounterBytes / sizeof(unsigned));
 constexpr int kGemmMinBatch = 16;           // batches above this run on the tensor-core GEMM
+constexpr int kDenseMinTokens = 1024;       // from here on the weight is reconstructed once into scratch and a dense GEMM follows
 // The last counter word is the GEMM's status word (EPTQ_ERR_TIMEOUT if a bounded wait ran out), so
 // GEMV plans may use at most kMaxCounters - 1 counters.
 

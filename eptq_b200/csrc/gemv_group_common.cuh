@@ -53,8 +53,11 @@ struct GroupLayer {
     float rope_scaling;
 };
 
-struct GroupArgs {
-    GroupLayer L[kMaxGroupLayers];
+// MAXL: capacity of the layer table.  Kernel parameters are copied at every launch, so launches of a few layers
+// use a small instantiation (half a microsecond per launch between 11 KB and 3 KB of parameters).
+template <int MAXL>
+struct GroupArgsT {
+    GroupLayer L[MAXL];
     const uint2* table16;     // E8-D4: fp16 (512, 4)
     const unsigned* packed;   // E8: 65536 packed entries (see e8_decode)
     float* acc;             // zero on entry, zero again on exit
@@ -72,9 +75,10 @@ struct GroupArgs {
     int total_tiles;
     unsigned* done;         // [phase][32] row tiles finalized in this launch, then one word of finished blocks; the
                             // last block to finish puts the zeros back.  Null when the launch has one phase.
-    int phase_unit0[kMaxGroupLayers];
-    int phase_units[kMaxGroupLayers];
+    int phase_unit0[MAXL];
+    int phase_units[MAXL];
 };
+using GroupArgs = GroupArgsT<kMaxGroupLayers>;
 
 namespace groupdev {
 
@@ -119,7 +123,8 @@ __device__ __forceinline__ Affine load_affine(const GroupLayer& L, int rt, int l
 
 // The warp that took the last ticket of row tile rt: reads the tile's accumulators, puts the zeros (and the
 // counter) back for the next launch, applies g, bias and the fused epilogue, writes y.
-__device__ __forceinline__ void finalize_tile(const GroupArgs& p, const GroupLayer& L, int rt, int lane,
+template <class GA>
+__device__ __forceinline__ void finalize_tile(const GA& p, const GroupLayer& L, int rt, int lane,
                                               const Affine& aff, const float* inv_rms) {
     if (lane == 0) p.counters[L.tile0 + rt] = 0u;
     __syncwarp();      // lane 0's acquire (its ticket), then the warp barrier: every lane sees the other warps' adds
@@ -187,7 +192,8 @@ __device__ __forceinline__ void finalize_tile(const GroupArgs& p, const GroupLay
 
 // Take a ticket for row tile rt of layer L; the last of the expected arrivals (n_main GEMV partials and
 // 4 correction quarters) reads the tile's accumulators, zeroes them for the next launch and writes y.
-__device__ __forceinline__ void arrive_and_finalize(const GroupArgs& p, const GroupLayer& L, int rt, int n_main,
+template <class GA>
+__device__ __forceinline__ void arrive_and_finalize(const GA& p, const GroupLayer& L, int rt, int n_main,
                                                     int lane, const Affine& aff, const float* inv_rms) {
     __syncwarp();      // orders every lane's adds before lane 0's release below (release is cumulative)
     unsigned ticket = 0;
@@ -201,8 +207,8 @@ __device__ __forceinline__ void arrive_and_finalize(const GroupArgs& p, const Gr
 
 // Correction of 4 consecutive Q rows (8 lanes per row, 4 entries per lane and pass).
 // Weight-side loads (row pointers, columns, O, h) are issued before `wait_dep`, x after.
-template <typename WaitFn, typename ContribFn>
-__device__ __forceinline__ void correction_unit(const GroupArgs& p, const GroupLayer& L, int qt, int lane,
+template <class GA, typename WaitFn, typename ContribFn>
+__device__ __forceinline__ void correction_unit(const GA& p, const GroupLayer& L, int qt, int lane,
                                                 float cstar0, float cstar1, float cstar2, float cstar3,
                                                 const float* inv_rms, WaitFn wait_dep, ContribFn contributors) {
     const int row = qt * 4 + (lane >> 3);

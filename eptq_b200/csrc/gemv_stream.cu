@@ -74,9 +74,10 @@ constexpr unsigned kSmemEnd = kRing + kStages * kStageBytes;        // 0x38000
 constexpr int kStreamSmemBytes = static_cast<int>(kSmemEnd - kBase);
 static_assert(kPlane + 2 * kStreamMaxN <= kTable, "digit planes overlap the table");
 
-struct StreamArgs {
-    GroupArgs g;                                  // layers and scratch; W = units, nw = blocks
-    alignas(64) CUtensorMap maps[kMaxGroupLayers];
+template <int MAXL>
+struct StreamArgsT {
+    GroupArgsT<MAXL> g;                           // layers and scratch; W = units, nw = blocks
+    alignas(64) CUtensorMap maps[MAXL];
     float unit;                                   // table value = integer coordinate * unit
     float inv_unit;
     unsigned zero;                                // 0: addend of the index multiplications
@@ -86,6 +87,8 @@ struct StreamArgs {
     int* status;
     unsigned long long wait_ns;                   // limit of one mbarrier wait
 };
+using StreamArgs = StreamArgsT<kMaxGroupLayers>;
+constexpr int kSmallGroup = 8;                // launches of up to this many layers pass the small parameter block
 
 // Phase time stamps for latency studies: compiled in only with -DEPTQ_STREAM_TRACE (never in the shipped
 // library).  Slot k of block b is g_stream_trace[b * 64 + k] (k = 8 * phase + event), nanoseconds of the global timer.
@@ -134,7 +137,7 @@ __device__ __noinline__ bool mbar_wait_slow(unsigned bar, unsigned parity, unsig
     for (;;) {
         for (int i = 0; i < 16; ++i) {
             if (mbar_try(bar, parity)) return true;
-            __nanosleep(250);                               // leave the issue slots to the warps that have work
+            __nanosleep(100);                               // leave the issue slots to the warps that have work
         }
         unsigned long long t;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -211,7 +214,8 @@ struct SegmentWalk {
     int k = -1;
     unsigned pos = 0, end = 0;
     int l = 0, last_l = -1;
-    __device__ __forceinline__ bool next(const GroupArgs& p, Segment& s) {
+    template <class GA>
+    __device__ __forceinline__ bool next(const GA& p, Segment& s) {
         while (pos == end) {
             if (++k >= p.n_phases) return false;
             const unsigned U = static_cast<unsigned>(p.phase_units[k]), G = gridDim.x;      // U * G < 2^32 (host)
@@ -230,7 +234,8 @@ struct SegmentWalk {
         return true;
     }
 };
-__device__ __forceinline__ int block_units(const GroupArgs& p) {
+template <class GA>
+__device__ __forceinline__ int block_units(const GA& p) {
     int n = 0;
     for (int k = 0; k < p.n_phases; ++k) {
         const unsigned U = static_cast<unsigned>(p.phase_units[k]), G = gridDim.x;
@@ -242,7 +247,8 @@ __device__ __forceinline__ int block_units(const GroupArgs& p) {
 // A layer of phase k may read its input once every row tile of phase k-1 is finalized (which implies the
 // phases before it).  Called by a whole warp: each lane reads one of the phase's 32 counters, the sum is the
 // number of finished tiles.  Polls with a pause, bounded by the global timer; false when the limit passes.
-__device__ __noinline__ bool wait_phase(const GroupArgs& p, int phase, int tiles, unsigned long long limit_ns) {
+template <class GA>
+__device__ __noinline__ bool wait_phase(const GA& p, int phase, int tiles, unsigned long long limit_ns) {
     unsigned long long t0;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
     const unsigned* line = p.done + (phase - 1) * 32 + (threadIdx.x & 31);
@@ -255,13 +261,14 @@ __device__ __noinline__ bool wait_phase(const GroupArgs& p, int phase, int tiles
         unsigned long long t;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
         if (t - t0 > limit_ns) return false;
-        __nanosleep(200);
+        __nanosleep(100);
     }
 }
 
 // End of a warp that may finalize tiles (finalizer, correction warps) in a chained launch: the last such warp
 // of the whole launch puts the zeros back into the phase counters -- every tile is finalized by then.
-__device__ __forceinline__ void launch_exit(const GroupArgs& p, int lane) {
+template <class GA>
+__device__ __forceinline__ void launch_exit(const GA& p, int lane) {
     if (p.done == nullptr) return;
     __syncwarp();
     unsigned old = 0;
@@ -311,8 +318,8 @@ __device__ __noinline__ float warp_inv_rms(const GroupLayer& L, int lane) {
 // Critical blocks of 4 consecutive Q rows, batch 1: 8 lanes per row, two entries per lane and pass (the
 // correction warps run with 64 registers).  Adds sum (O - marker code) * h*x to the tile's accumulators and
 // arrives as one of the tile's four correction quarters; finalizes the tile if that completes it.
-template <typename WaitFn>
-__device__ __forceinline__ void stream_correction_unit(const GroupArgs& p, const GroupLayer& L, int qt, int lane,
+template <class GA, typename WaitFn>
+__device__ __forceinline__ void stream_correction_unit(const GA& p, const GroupLayer& L, int qt, int lane,
                                                        float c0, float c1, float c2, float c3, float* inv_rms_slot,
                                                        WaitFn wait_input) {
     const int row = qt * 4 + (lane >> 3);
@@ -386,7 +393,8 @@ __device__ __forceinline__ void stream_correction_unit(const GroupArgs& p, const
 
 // A finished 64-row tile of a launch that patches critical blocks from unit lists (batch 1): the four 16-row
 // tiles at once, every load issued before the first use.  Same arithmetic as finalize_tile.
-__device__ __forceinline__ void finalize_tile64(const GroupArgs& p, const GroupLayer& L, int rt64, int lane,
+template <class GA>
+__device__ __forceinline__ void finalize_tile64(const GA& p, const GroupLayer& L, int rt64, int lane,
                                                 const float* inv_rms) {
     if (lane == 0) p.counters[L.tile0 + rt64 * 4] = 0u;
     __syncwarp();      // lane 0's acquire (its ticket), then the warp barrier: every lane sees the other warps' adds
@@ -469,9 +477,10 @@ __device__ __forceinline__ void finalize_tile64(const GroupArgs& p, const GroupL
     }
 }
 
-__global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __grid_constant__ StreamArgs P) {
+template <int MAXL>
+__global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __grid_constant__ StreamArgsT<MAXL> P) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
-    const GroupArgs& p = P.g;
+    const GroupArgsT<MAXL>& p = P.g;
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const unsigned base = smem_addr(smem_raw);
@@ -1077,6 +1086,23 @@ bool stream_gemv_supported(const EptqLayer* layers, int n, int B) {
 // `phases` (or null: one phase): phase of each layer, non-decreasing from 0.  Layers of phase k+1 may read
 // what phase k wrote (the kernel waits for the tiles of all earlier phases before it reads their inputs); with
 // more than one phase the launch is cooperative, so that every block is resident while others wait for it.
+// The first n layers (n <= kSmallGroup; phases never outnumber layers) into the small parameter block.
+void shrink_args(const StreamArgs& a, StreamArgsT<kSmallGroup>& s, int n) {
+    for (int i = 0; i < kSmallGroup; ++i) {
+        s.g.L[i] = a.g.L[i < n ? i : 0];
+        s.g.phase_unit0[i] = a.g.phase_unit0[i];
+        s.g.phase_units[i] = a.g.phase_units[i];
+        s.maps[i] = a.maps[i < n ? i : 0];
+    }
+    s.g.table16 = a.g.table16; s.g.packed = a.g.packed; s.g.acc = a.g.acc; s.g.counters = a.g.counters;
+    s.g.W = a.g.W; s.g.n_layers = a.g.n_layers; s.g.B = a.g.B; s.g.nw = a.g.nw;
+    s.g.corr_units = a.g.corr_units; s.g.n_corr_warps = a.g.n_corr_warps;
+    s.g.x_norm = a.g.x_norm; s.g.norm_eps = a.g.norm_eps;
+    s.g.n_phases = a.g.n_phases; s.g.total_tiles = a.g.total_tiles; s.g.done = a.g.done;
+    s.unit = a.unit; s.inv_unit = a.inv_unit; s.zero = a.zero; s.mul[0] = a.mul[0]; s.mul[1] = a.mul[1];
+    s.use_lists = a.use_lists; s.status = a.status; s.wait_ns = a.wait_ns;
+}
+
 int launch_gemv_stream(const EptqLayer* layers, int n, const EptqFusion* fusions, const int* phases,
                        const uint16_t* const* xs, uint16_t* const* ys, int B, void* workspace, size_t workspace_bytes,
                        cudaStream_t stream) {
@@ -1142,7 +1168,8 @@ int launch_gemv_stream(const EptqLayer* layers, int n, const EptqFusion* fusions
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return EPTQ_ERR_LAUNCH;
     if (!attr_done[dev]) {
-        if (cudaFuncSetAttribute(gemv_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamSmemBytes) != cudaSuccess)
+        if (cudaFuncSetAttribute(gemv_stream_kernel<kMaxGroupLayers>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamSmemBytes) != cudaSuccess ||
+            cudaFuncSetAttribute(gemv_stream_kernel<kSmallGroup>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamSmemBytes) != cudaSuccess)
             return EPTQ_ERR_LAUNCH;
         attr_done[dev] = true;
     }
@@ -1161,7 +1188,14 @@ int launch_gemv_stream(const EptqLayer* layers, int n, const EptqFusion* fusions
     }
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    const cudaError_t err = cudaLaunchKernelEx(&cfg, gemv_stream_kernel, a);
+    cudaError_t err;
+    if (n <= kSmallGroup) {
+        static StreamArgsT<kSmallGroup> small_args;        // guarded by args_mutex
+        shrink_args(a, small_args, n);
+        err = cudaLaunchKernelEx(&cfg, gemv_stream_kernel<kSmallGroup>, small_args);
+    } else {
+        err = cudaLaunchKernelEx(&cfg, gemv_stream_kernel<kMaxGroupLayers>, a);
+    }
     count_launch(EPTQ_KERNEL_GEMV_STREAM);
     return err == cudaSuccess ? EPTQ_OK : EPTQ_ERR_LAUNCH;
 }

@@ -148,8 +148,10 @@ int eptq_prepare_d4_table8(const float* table, uint8_t* out, float* scale);
  * read.  Calls that may overlap on the GPU need separate scratch.
  */
 size_t eptq_workspace_bytes(int M, int N, int B);
-/* The same from the layer itself: smaller for prefill-sized B when the tensor-core GEMM takes the layer
- * (it needs the first 1 MiB only), eptq_workspace_bytes(M, N, B) otherwise. */
+/* The same from the layer itself: for prefill-sized B when the tensor-core GEMM takes the layer, the first
+ * 1 MiB only (16 < B < 1024) or 1 MiB + 16*M*N bytes (B >= 1024: the fp16 weight is reconstructed once into the
+ * scratch and a dense GEMM follows; with a smaller scratch the call still works and reconstructs tile by tile);
+ * eptq_workspace_bytes(M, N, B) otherwise. */
 size_t eptq_layer_workspace_bytes(const EptqLayer* layer, int B);
 
 /*
