@@ -442,6 +442,105 @@ class LlamaDecodeEngine:
                      "ms_per_token": 1e3 * dev_s / max(max_new_tokens - 1, 1)}
 
 
+@dataclass
+class OPTLayerWeights:
+    """The six linears (with their biases inside) and the two LayerNorms of one OPT decoder layer."""
+    q: Callable
+    k: Callable
+    v: Callable
+    o: Callable
+    fc1: Callable
+    fc2: Callable
+    ln1_w: torch.Tensor
+    ln1_b: torch.Tensor
+    ln2_w: torch.Tensor
+    ln2_b: torch.Tensor
+
+
+class OPTDecodeEngine(LlamaDecodeEngine):
+    """The same engine for OPT-style decoders (models/opt.py:14-16, 62-68 of the reference; pre-LayerNorm
+    variants, i.e. every published size except 350m): learned positions, LayerNorm with bias, ReLU MLP, biases
+    in every projection, no rotary embedding.  One token = one CUDA graph as in the LLaMA engine (prefill,
+    capture, decode and the greedy state are inherited).  The quantized projections run in this package's
+    kernels (q/k/v as one grouped launch, single-query attention over the cache); LayerNorm, ReLU and the
+    residual adds are PyTorch elementwise ops inside the captured step."""
+
+    def __init__(self, layers: List[OPTLayerWeights], embed: torch.Tensor, pos_embed: torch.Tensor,
+                 final_ln_w: torch.Tensor, final_ln_b: torch.Tensor, lm_head: torch.Tensor, head_dim: int,
+                 n_heads: int, max_len: int, batch: int = 1, ln_eps: float = 1e-5, pos_offset: int = 2):
+        super().__init__(layers, embed, final_ln_w, lm_head, torch.zeros(head_dim // 2), ln_eps, head_dim,
+                         n_heads, n_heads, max_len, batch)
+        self.pos_embed, self.pos_offset = pos_embed, int(pos_offset)
+        self.final_ln_b = final_ln_b
+        self._fused = False                                   # the fused LLaMA steps do not apply
+
+    @classmethod
+    def from_model(cls, model, max_len: int, batch: int = 1, tp_group=None) -> "OPTDecodeEngine":
+        """Engine over the modules of a HuggingFace OPT model (as returned by load_quantized_model); weights are
+        shared, not copied."""
+        if tp_group is not None:
+            raise NotImplementedError("the OPT engine is single-GPU")
+        dec = model.model.decoder
+        cfg = model.config
+        if not cfg.do_layer_norm_before or dec.project_in is not None or dec.project_out is not None:
+            raise NotImplementedError("post-LayerNorm / projected-embedding OPT variants (opt-350m) are not covered")
+        layers = []
+        for layer in dec.layers:
+            a = layer.self_attn
+            layers.append(OPTLayerWeights(a.q_proj, a.k_proj, a.v_proj, a.out_proj, layer.fc1, layer.fc2,
+                                          layer.self_attn_layer_norm.weight.data, layer.self_attn_layer_norm.bias.data,
+                                          layer.final_layer_norm.weight.data, layer.final_layer_norm.bias.data))
+        head_dim = cfg.hidden_size // cfg.num_attention_heads
+        return cls(layers, dec.embed_tokens.weight.data, dec.embed_positions.weight.data,
+                   dec.final_layer_norm.weight.data, dec.final_layer_norm.bias.data, model.lm_head.weight.data,
+                   head_dim, cfg.num_attention_heads, max_len, batch,
+                   ln_eps=float(dec.final_layer_norm.eps), pos_offset=int(getattr(dec.embed_positions, "offset", 2)))
+
+    def _ln(self, x: torch.Tensor, w: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+        return F.layer_norm(x, (x.shape[-1],), w, b, self.eps)
+
+    def _stack(self, ids: torch.Tensor, positions: torch.Tensor, kernels: bool) -> torch.Tensor:
+        B, T = ids.shape
+        hd, nh = self.head_dim, self.n_heads
+        x = (F.embedding(ids, self.embed) + F.embedding(positions + self.pos_offset, self.pos_embed)[None]).reshape(B * T, -1)
+        fused_attention = kernels and T <= 8 and hd in (64, 128)
+        mask = None if fused_attention else (self.key_index[None, :] <= positions[:, None])[None, None]
+        if kernels:
+            from .kernels import glue
+        for li, L in enumerate(self.layers):
+            hn = self._ln(x, L.ln1_w, L.ln1_b)
+            q, k, v = apply_group((L.q, L.k, L.v), hn) if kernels else [f(hn) for f in (L.q, L.k, L.v)]
+            kc, vc = self.k_cache[li], self.v_cache[li]
+            kc.index_copy_(2, positions, k.reshape(B, T, nh, hd).transpose(1, 2))
+            vc.index_copy_(2, positions, v.reshape(B, T, nh, hd).transpose(1, 2))
+            if fused_attention:
+                att = glue.decode_attention(q.contiguous(), kc, vc, positions, B)
+            else:
+                att = F.scaled_dot_product_attention(q.reshape(B, T, nh, hd).transpose(1, 2), kc, vc, attn_mask=mask)
+                att = att.transpose(1, 2).reshape(B * T, nh * hd)
+            x = x + L.o(att)
+            hn = self._ln(x, L.ln2_w, L.ln2_b)
+            x = x + L.fc2(F.relu(L.fc1(hn)))
+        x = self._ln(x, self.final_norm, self.final_ln_b)
+        return F.linear(x, self.lm_head).reshape(B, T, -1)
+
+    def forward(self, ids: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
+        if not ids.is_cuda or self.dtype != torch.float16:
+            raise RuntimeError("OPTDecodeEngine.forward runs on CUDA fp16 weights only "
+                               "(forward_reference is the plain PyTorch statement of the same step)")
+        return self._stack(ids, positions, kernels=True)
+
+    def forward_reference(self, ids: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
+        return self._stack(ids, positions, kernels=False)
+
+
+def decode_engine_for(model, max_len: int, batch: int = 1, tp_group=None) -> LlamaDecodeEngine:
+    """The engine class that matches a HuggingFace model's architecture (OPT or LLaMA-style)."""
+    kind = str(getattr(model.config, "model_type", "")).lower()
+    cls = OPTDecodeEngine if kind == "opt" else LlamaDecodeEngine
+    return cls.from_model(model, max_len, batch, tp_group=tp_group)
+
+
 def synthetic_llama_engine(hidden: int, intermediate: int, n_layers: int, n_heads: int, n_kv_heads: int,
                            vocab: int, quantizer_type: str, codebook: torch.Tensor, max_len: int, batch: int = 1,
                            device: str = "cuda", seed: int = 42, outlier_frac: float = 0.002,

@@ -64,3 +64,14 @@ def test_prepare_d4_table8_on_host(built_library):
     warped = tab * (1 + 0.05 * np.abs(tab))
     assert lib.eptq_prepare_d4_table8(np.ascontiguousarray(warped).ctypes.data, out.ctypes.data,
                                       ctypes.addressof(scale)) == 7
+
+
+def test_workspace_sizes_for_long_prefills(built_library):
+    """From 1024 tokens on the scratch also holds the reconstructed fp16 weight (16 M N bytes behind the first MiB)."""
+    from eptq_b200 import _lib
+    lib = _lib.load()
+    M, N = 512, 4096
+    weight = 8 * M * N * 2
+    assert lib.eptq_workspace_bytes(M, N, 1024) == (1 << 20) + weight
+    assert lib.eptq_workspace_bytes(M, N, 4096) >= (1 << 20) + weight        # the shape-only bound also covers the SIMT path
+    assert lib.eptq_workspace_bytes(M, N, 1023) < (1 << 20) + weight

@@ -1,5 +1,9 @@
 """Chained launch (eptq_linear_forward_chain): o_proj -> gate/up -> down of a decoder layer in one launch,
-checked against an fp32 PyTorch statement of the same arithmetic on oracle-reconstructed weights."""
+checked against an fp32 PyTorch statement of the same arithmetic on oracle-reconstructed weights.
+
+Three cases: a small layer (fewer units than blocks in a phase, so some blocks sit a phase out), a Llama-2-7B-sized
+layer with the residual stream updated in place, and the same layer with the residual stream alternating between
+two buffers."""
 import numpy as np
 import pytest
 import torch
@@ -9,7 +13,7 @@ from tests.util import qld_arrays
 
 pytestmark = pytest.mark.gpu
 
-H, F_, EPS = 1024, 2816, 1e-5
+EPS = 1e-5
 
 
 def _layer(out_f, in_f, seed, table):
@@ -38,7 +42,8 @@ def _reference(att, x, w_norm, Wo, Wg, Wu, Wd):
     return f16(x1 + f16(act @ Wd.T)), gate, up
 
 
-def test_chain_o_gateup_down(table):
+@pytest.mark.parametrize("H,F_,two_buffers", [(1024, 2816, False), (4096, 11008, False), (4096, 11008, True)])
+def test_chain_o_gateup_down(table, H, F_, two_buffers):
     from eptq_b200 import _lib
     from eptq_b200.kernels import linear_forward_chain, workspace_status
     (o, Wo), (gate, Wg), (up, Wu), (down, Wd) = (_layer(H, H, 1, table), _layer(F_, H, 2, table),
@@ -59,6 +64,7 @@ def test_chain_o_gateup_down(table):
         descs.append(d)
     for _ in range(2):                                    # twice: the scratch must come back clean
         x = x0.clone()
+        xm = torch.empty_like(x) if two_buffers else x         # residual stream after the attention block
         gbuf = torch.empty(1, F_, device="cuda", dtype=torch.float16)
         ubuf = torch.empty_like(gbuf)
 
@@ -69,8 +75,8 @@ def test_chain_o_gateup_down(table):
             f.x_aux = None if x_aux is None else x_aux.data_ptr()
             return f
         fz = [fus(y_op=_lib.Y_ADD_RESIDUAL, residual=x), fus(_lib.X_RMSNORM), fus(_lib.X_RMSNORM),
-              fus(_lib.X_SILU_MUL, _lib.Y_ADD_RESIDUAL, residual=x, x_aux=ubuf)]
-        linear_forward_chain(descs, [0, 1, 1, 2], [att, x, x, gbuf], [0, F_, F_, 0], fz, ys=[x, gbuf, ubuf, x])
+              fus(_lib.X_SILU_MUL, _lib.Y_ADD_RESIDUAL, residual=xm, x_aux=ubuf)]
+        linear_forward_chain(descs, [0, 1, 1, 2], [att, xm, xm, gbuf], [0, F_, F_, 0], fz, ys=[xm, gbuf, ubuf, x])
         assert workspace_status(device="cuda") == 0
         tol = 2e-3
         for got, ref in ((gbuf, want_gate), (ubuf, want_up), (x, want)):
