@@ -24,6 +24,7 @@
 // Reference counterpart: e8d4_wmma_v2_kernel (csrc/eptq_kernels.cu:309-461).
 
 #include <cuda.h>
+#include <atomic>
 #include <cudaTypedefs.h>
 
 #include "common.cuh"
@@ -410,7 +411,7 @@ PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() {
 
 template <int KIND, int TM, int NT>
 int launch_ws(const CUtensorMap& tmap, const GemmWsArgs& a, dim3 grid, cudaStream_t stream) {
-    static bool attr_done[64] = {};
+    static std::atomic<bool> attr_done[64];       // setting the attribute twice is harmless; the flag itself must not race
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return EPTQ_ERR_LAUNCH;
     if (!attr_done[dev]) {

@@ -41,6 +41,7 @@
 // (csrc/eptq_kernels.cu:39-150), one launch per layer and batch row there.
 
 #include <cmath>
+#include <atomic>
 #include <mutex>
 
 #include "gemv_group_common.cuh"
@@ -642,7 +643,7 @@ int launch_gemv_group_pass(const EptqLayer* layers, int n, const EptqFusion* fus
         if (st != EPTQ_OK) return st;
     }
 
-    static bool attr_done[64] = {};
+    static std::atomic<bool> attr_done[64];       // setting the attribute twice is harmless; the flag itself must not race
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return EPTQ_ERR_LAUNCH;
     if (!attr_done[dev]) {

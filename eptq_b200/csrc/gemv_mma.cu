@@ -48,6 +48,7 @@
 // Reference counterpart: e8d4_fused_kernel_t (csrc/eptq_kernels.cu:161-292).
 
 #include "common.cuh"
+#include <atomic>
 
 namespace eptq {
 
@@ -542,7 +543,7 @@ __global__ void __launch_bounds__(kThreads, NBP == 1 ? 2 : 1) gemv_mma_d4_kernel
 
 template <int WC, int NBP>
 int launch_variant(const MmaGemvArgs& a, dim3 grid, cudaStream_t stream) {
-    static bool attr_done[16] = {};
+    static std::atomic<bool> attr_done[16];       // setting the attribute twice is harmless; the flag itself must not race
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return EPTQ_ERR_LAUNCH;
     if (dev < 0 || dev >= 16) return EPTQ_ERR_UNSUPPORTED;

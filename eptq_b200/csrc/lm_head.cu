@@ -10,6 +10,7 @@
 // (ticket in scratch, bounded by nothing: no block waits) merges the per-block results and writes the tokens.
 
 #include "common.cuh"
+#include <atomic>
 
 namespace eptq {
 namespace {
@@ -185,7 +186,7 @@ extern "C" int eptq_lm_head_argmax(const uint16_t* W, const uint16_t* x, const u
     a.part_idx = reinterpret_cast<int*>(reinterpret_cast<char*>(workspace) + 256 + static_cast<size_t>(1024) * B * 4);
     a.V = V; a.H = H; a.B = B; a.eps = eps;
     const size_t smem = static_cast<size_t>(B) * H * sizeof(__half);
-    static bool attr_done[64] = {};
+    static std::atomic<bool> attr_done[64];       // setting the attribute twice is harmless; the flag itself must not race
     if (dev >= 0 && dev < 64 && !attr_done[dev] && smem > 48 * 1024) {
         if (cudaFuncSetAttribute(lm_head_argmax_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kLmMaxBatch * kLmMaxHidden * 2) != cudaSuccess)
             return EPTQ_ERR_LAUNCH;
