@@ -647,6 +647,31 @@ def run_gpu_arm(args):
             torch.cuda.empty_cache()
         decode_stats["config"] = ("llama2-7b architecture, random init, 32 layers, 512-token prompt + 128 greedy "
                                   f"tokens, batch 1, tp{world}, one CUDA graph per token")
+        if world > 1:
+            # The tensor-parallel token step (sharded GEMV launches, chained MLP, push all-reduce) against the same
+            # model unsharded on this GPU: logits of one decoded token after a 32-token prompt, 2 decoder layers.
+            tab = E8D4Quantizer(radius=RADIUS).codes.to(dev)
+            kw = dict(max_len=64, batch=1, device=str(dev))
+            tp_eng = synthetic_llama_engine(hidden, inter, 2, heads, kv, vocab, "e8_d4", tab, tp_rank=rank, tp_size=world,
+                                            tp_group=dist.group.WORLD, comm=comm, **kw)
+            one = synthetic_llama_engine(hidden, inter, 2, heads, kv, vocab, "e8_d4", tab, **kw)
+            short = ids[:, :32]
+            with torch.no_grad():
+                tok_tp, tok_one = tp_eng.prefill(short), one.prefill(short)
+                pos = torch.tensor([32], device=dev)
+                a = tp_eng.forward(tok_one[:, None], pos).float()
+                b = one.forward(tok_one[:, None], pos).float()
+            t = torch.tensor([float((a - b).abs().max() / b.abs().max())], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            decode_stats["tp_step_check"] = {"logits_max_rel": float(t[0]), "ok": bool(float(t[0]) <= 2e-2)}
+            del tp_eng, one
+            torch.cuda.empty_cache()
+            if not decode_stats["tp_step_check"]["ok"]:
+                if rank == 0:
+                    print(json.dumps({"metric": METRIC, "error": "tensor-parallel decode step check failed",
+                                      "tp_step_check": decode_stats["tp_step_check"]}))
+                sys.stdout.flush()
+                os._exit(3)
 
     if comm is not None:
         comm.check()                                   # a device-side wait that ran out would show here

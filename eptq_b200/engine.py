@@ -205,7 +205,8 @@ class LlamaDecodeEngine:
         """Six launches per decoder layer: q/k/v (RMSNorm folded in; rotary embedding and the cache
         append done by the finalizing warps), attention, o (+ residual), gate/up (RMSNorm folded in),
         SiLU*up, down (+ residual).  Tensor-parallel: o and down store partial sums and the push
-        all-reduce adds them to the residual stream (eight launches)."""
+        all-reduce adds them to the residual stream (eight launches).  (gate/up -> down as two phases of one
+        chained launch was measured here too: 425 against 433 tokens/s at two GPUs, so the separate launches stay.)"""
         from . import _lib
         from .kernels import glue, linear_forward_group
         B = ids.shape[0]
@@ -213,10 +214,11 @@ class LlamaDecodeEngine:
         x = F.embedding(ids, self.embed).reshape(B, -1).contiguous()                # residual stream, updated in place
         pos_ptr, freq_ptr = positions.data_ptr(), self.inv_freq.data_ptr()
 
-        def fus(x_op=_lib.X_PLAIN, y_op=_lib.Y_STORE, residual=None):
+        def fus(x_op=_lib.X_PLAIN, y_op=_lib.Y_STORE, residual=None, x_aux=None):
             f = _lib.EptqFusion()
             f.x_op, f.y_op, f.norm_eps, f.rope_scaling, f.max_len = x_op, y_op, self.eps, self.rope_scaling, self.max_len
             f.residual = None if residual is None else residual.data_ptr()
+            f.x_aux = None if x_aux is None else x_aux.data_ptr()
             f.position, f.inv_freq = pos_ptr, freq_ptr
             return f
         qkv_f = [fus(_lib.X_RMSNORM, _lib.Y_ROPE), fus(_lib.X_RMSNORM, _lib.Y_ROPE_TO_CACHE),
@@ -248,7 +250,7 @@ class LlamaDecodeEngine:
             if ok:
                 for P in self._fused:
                     for d in P["qkv"] + P["o"] + P["gate_up"] + P["down"]:
-                        ok = ok and bool(d.table8) and d.table8_scale > 0 and d.N % 64 == 0 and d.N <= 27648
+                        ok = ok and bool(d.table8) and d.table8_scale > 0 and d.N % 64 == 0 and d.N <= 25600
             self._chain_ok = bool(ok)
         return self._chain_ok
 
