@@ -5,10 +5,11 @@ The reference decodes through the HuggingFace forward wrapped in torch.compile a
 captured into ONE CUDA graph that also advances the position and feeds the picked token back, so a
 decoded token costs one graph launch and no host work.  Three statements of the same step:
 
-* batch 1, one GPU, E8-D4: per decoder layer the attention kernel and ONE chained launch of the streaming
-  GEMV -- o (+ residual) -> gate/up (RMSNorm folded in) -> down (SiLU(gate)*up formed as it reads its input,
-  + residual) -> the next layer's q/k/v (RMSNorm folded in, rotary embedding and cache append in the
-  epilogue) -- then the final norm, lm_head and greedy pick in the library's own kernel;
+* batch 1, one GPU, E8-D4: per decoder layer the attention kernel and four launches of the streaming GEMV --
+  o (+ residual), gate/up (RMSNorm folded in), down (SiLU(gate)*up formed as it reads its input, + residual),
+  the next layer's q/k/v (RMSNorm folded in, rotary embedding and cache append in the epilogue); with
+  `one_launch_per_layer` the four become the phases of ONE chained launch -- then the final norm, lm_head and
+  greedy pick in the library's own kernel;
 * batch <= 2 otherwise (E8, tensor parallel): the same work as separate grouped launches;
 * anything else, and the prefill: RMSNorm, grouped q/k/v, rotary embedding + cache append, attention, o,
   RMSNorm, grouped gate/up, SiLU*up, down as separate kernels (many tokens: the linears then take the
@@ -92,6 +93,11 @@ class LlamaDecodeEngine:
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self._pick: Optional[torch.Tensor] = None     # where a fused step writes its token (set inside _step)
         self._fused = None           # descriptors for the fully fused one-token step, False if not eligible
+        # Batch-1 decode with the streaming kernel: the four dependent stages of a layer (o, gate/up, down, next
+        # q/k/v) as four stream-ordered launches of the same kernel (default), or as ONE chained launch.  Measured
+        # on B200, Llama-2-7B shapes: 507 against 470 tokens/s -- a kernel boundary under programmatic dependent
+        # launch costs less than a phase boundary inside the launch (ticket, finalize, counter, poll).
+        self.one_launch_per_layer = False
 
     # ---- construction -------------------------------------------------------------------------
     @classmethod
@@ -296,7 +302,14 @@ class LlamaDecodeEngine:
                 xs += [x, x, x]
                 ys += [qs[(li + 1) & 1], self.k_cache[li + 1], self.v_cache[li + 1]]
                 fz += qkv_f
-            linear_forward_chain(descs, phases, xs, [0] * len(descs), fz, ys=ys)
+            if self.one_launch_per_layer:
+                linear_forward_chain(descs, phases, xs, [0] * len(descs), fz, ys=ys)
+            else:                                            # the same stages as stream-ordered launches
+                lo = 0
+                for hi in range(1, len(descs) + 1):
+                    if hi == len(descs) or phases[hi] != phases[lo]:
+                        linear_forward_chain(descs[lo:hi], [0] * (hi - lo), xs[lo:hi], [0] * (hi - lo), fz[lo:hi], ys=ys[lo:hi])
+                        lo = hi
         return self._head(x, 1)
 
     def _head(self, x: torch.Tensor, B: int) -> torch.Tensor:

@@ -88,6 +88,13 @@ def test_engine_graph_decode_gpu(quantizer_type, hidden, heads, inter):
         assert float((a - b).abs().max()) <= 2e-2 * scale
         # head size 128 takes the fully fused step (norm, rotary, cache, residual in the GEMVs)
         assert (eng._fused not in (None, False)) == (hidden // heads == 128)
+        if eng._fused and eng._chainable():
+            # the same token with a layer's four GEMV stages as ONE chained launch instead of four launches
+            one = LlamaDecodeEngine.from_model(model, max_len=64, batch=1)
+            one.one_launch_per_layer = True
+            one.forward(ids, pos)
+            c = one.forward(nxt, p1).float()
+            assert float((c - b).abs().max()) <= 2e-2 * scale
     eager, _ = eng.decode(ids, 12, use_graph=False)
     graphed, stats = eng.decode(ids, 12, use_graph=True)
     assert eng.graph is not None
