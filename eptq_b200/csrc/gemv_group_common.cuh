@@ -10,6 +10,7 @@
 namespace eptq {
 
 constexpr int kMaxGroupLayers = 32;
+constexpr int kMaxCutBlocks = 160;           // blocks a host-made work split may name (streaming kernel, one phase)
 
 struct GroupLayer {
     const int16_t* Q;

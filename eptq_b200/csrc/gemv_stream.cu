@@ -74,10 +74,16 @@ constexpr unsigned kSmemEnd = kRing + kStages * kStageBytes;        // 0x38000
 constexpr int kStreamSmemBytes = static_cast<int>(kSmemEnd - kBase);
 static_assert(kPlane + 2 * kStreamMaxN <= kTable, "digit planes overlap the table");
 
-template <int MAXL>
+// One-phase launches of several long layers: block b works on units [W b / G + cut[b], W (b + 1) / G + cut[b + 1]),
+// the even split shifted by a few units per block, so that a block which goes on into another layer (and prepares
+// that layer's input in between) gets fewer units.  Only the instantiation that uses it carries the table.
+template <bool CUT> struct CutTable { signed char cut[kMaxCutBlocks + 1]; };
+template <> struct CutTable<false> {};
+template <int MAXL, bool CUT = false>
 struct StreamArgsT {
     GroupArgsT<MAXL> g;                           // layers and scratch; W = units, nw = blocks
     alignas(64) CUtensorMap maps[MAXL];
+    CutTable<CUT> shift;
     float unit;                                   // table value = integer coordinate * unit
     float inv_unit;
     unsigned zero;                                // 0: addend of the index multiplications
@@ -87,7 +93,7 @@ struct StreamArgsT {
     int* status;
     unsigned long long wait_ns;                   // limit of one mbarrier wait
 };
-using StreamArgs = StreamArgsT<kMaxGroupLayers>;
+using StreamArgs = StreamArgsT<kMaxGroupLayers, false>;
 constexpr int kSmallGroup = 8;                // launches of up to this many layers pass the small parameter block
 
 // Phase time stamps for latency studies: compiled in only with -DEPTQ_STREAM_TRACE (never in the shipped
@@ -214,6 +220,8 @@ struct SegmentWalk {
     int k = -1;
     unsigned pos = 0, end = 0;
     int l = 0, last_l = -1;
+    const signed char* cut = nullptr;        // shifts of the even split (one-phase launches that carry a CutTable)
+    __device__ __forceinline__ explicit SegmentWalk(const signed char* c = nullptr) : cut(c) {}
     template <class GA>
     __device__ __forceinline__ bool next(const GA& p, Segment& s) {
         while (pos == end) {
@@ -221,6 +229,10 @@ struct SegmentWalk {
             const unsigned U = static_cast<unsigned>(p.phase_units[k]), G = gridDim.x;      // U * G < 2^32 (host)
             pos = static_cast<unsigned>(p.phase_unit0[k]) + (U * blockIdx.x) / G;
             end = static_cast<unsigned>(p.phase_unit0[k]) + (U * (blockIdx.x + 1u)) / G;
+            if (cut != nullptr) {                            // one phase: the host's corrections to the even split
+                pos += cut[blockIdx.x];
+                end += cut[blockIdx.x + 1];
+            }
         }
         while (l + 1 < p.n_layers && static_cast<unsigned>(p.L[l + 1].unit0) <= pos) ++l;
         const int local = static_cast<int>(pos) - p.L[l].unit0;
@@ -235,12 +247,13 @@ struct SegmentWalk {
     }
 };
 template <class GA>
-__device__ __forceinline__ int block_units(const GA& p) {
+__device__ __forceinline__ int block_units(const GA& p, const signed char* cut) {
     int n = 0;
     for (int k = 0; k < p.n_phases; ++k) {
         const unsigned U = static_cast<unsigned>(p.phase_units[k]), G = gridDim.x;
         n += static_cast<int>((U * (blockIdx.x + 1u)) / G - (U * blockIdx.x) / G);
     }
+    if (cut != nullptr) n += cut[blockIdx.x + 1] - cut[blockIdx.x];
     return n;
 }
 
@@ -477,10 +490,15 @@ __device__ __forceinline__ void finalize_tile64(const GA& p, const GroupLayer& L
     }
 }
 
-template <int MAXL>
-__global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __grid_constant__ StreamArgsT<MAXL> P) {
+template <bool CUT> struct CutPointer;
+template <> struct CutPointer<true> { static __device__ __forceinline__ const signed char* of(const CutTable<true>& t) { return t.cut; } };
+template <> struct CutPointer<false> { static __device__ __forceinline__ const signed char* of(const CutTable<false>&) { return nullptr; } };
+
+template <int MAXL, bool CUT>
+__global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __grid_constant__ StreamArgsT<MAXL, CUT> P) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     const GroupArgsT<MAXL>& p = P.g;
+    const signed char* const cut = CutPointer<CUT>::of(P.shift);
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const unsigned base = smem_addr(smem_raw);
@@ -518,7 +536,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
         // ------------------------------------------------------------ producer
         if (warp == kProducerWarp) {
             if (lane == 0) {
-                SegmentWalk walk;
+                SegmentWalk walk(cut);
                 Segment sg;
                 int s = 0, issued = 0;
                 unsigned ph = 0;
@@ -548,7 +566,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
         // this warp turns them into floats, adds them to the accumulators in scratch, arrives at the four
         // 16-row tiles with the segment's units as weight and finalizes those it completes.
         if (warp == kFinalizerWarp) {
-            SegmentWalk walk;
+            SegmentWalk walk(cut);
             Segment sg;
             unsigned k = 0;
             bool waited = false;
@@ -652,7 +670,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
             // Unit lists: the critical blocks of a segment are one contiguous run of (position, 8 values); the two
             // warps take alternate entries, read the activation digits the consumers prepared and add
             // (O - marker code) / unit * digits to the segment's correction tile, in step with the flushes.
-            SegmentWalk walk;
+            SegmentWalk walk(cut);
             Segment sg, nxt;
             unsigned k = 0, n_prep = 0;
             bool ok = true;
@@ -941,8 +959,8 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
     };
 
     if (tid == 0) misc[47] = 0.f;
-    const int n_units = block_units(p);
-    SegmentWalk walk;
+    const int n_units = block_units(p, cut);
+    SegmentWalk walk(cut);
     Segment sg;
     unsigned q[8];
     unsigned ph = 0;
@@ -1086,8 +1104,42 @@ bool stream_gemv_supported(const EptqLayer* layers, int n, int B) {
 // `phases` (or null: one phase): phase of each layer, non-decreasing from 0.  Layers of phase k+1 may read
 // what phase k wrote (the kernel waits for the tiles of all earlier phases before it reads their inputs); with
 // more than one phase the launch is cooperative, so that every block is resident while others wait for it.
+// Work split of a one-phase launch of several layers.  A block that goes on from one layer into the next prepares
+// the next layer's input in between, which costs about kSwitchUnits units of streaming; its share is that much
+// shorter, and a share that would end just behind a layer's first units ends at the layer's edge instead.
+// starts: first unit of each layer (ascending, starts[0] == 0); cut[b] .. cut[b + 1] is block b's range.
+constexpr int kSwitchUnits = 3;
+void balanced_cut(const int* starts, int n_layers, int units, int blocks, int* cut) {
+    int pos = 0;
+    for (int b = 0; b < blocks; ++b) {
+        cut[b] = pos;
+        if (b == blocks - 1) { pos = units; break; }
+        int inner = 0;                                        // layer edges strictly inside what is left
+        for (int l = 1; l < n_layers; ++l) if (starts[l] > pos && starts[l] < units) ++inner;
+        const double target = (static_cast<double>(units - pos) + kSwitchUnits * inner) / (blocks - b);
+        double cost = 0.0;
+        while (pos < units) {
+            int edge = units;                                 // next layer edge behind pos
+            for (int l = 1; l < n_layers; ++l) if (starts[l] > pos) { edge = starts[l]; break; }
+            const int room = static_cast<int>(target - cost + 0.5);
+            if (room <= 0) break;
+            const int take = room < edge - pos ? room : edge - pos;
+            pos += take;
+            cost += take;
+            if (pos == edge && pos < units) {                 // at an edge: go on only if the switch and a unit fit
+                if (cost + kSwitchUnits + 1 > target) break;
+                cost += kSwitchUnits;
+            }
+        }
+        if (pos == cut[b] && pos < units) ++pos;              // never an empty share while work is left
+    }
+    for (int b = blocks; b <= kMaxCutBlocks; ++b) cut[b] = units;
+    cut[blocks] = units;
+}
+
 // The first n layers (n <= kSmallGroup; phases never outnumber layers) into the small parameter block.
-void shrink_args(const StreamArgs& a, StreamArgsT<kSmallGroup>& s, int n) {
+template <bool CUT>
+void shrink_args(const StreamArgs& a, StreamArgsT<kSmallGroup, CUT>& s, int n) {
     for (int i = 0; i < kSmallGroup; ++i) {
         s.g.L[i] = a.g.L[i < n ? i : 0];
         s.g.phase_unit0[i] = a.g.phase_unit0[i];
@@ -1153,6 +1205,21 @@ int launch_gemv_stream(const EptqLayer* layers, int n, const EptqFusion* fusions
     // Every phase is split over all blocks; a phase with fewer units than blocks leaves some without work in it.
     const int blocks = chained ? n_sms : (units < n_sms ? static_cast<int>(units) : n_sms);
     if (!chained) a.g.phase_units[0] = static_cast<int>(units);
+    // Long shares of several layers: shifts of the even split (see CutTable); small enough to be int8 by construction.
+    static StreamArgsT<kSmallGroup, true> cut_args;          // guarded by args_mutex
+    bool use_cut = false;
+    if (!chained && n >= 4 && n <= kSmallGroup && blocks <= kMaxCutBlocks && units >= 8ll * blocks) {
+        int starts[kMaxGroupLayers], cut[kMaxCutBlocks + 1];
+        for (int i = 0; i < n; ++i) starts[i] = a.g.L[i].unit0;
+        balanced_cut(starts, n, static_cast<int>(units), blocks, cut);
+        use_cut = true;
+        for (int b = 0; b <= kMaxCutBlocks; ++b) {
+            const long long even = b <= blocks ? units * b / blocks : units;
+            const long long d = (b <= blocks ? cut[b] : static_cast<int>(units)) - even;
+            if (d < -127 || d > 127) use_cut = false;
+            cut_args.shift.cut[b] = static_cast<signed char>(b <= blocks ? d : 0);
+        }
+    }
     a.g.W = units;
     a.g.nw = blocks;
     a.g.corr_units = corr_units;
@@ -1168,8 +1235,9 @@ int launch_gemv_stream(const EptqLayer* layers, int n, const EptqFusion* fusions
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return EPTQ_ERR_LAUNCH;
     if (!attr_done[dev]) {
-        if (cudaFuncSetAttribute(gemv_stream_kernel<kMaxGroupLayers>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamSmemBytes) != cudaSuccess ||
-            cudaFuncSetAttribute(gemv_stream_kernel<kSmallGroup>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamSmemBytes) != cudaSuccess)
+        if (cudaFuncSetAttribute(gemv_stream_kernel<kMaxGroupLayers, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamSmemBytes) != cudaSuccess ||
+            cudaFuncSetAttribute(gemv_stream_kernel<kSmallGroup, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamSmemBytes) != cudaSuccess ||
+            cudaFuncSetAttribute(gemv_stream_kernel<kSmallGroup, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamSmemBytes) != cudaSuccess)
             return EPTQ_ERR_LAUNCH;
         attr_done[dev] = true;
     }
@@ -1189,12 +1257,15 @@ int launch_gemv_stream(const EptqLayer* layers, int n, const EptqFusion* fusions
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     cudaError_t err;
-    if (n <= kSmallGroup) {
-        static StreamArgsT<kSmallGroup> small_args;        // guarded by args_mutex
+    if (use_cut) {
+        shrink_args(a, cut_args, n);
+        err = cudaLaunchKernelEx(&cfg, gemv_stream_kernel<kSmallGroup, true>, cut_args);
+    } else if (n <= kSmallGroup) {
+        static StreamArgsT<kSmallGroup, false> small_args;     // guarded by args_mutex
         shrink_args(a, small_args, n);
-        err = cudaLaunchKernelEx(&cfg, gemv_stream_kernel<kSmallGroup>, small_args);
+        err = cudaLaunchKernelEx(&cfg, gemv_stream_kernel<kSmallGroup, false>, small_args);
     } else {
-        err = cudaLaunchKernelEx(&cfg, gemv_stream_kernel<kMaxGroupLayers>, a);
+        err = cudaLaunchKernelEx(&cfg, gemv_stream_kernel<kMaxGroupLayers, false>, a);
     }
     count_launch(EPTQ_KERNEL_GEMV_STREAM);
     return err == cudaSuccess ? EPTQ_OK : EPTQ_ERR_LAUNCH;
