@@ -141,10 +141,12 @@ __device__ __noinline__ bool mbar_wait_slow(unsigned bar, unsigned parity, unsig
     unsigned long long t0;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
     for (;;) {
-        for (int i = 0; i < 16; ++i) {
-            if (mbar_try(bar, parity)) return true;
-            __nanosleep(100);                               // leave the issue slots to the warps that have work
-        }
+        // suspended by the hardware until the phase completes or the hint (20 us) passes: no polling in between,
+        // so the issue slots stay with the warps that have work and the wake-up does not wait for a sleep to end
+        unsigned done;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(done) : "r"(bar), "r"(parity), "r"(20000u) : "memory");
+        if (done != 0) return true;
         unsigned long long t;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
         if (t - t0 > limit_ns) return false;
