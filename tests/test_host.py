@@ -98,3 +98,30 @@ def test_e8_table_packs_and_unpacks():
     assert float(back[65535].abs().max()) == 0.0                 # marker slot decodes to zero
     assert pack_e8_table(t * (1 + 0.05 * t.abs())) is None       # radially warped: not a lattice multiple
     assert pack_e8_table(t[:, :4]) is None
+
+
+def test_critical_lists_group_blocks_by_unit_and_check_their_range(built_library):
+    """The per-unit lists of critical blocks are a permutation of the CSR side tables grouped by 64 x 128 unit,
+    and a layer whose corrections could overflow the kernel's 32-bit fixed-point sums gets no lists."""
+    from eptq_b200.kernels import CRIT_ROW_LIMIT, critical_lists
+    qd = make_layer(1024, 512, seed=5, outlier_frac=0.01)
+    lin = EPTQLinear.from_quantized_data(qd, torch.from_numpy(oracle.d4_table(1.75)), "e8_d4")
+    M, N = lin.Q.shape
+    ptr, pos, O = lin.crit_ptr, lin.crit_pos, lin.crit_O
+    assert ptr is not None and int(ptr[-1]) == lin.O_col.shape[0] == pos.shape[0] == O.shape[0]
+    cc = (N + 127) // 128
+    assert ptr.shape[0] == ((M + 63) // 64) * cc + 1
+    rows = torch.repeat_interleave(torch.arange(M), (lin.O_row_ptr[1:] - lin.O_row_ptr[:-1]).long())
+    want = sorted(zip(((rows // 64) * cc + lin.O_col.long() // 128).tolist(), (rows % 64).tolist(), lin.O_col.tolist()))
+    unit_of_entry = torch.repeat_interleave(torch.arange(ptr.shape[0] - 1), (ptr[1:] - ptr[:-1]).long())
+    p = pos.long() & 0xFFFFFFFF
+    got = sorted(zip(unit_of_entry.tolist(), (p >> 16).tolist(), (p & 0xFFFF).tolist()))
+    assert got == want
+    # the same O values, regrouped
+    assert sorted(O.float().sum(1).tolist()) == pytest.approx(sorted(lin.O_vals.reshape(-1, 8).float().sum(1).tolist()))
+    # out of range: huge critical values relative to the codebook step
+    big = lin.O_vals.reshape(-1, 8).float() * 1e4
+    none = critical_lists(big.half(), lin.O_col, lin.O_row_ptr, N, unit=0.1, code_max=2.0)
+    assert none == (None, None, None)
+    ok = critical_lists(lin.O_vals, lin.O_col, lin.O_row_ptr, N, unit=0.1, code_max=2.0)
+    assert ok[0] is not None and CRIT_ROW_LIMIT > 0
