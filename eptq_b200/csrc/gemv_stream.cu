@@ -594,20 +594,23 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
                 // This lane: row lane>>1 of each 16-row tile, dimensions 4*(lane&1)..+3.  The buffer stores
                 // dimension d at d ^ 4*((row>>2)&1) ^ digit: the halves of a row swap when bit 2 of the row is
                 // set, and the high-digit words are pairwise exchanged.
-                uint4 lo[4], hi[4];
-                float4 cr[4];
+                // sums of the four 16-row tiles as floats (digits combined, corrections added, scaled): 16 registers
+                float4 v[4];
                 const unsigned my = static_cast<unsigned>((lane * 4) ^ (((lane >> 3) & 1) << 2));
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    lo[j] = lds128(buf + (j * 128 + my) * 4);
-                    const uint4 hsw = lds128(buf + 2048 + (j * 128 + my) * 4);
-                    hi[j] = make_uint4(hsw.y, hsw.x, hsw.w, hsw.z);
-                    cr[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    const uint4 lo = lds128(buf + (j * 128 + my) * 4);
+                    const uint4 hsw = lds128(buf + 2048 + (j * 128 + my) * 4);      // words pairwise exchanged
+                    float4 cr = make_float4(0.f, 0.f, 0.f, 0.f);
                     if (P.use_lists) {
                         const uint4 c = lds128(kCorr + b * 2048 + (j * 128 + lane * 4) * 4);
-                        cr[j] = make_float4(static_cast<float>(static_cast<int>(c.x)) * kCorrStep, static_cast<float>(static_cast<int>(c.y)) * kCorrStep,
-                                            static_cast<float>(static_cast<int>(c.z)) * kCorrStep, static_cast<float>(static_cast<int>(c.w)) * kCorrStep);
+                        cr = make_float4(static_cast<float>(static_cast<int>(c.x)) * kCorrStep, static_cast<float>(static_cast<int>(c.y)) * kCorrStep,
+                                         static_cast<float>(static_cast<int>(c.z)) * kCorrStep, static_cast<float>(static_cast<int>(c.w)) * kCorrStep);
                     }
+                    v[j].x = (fmaf(256.f, static_cast<float>(static_cast<int>(hsw.y)), static_cast<float>(static_cast<int>(lo.x))) + cr.x) * scale;
+                    v[j].y = (fmaf(256.f, static_cast<float>(static_cast<int>(hsw.x)), static_cast<float>(static_cast<int>(lo.y))) + cr.y) * scale;
+                    v[j].z = (fmaf(256.f, static_cast<float>(static_cast<int>(hsw.w)), static_cast<float>(static_cast<int>(lo.z))) + cr.z) * scale;
+                    v[j].w = (fmaf(256.f, static_cast<float>(static_cast<int>(hsw.z)), static_cast<float>(static_cast<int>(lo.w))) + cr.w) * scale;
                 }
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
@@ -620,13 +623,8 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const __
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const int rt16 = sg.rt * 4 + j;
-                    if (rt16 < L.row_tiles) {
-                        float* dst = p.acc + L.acc_off + static_cast<size_t>(rt16) * p.B * 128 + lane * 4;
-                        red_add4(dst, (fmaf(256.f, static_cast<float>(static_cast<int>(hi[j].x)), static_cast<float>(static_cast<int>(lo[j].x))) + cr[j].x) * scale,
-                                 (fmaf(256.f, static_cast<float>(static_cast<int>(hi[j].y)), static_cast<float>(static_cast<int>(lo[j].y))) + cr[j].y) * scale,
-                                 (fmaf(256.f, static_cast<float>(static_cast<int>(hi[j].z)), static_cast<float>(static_cast<int>(lo[j].z))) + cr[j].z) * scale,
-                                 (fmaf(256.f, static_cast<float>(static_cast<int>(hi[j].w)), static_cast<float>(static_cast<int>(lo[j].w))) + cr[j].w) * scale);
-                    }
+                    if (rt16 < L.row_tiles)
+                        red_add4(p.acc + L.acc_off + static_cast<size_t>(rt16) * p.B * 128 + lane * 4, v[j].x, v[j].y, v[j].z, v[j].w);
                 }
                 const unsigned weight = static_cast<unsigned>(sg.n);
                 const float* inv_rms = L.x_op == EPTQ_X_RMSNORM ? misc + 48 : nullptr;
