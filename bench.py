@@ -647,6 +647,29 @@ def run_gpu_arm(args):
             torch.cuda.empty_cache()
         decode_stats["config"] = ("llama2-7b architecture, random init, 32 layers, 512-token prompt + 128 greedy "
                                   f"tokens, batch 1, tp{world}, one CUDA graph per token")
+        if world > 1 and not args.no_extras:
+            # The baseline's fifth configuration: Llama-2-70B architecture, E8 codebook, tensor-parallel over all
+            # ranks, batch 1, 1024-token prompt; all 80 decoder layers, 32 new tokens to keep the run short.
+            try:
+                h70, i70, n70, heads70, kv70, v70 = ARCHITECTURES["llama2-70b"]
+                qz = E8LatticeQuantizer(radius=1.6)
+                qz.remove_last()
+                eng = synthetic_llama_engine(h70, i70, n70, heads70, kv70, v70, "e8_lattice", qz.points.to(dev),
+                                             max_len=1024 + 32, batch=1, device=str(dev), tp_rank=rank, tp_size=world,
+                                             tp_group=dist.group.WORLD, comm=comm)
+                ids70 = torch.randint(0, v70, (1, 1024), generator=torch.Generator().manual_seed(1)).to(dev)
+                eng.decode(ids70, 4)
+                _, st = eng.decode(ids70, 32)
+                t = torch.tensor([st["decode_s"]], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                decode_stats["llama2_70b_e8"] = {"tokens_per_s": 31 / float(t.item()), "ms_per_token": 1e3 * float(t.item()) / 31,
+                                                 "prefill_s": st["prefill_s"],
+                                                 "config": f"llama2-70b architecture, random init, 80 layers, E8 r=1.6, 1024-token "
+                                                           f"prompt + 32 greedy tokens, batch 1, tp{world}"}
+                del eng
+            except Exception as exc:                         # noqa: BLE001 -- never lose the bench line over an extra
+                decode_stats["llama2_70b_e8"] = {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
+            torch.cuda.empty_cache()
         if world > 1:
             # The tensor-parallel token step (sharded GEMV launches, chained MLP, push all-reduce) against the same
             # model unsharded on this GPU: logits of one decoded token after a 32-token prompt, 2 decoder layers.

@@ -32,6 +32,16 @@ struct LmArgs {
     float eps;
 };
 
+// Order of the pick, as torch.argmax has it: a NaN ranks above every number, equal values (and NaNs among
+// themselves) go to the lower index.  Any real candidate beats the start value (-inf, INT_MAX), so the result is a
+// valid row whatever the logits are -- a token outside the vocabulary would fault the next embedding lookup.
+__device__ __forceinline__ bool better_pick(float v, int i, float m, int mi) {
+    const bool vn = v != v, mn = m != m;
+    if (vn != mn) return vn;
+    if (!vn && v != m) return v > m;
+    return i < mi;
+}
+
 __global__ void __launch_bounds__(kLmThreads) lm_head_argmax_kernel(const LmArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
     __half* xs = reinterpret_cast<__half*>(smem);                        // [B][H]
@@ -112,7 +122,7 @@ __global__ void __launch_bounds__(kLmThreads) lm_head_argmax_kernel(const LmArgs
             const __half h = __float2half_rn(v);
             if (lane == 0 && a.logits != nullptr) a.logits[static_cast<size_t>(b) * a.V + row] = h;
             const float hv = __half2float(h);
-            if (hv > best[b] || (hv == best[b] && row < best_i[b])) { best[b] = hv; best_i[b] = row; }
+            if (better_pick(hv, row, best[b], best_i[b])) { best[b] = hv; best_i[b] = row; }
         }
     }
     if (lane == 0) {
@@ -125,7 +135,7 @@ __global__ void __launch_bounds__(kLmThreads) lm_head_argmax_kernel(const LmArgs
         float m = -INFINITY;
         int mi = 0x7fffffff;
         for (int w = 0; w < kLmThreads / 32; ++w)
-            if (red[w][b] > m || (red[w][b] == m && redi[w][b] < mi)) { m = red[w][b]; mi = redi[w][b]; }
+            if (better_pick(red[w][b], redi[w][b], m, mi)) { m = red[w][b]; mi = redi[w][b]; }
         a.part_val[blockIdx.x * a.B + b] = m;
         a.part_idx[blockIdx.x * a.B + b] = mi;
     }
@@ -144,9 +154,9 @@ __global__ void __launch_bounds__(kLmThreads) lm_head_argmax_kernel(const LmArgs
         for (unsigned k = 0; k < gridDim.x; ++k) {
             const float v = __ldcg(a.part_val + k * a.B + b);
             const int i = __ldcg(a.part_idx + k * a.B + b);
-            if (v > m || (v == m && i < mi)) { m = v; mi = i; }
+            if (better_pick(v, i, m, mi)) { m = v; mi = i; }
         }
-        a.tokens[b] = mi;
+        a.tokens[b] = (mi >= 0 && mi < a.V) ? mi : 0;
     }
 }
 

@@ -582,7 +582,10 @@ def synthetic_llama_engine(hidden: int, intermediate: int, n_layers: int, n_head
         for k, (name, (o, i)) in enumerate(shapes.items()):
             qd = make_layer(o, i, seed=seed + 1000 * lid + k, outlier_frac=outlier_frac, device=str(dev),
                             scale_sigma=0.05)
-            qd.g = (qd.g.float() * (init_std * 1.5)).to(torch.float16)
+            # wider and deeper stacks get proportionally smaller row scales, so that the residual stream of a
+            # random-init model stays finite in fp16 (no effect at hidden size 4096 and 32 layers or fewer)
+            damp = (4096.0 / max(hidden, 4096)) ** 0.5 * (32.0 / max(n_layers, 32)) ** 0.5
+            qd.g = (qd.g.float() * (init_std * 1.5 * damp)).to(torch.float16)
             qd = shard_layer(qd, name, tp_rank, tp_size)
             mods[name] = EPTQLinear.from_quantized_data(qd, codebook, quantizer_type)
         ones = torch.ones(hidden, dtype=torch.float16, device=dev)

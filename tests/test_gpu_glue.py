@@ -109,3 +109,20 @@ def test_lm_head_argmax_matches_torch(B, V, H, norm):
         assert bool((want_logits.max(dim=-1).values - picked <= 2e-3 * want_logits.abs().max()).all())
         t2, none = glue.lm_head_argmax(x, W, w, eps)
         assert none is None and torch.equal(t2, tokens)
+
+
+def test_lm_head_argmax_always_names_a_vocabulary_row():
+    """Non-finite activations (a model that overflowed) still give a token inside the vocabulary, picked like
+    torch.argmax does: a NaN logit ranks above every number, ties go to the lower index."""
+    from eptq_b200.kernels import glue
+    g = torch.Generator(device="cuda").manual_seed(5)
+    V, H = 3000, 512
+    W = (0.05 * torch.randn(V, H, generator=g, device="cuda")).half()
+    x = torch.randn(2, H, generator=g, device="cuda").half()
+    x[0, 7] = float("nan")                                  # every logit of row 0 becomes NaN
+    x[1, 3] = float("inf")                                  # +-inf logits in row 1 (NaN where the weight is 0)
+    tokens, logits = glue.lm_head_argmax(x, W, None, 1e-5, want_logits=True)
+    torch.cuda.synchronize()
+    assert bool(((tokens >= 0) & (tokens < V)).all())
+    assert torch.equal(tokens, logits.float().argmax(dim=-1))
+    assert int(tokens[0]) == 0
