@@ -666,7 +666,20 @@ def run_gpu_arm(args):
                                                  "prefill_s": st["prefill_s"],
                                                  "config": f"llama2-70b architecture, random init, 80 layers, E8 r=1.6, 1024-token "
                                                            f"prompt + 32 greedy tokens, batch 1, tp{world}"}
+                # the same weights at batch 8 (GEMV passes of two rows; reductions of 8 x 8192 values go through NCCL)
+                from eptq_b200.engine import LlamaDecodeEngine
+                eng8 = LlamaDecodeEngine(eng.layers, eng.embed, eng.final_norm, eng.lm_head, eng.inv_freq, eng.eps,
+                                         eng.head_dim, eng.n_heads, eng.n_kv_heads, 1024 + 32, batch=8,
+                                         tp_group=dist.group.WORLD, comm=comm)
                 del eng
+                ids8 = torch.randint(0, v70, (8, 1024), generator=torch.Generator().manual_seed(2)).to(dev)
+                eng8.decode(ids8, 4)
+                _, st8 = eng8.decode(ids8, 16)
+                t = torch.tensor([st8["decode_s"]], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                decode_stats["llama2_70b_e8"]["batch8"] = {"tokens_per_s": 15 * 8 / float(t.item()),
+                                                           "ms_per_step": 1e3 * float(t.item()) / 15}
+                del eng8
             except Exception as exc:                         # noqa: BLE001 -- never lose the bench line over an extra
                 decode_stats["llama2_70b_e8"] = {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
             torch.cuda.empty_cache()
