@@ -214,7 +214,7 @@ class LlamaDecodeEngine:
         all-reduce adds them to the residual stream (eight launches).  (gate/up -> down as two phases of one
         chained launch was measured here too: 425 against 433 tokens/s at two GPUs, so the separate launches stay.)"""
         from . import _lib
-        from .kernels import glue, linear_forward_group
+        from .kernels import glue, linear_forward_chain, linear_forward_group
         B = ids.shape[0]
         hd, nh, nkv = self.head_dim, self.n_heads, self.n_kv_heads
         x = F.embedding(ids, self.embed).reshape(B, -1).contiguous()                # residual stream, updated in place
@@ -240,6 +240,16 @@ class LlamaDecodeEngine:
             else:                                   # partial sums: the reduction adds them to the residual stream
                 self.comm.all_reduce_(linear_forward_group(P["o"], [att], [L.o.out_features])[0], residual=x)
             gate, up = linear_forward_group(P["gate_up"], [x, x], [L.gate.out_features, L.up.out_features], fusions=gu_f)
+            d = P["down"][0]
+            if B == 1 and bool(d.table8) and d.table8_scale > 0 and d.N % 64 == 0 and d.N <= 25600:
+                # the streaming kernel forms silu(gate) * up as it reads its input: no launch for it
+                f = fus(_lib.X_SILU_MUL, x_aux=up) if self.tp_group is not None else \
+                    fus(_lib.X_SILU_MUL, _lib.Y_ADD_RESIDUAL, residual=x, x_aux=up)
+                out = linear_forward_chain(P["down"], [0], [gate], [0 if self.tp_group is None else L.down.out_features],
+                                           [f], ys=[x] if self.tp_group is None else None)
+                if self.tp_group is not None:
+                    self.comm.all_reduce_(out[0], residual=x)
+                continue
             act = glue.silu_mul(gate, up)
             if self.tp_group is None:
                 linear_forward_group(P["down"], [act], [0], fusions=res_f, ys=[x])
