@@ -668,9 +668,9 @@ def run_gpu_arm(args):
                                                            f"prompt + 32 greedy tokens, batch 1, tp{world}"}
                 # the same weights at batch 8 (GEMV passes of two rows; reductions of 8 x 8192 values go through NCCL)
                 from eptq_b200.engine import LlamaDecodeEngine
-                eng8 = LlamaDecodeEngine(eng.layers, eng.embed, eng.final_norm, eng.lm_head, eng.inv_freq, eng.eps,
-                                         eng.head_dim, eng.n_heads, eng.n_kv_heads, 1024 + 32, batch=8,
-                                         tp_group=dist.group.WORLD, comm=comm)
+                layers70 = eng.layers
+                head70 = (eng.embed, eng.final_norm, eng.lm_head, eng.inv_freq, eng.eps, eng.head_dim, eng.n_heads, eng.n_kv_heads)
+                eng8 = LlamaDecodeEngine(layers70, *head70, 1024 + 32, batch=8, tp_group=dist.group.WORLD, comm=comm)
                 del eng
                 ids8 = torch.randint(0, v70, (8, 1024), generator=torch.Generator().manual_seed(2)).to(dev)
                 eng8.decode(ids8, 4)
@@ -680,6 +680,17 @@ def run_gpu_arm(args):
                 decode_stats["llama2_70b_e8"]["batch8"] = {"tokens_per_s": 15 * 8 / float(t.item()),
                                                            "ms_per_step": 1e3 * float(t.item()) / 15}
                 del eng8
+                torch.cuda.empty_cache()
+                # and at batch 64 (the linears take the tensor-core GEMM path), 8 steps
+                eng64 = LlamaDecodeEngine(layers70, *head70, 1024 + 16, batch=64, tp_group=dist.group.WORLD, comm=comm)
+                ids64 = torch.randint(0, v70, (64, 1024), generator=torch.Generator().manual_seed(3)).to(dev)
+                eng64.decode(ids64, 3)
+                _, st64 = eng64.decode(ids64, 9)
+                t = torch.tensor([st64["decode_s"]], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                decode_stats["llama2_70b_e8"]["batch64"] = {"tokens_per_s": 8 * 64 / float(t.item()),
+                                                            "ms_per_step": 1e3 * float(t.item()) / 8}
+                del eng64, layers70, head70
             except Exception as exc:                         # noqa: BLE001 -- never lose the bench line over an extra
                 decode_stats["llama2_70b_e8"] = {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
             torch.cuda.empty_cache()
