@@ -21,10 +21,22 @@ batch B (default 1), i.e. the quantized-linear work of one decode token.
   cpu_baseline  the reconstruct-then-matmul CPU path (numpy port of the
             reference's dequantize_layer, torch CPU matmul) on a bounded sample
 
+Further objects on the same line (skipped with --no-extras / --no-decode /
+--no-e8): `realistic_grouping` (the four stream-ordered launches per decoder
+layer a model can issue), `chained_layer` (the same as one chained launch),
+`batch4`, `batch16`, `e8_layer_set`, `gemm` (prefill shapes of the baseline's
+fourth configuration against the tensor peak), `decode` (whole-model tokens/s
+through the decode engine for both codebooks).
+
 With --gpus N > 1 (torchrun) the linears are sharded tensor-parallel
 (q/k/v/gate/up by output rows, o/down by input columns followed by an
 all-reduce: the library's one-shot push kernel over peer memory, or NCCL with
 --nccl) and the whole-model bytes are divided by the slowest rank's time.
+Before anything is timed, `tp_check` compares the sharded, all-reduced outputs
+with the unsharded layer; `decode.tp_step_check` does the same for one token of
+the tensor-parallel engine, and `decode.llama2_70b_e8` decodes the baseline's
+fifth configuration (batches 1, 8 and 64).  A failed check ends the run with
+exit code 3 and an error line instead of a result.
 
 `--impl reference` times the CPU path alone, on rank 0.
 """
